@@ -1,0 +1,522 @@
+// The one tensor-core kernel of the library: a persistent, warp-specialised
+// sm_100a GEMM  D[M,N] = A[M,K] * B[N,K]^T  (both operands K-major, fp32
+// accumulation in tensor memory) whose prologue and epilogue carry the
+// tensor-parallel collectives:
+//
+//   * all-gather prologue  - four "comm" warps in every CTA push this rank's
+//     activation shard into every peer's gather buffer over NVLink (plain
+//     16-byte stores to peer memory) and bump per-chunk arrival counters; the
+//     TMA warp waits (bounded) on the counter of the chunk a tile reads before
+//     it issues the loads, and tiles are visited own-shard-first.
+//     Replaces the reference's copy-engine all-gather + per-rank flags
+//     (src/coll/ths_op/all_gather_op.cc:529-574) and the flag waits inside its
+//     sm90 kernel (src/ag_gemm/sm90_all_gather_gemm_tma_warpspecialized_cooperative.hpp:512-586).
+//   * reduce-scatter epilogue - the epilogue warps store fp32 partial tiles
+//     straight into the staging slot of the rank that owns those rows and bump
+//     that rank's per-tile counter; rows owned by peers are computed first.
+//     Replaces the reference's store-then-pull design
+//     (src/gemm_rs/sm90_epilogue_evt.hpp:231-242, sm90_reduce_scatter_utils.hpp:212-262).
+//   * grouped (MoE) mode - M tiles come from a device-side table, A rows are
+//     fetched by index with TMA gather4, B is the expert's weight slab.
+//
+// Warp roles (320 threads): warp 0 TMA producer, warp 1 UMMA issuer + TMEM
+// owner, warps 2-5 epilogue (one TMEM lane quadrant each), warps 6-9 comm.
+#pragma once
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace fluxb {
+
+constexpr int kBM = 128;          // rows per tile (= TMEM lanes)
+constexpr int kRowBytes = 128;    // bytes of K per smem row (one swizzle span)
+constexpr int kThreads = 320;
+constexpr int kMaxWorld = 8;
+constexpr int kCommSliceBytes = 2048;  // bytes of one row handled by one comm unit
+
+enum EpiMode : int {
+  kEpiStore = 0,    // write D (out dtype) to p.out
+  kEpiRsPush = 1,   // write fp32 partials into the owner's staging slot + counter
+};
+enum OutType : int { kOutBf16 = 0, kOutF16 = 1, kOutF32 = 2 };
+enum BiasMode : int { kBiasNone = 0, kBiasFull = 1, kBiasRow = 2 };
+
+// One M tile of a grouped problem (MoE). `a_row0` indexes the sorted row space.
+struct GroupTile {
+  int a_row0;      // first sorted row of the tile
+  int rows;        // valid rows (1..128)
+  int expert;      // which weight slab
+  int need_mask;   // bit r set = tile reads tokens that live on source rank r
+};
+
+struct GemmParams {
+  CUtensorMap tmap_a;
+  CUtensorMap tmap_b;
+  int M, N, K;
+  // M segmentation: nseg segments of seg_rows rows; tiles never straddle a
+  // segment; segments are visited (seg_first + i) % nseg.
+  int nseg, seg_rows, seg_first;
+  int group_m;  // rasterisation band height in M tiles
+  // epilogue
+  int epi_mode, out_type, bias_mode;
+  void* out;
+  long long ldo;  // elements
+  const void* bias;  // same dtype as out
+  long long ldbias;
+  const float* scale_a;  // per output row (may be null)
+  const float* scale_b;  // per output column (may be null)
+  float alpha;
+  // all-gather: consumer side
+  const int* ag_flags;  // [nseg][ag_flag_stride], null = no waits
+  int ag_flag_stride;
+  int ag_expected;
+  // all-gather: producer side (comm warps)
+  const uint8_t* ag_src;          // this rank's shard, row-major, row_bytes per row
+  uint8_t* ag_dst[kMaxWorld];     // gather buffer of every rank (own included)
+  int* ag_dst_flags[kMaxWorld];   // flag array of every rank
+  const float* ag_src_scale;      // optional per-row scales of the shard
+  float* ag_dst_scale[kMaxWorld];
+  long long ag_row_bytes;
+  int rank, world;
+  // reduce-scatter push
+  float* rs_stage[kMaxWorld];  // rs_stage[o] = slot of this rank inside owner o's staging
+  int* rs_cnt[kMaxWorld];      // per-tile counters at owner o: [tiles_per_seg][n_tiles]
+  // grouped mode
+  const GroupTile* g_tiles;  // null = dense
+  const int* g_num_tiles;    // device scalar
+  const int* g_gather;       // sorted row -> source row of A
+  int g_rows_per_expert_b;   // rows of B per expert (= N)
+  const float* g_expert_scale;  // optional per-expert alpha
+  const int* g_scatter_rows;    // optional: sorted row -> output row (null = identity)
+  int g_rows_per_rank;          // tokens per source rank (for need_mask -> flags)
+  // status / bounded waits
+  int* status;
+  unsigned long long timeout_ns;
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kABytes = kBM * kRowBytes;
+  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
+  static constexpr int kTotal = kMiscOffset + 64 + 1024;  // + slack for 1024-byte alignment
+};
+
+struct TileCoord {
+  int row0;        // first A row (global row, or sorted row in grouped mode)
+  int rows;        // valid rows
+  int n0;          // first output column
+  int seg, chunk;  // segment and 128-row chunk inside it (dense)
+  int b_row0;      // first B row
+  int n_idx;
+  int need_mask;
+  int expert;
+};
+
+__device__ __forceinline__ int imin(int a, int b) { return a < b ? a : b; }
+
+template <int BN>
+__device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_tiles, int n_tiles,
+                                            int tps, TileCoord& tc) {
+  const int gmn = p.group_m * n_tiles;
+  const int band = t / gmn;
+  const int r = t - band * gmn;
+  const int gm_eff = imin(p.group_m, m_tiles - band * p.group_m);
+  const int m_idx = band * p.group_m + r % gm_eff;
+  const int n_idx = r / gm_eff;
+  tc.n_idx = n_idx;
+  tc.n0 = n_idx * BN;
+  if (p.g_tiles == nullptr) {
+    const int sp = m_idx / tps;
+    const int c = m_idx - sp * tps;
+    int seg = p.seg_first + sp;
+    if (seg >= p.nseg) seg -= p.nseg;
+    tc.seg = seg;
+    tc.chunk = c;
+    tc.row0 = seg * p.seg_rows + c * kBM;
+    tc.rows = imin(kBM, p.seg_rows - c * kBM);
+    tc.b_row0 = tc.n0;
+    tc.need_mask = 0;
+    tc.expert = 0;
+  } else {
+    const GroupTile g = p.g_tiles[m_idx];
+    tc.seg = 0;
+    tc.chunk = m_idx;
+    tc.row0 = g.a_row0;
+    tc.rows = g.rows;
+    tc.expert = g.expert;
+    tc.b_row0 = g.expert * p.g_rows_per_expert_b + tc.n0;
+    tc.need_mask = g.need_mask;
+  }
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+__device__ __forceinline__ uint32_t pack_f16(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// KIND: 0 = 16-bit inputs (bf16/f16 chosen by `ab_format`), 1 = fp8
+template <int BN, int STAGES, int KIND>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr int ELT = (KIND == 0) ? 2 : 1;
+  constexpr int BKE = kRowBytes / ELT;            // K elements per stage
+  constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
+                                 : (2 * BN <= 256) ? 256 : 512;
+  static_assert(2 * BN <= 512, "two accumulators must fit in tensor memory");
+  static_assert(BN % 32 == 0, "epilogue reads 32 columns at a time");
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint32_t* tmem_holder = reinterpret_cast<uint32_t*>(smem + L::kMiscOffset);
+  volatile int* s_abort = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 8);
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_base = smem_u32(bars);
+  auto bar_full = [&](int s) { return bar_base + 8u * s; };
+  auto bar_empty = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto bar_tfull = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
+  auto bar_tempty = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  auto smem_a = [&](int s) { return smem_base + s * L::kStageBytes; };
+  auto smem_b = [&](int s) { return smem_base + s * L::kStageBytes + L::kABytes; };
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const uint64_t budget = p.timeout_ns;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0;
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full(s), 1);
+      mbar_init(bar_empty(s), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull(a), 1);
+      mbar_init(bar_tempty(a), 4);
+    }
+    mbar_init_fence();
+    tma_prefetch_desc(&p.tmap_a);
+    tma_prefetch_desc(&p.tmap_b);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_holder;
+
+  const int n_tiles = (p.N + BN - 1) / BN;
+  int tps = 1, m_tiles;
+  if (p.g_tiles == nullptr) {
+    tps = (p.seg_rows + kBM - 1) / kBM;
+    m_tiles = p.nseg * tps;
+  } else {
+    m_tiles = *p.g_num_tiles;
+  }
+  const int total_tiles = m_tiles * n_tiles;
+  const int num_kb = (p.K + BKE - 1) / BKE;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------------ TMA
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+        TileCoord tc;
+        decode_tile<BN>(p, t, m_tiles, n_tiles, tps, tc);
+        if (p.ag_flags != nullptr) {
+          if (p.g_tiles == nullptr) {
+            ok = flag_wait_eq(p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk, p.ag_expected,
+                              s_abort, kStatusTimeoutFlag, budget);
+          } else {
+            // grouped: wait for every chunk of every source rank the tile touches
+            const int chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
+            for (int r = 0; ok && r < p.world; ++r) {
+              if (!((tc.need_mask >> r) & 1)) continue;
+              for (int c = 0; ok && c < chunks; ++c)
+                ok = flag_wait_eq(p.ag_flags + r * p.ag_flag_stride + c, p.ag_expected, s_abort,
+                                  kStatusTimeoutFlag, budget);
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async();
+        }
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty(stage), phase ^ 1u, s_abort, kStatusTimeoutSmemEmpty, budget)) {
+            ok = false;
+            break;
+          }
+          mbar_arrive_expect_tx(bar_full(stage), L::kStageBytes);
+          if (p.g_tiles == nullptr) {
+            tma_load_2d(smem_a(stage), &p.tmap_a, bar_full(stage), kb * BKE, tc.row0);
+          } else {
+            // 32 gather4 copies of 4 rows each; rows past the tile end re-read row 0 of the tile
+            const int* gi = p.g_gather + tc.row0;
+            for (int q = 0; q < kBM / 4; ++q) {
+              const int r0 = q * 4;
+              const int i0 = gi[r0 < tc.rows ? r0 : 0];
+              const int i1 = gi[r0 + 1 < tc.rows ? r0 + 1 : 0];
+              const int i2 = gi[r0 + 2 < tc.rows ? r0 + 2 : 0];
+              const int i3 = gi[r0 + 3 < tc.rows ? r0 + 3 : 0];
+              tma_gather4_2d(smem_a(stage) + q * 4 * kRowBytes, &p.tmap_a, bar_full(stage),
+                             kb * BKE, i0, i1, i2, i3);
+            }
+          }
+          tma_load_2d(smem_b(stage), &p.tmap_b, bar_full(stage), kb * BKE, tc.b_row0);
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ----------------------------------------------------------------- UMMA
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
+        const int acc = it & 1;
+        const uint32_t acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty(acc), acc_phase ^ 1u, s_abort, kStatusTimeoutTmemEmpty, budget))
+          break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full(stage), phase, s_abort, kStatusTimeoutSmemFull, budget)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t a_desc = make_kmajor_sw128_desc(smem_a(stage));
+          const uint64_t b_desc = make_kmajor_sw128_desc(smem_b(stage));
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            // each UMMA consumes 32 bytes of K: advance the start address by 32 B (>>4 = 2)
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            if (KIND == 0)
+              umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+            else
+              umma_f8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+          }
+          umma_commit(bar_empty(stage));
+          if (++stage == STAGES) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (ok) umma_commit(bar_tfull(acc));
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------- epilogue
+    const int quad = warp & 3;
+    const int row_in_tile = quad * 32 + lane;
+    int it = 0;
+    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+      const int acc = it & 1;
+      const uint32_t acc_phase = (it >> 1) & 1;
+      TileCoord tc;
+      decode_tile<BN>(p, t, m_tiles, n_tiles, tps, tc);
+      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget)) break;
+      tc_fence_after();
+      const bool row_ok = row_in_tile < tc.rows;
+      const int grow = tc.row0 + row_in_tile;  // global / sorted row
+      float row_scale = p.alpha;
+      if (p.scale_a != nullptr && row_ok) row_scale *= p.scale_a[grow];
+      if (p.g_expert_scale != nullptr) row_scale *= p.g_expert_scale[tc.expert];
+
+      // destination row pointer
+      uint8_t* dst_row = nullptr;
+      const uint8_t* bias_row = nullptr;
+      if (p.epi_mode == kEpiStore) {
+        long long orow = grow;
+        if (p.g_scatter_rows != nullptr && row_ok) orow = p.g_scatter_rows[grow];
+        const int osz = (p.out_type == kOutF32) ? 4 : 2;
+        dst_row = static_cast<uint8_t*>(p.out) + orow * p.ldo * osz;
+        if (p.bias_mode == kBiasFull)
+          bias_row = static_cast<const uint8_t*>(p.bias) + orow * p.ldbias * osz;
+        else if (p.bias_mode == kBiasRow)
+          bias_row = static_cast<const uint8_t*>(p.bias);
+      } else {
+        // reduce-scatter: the segment is the owner, the row inside it is the owner's local row
+        const long long lrow = static_cast<long long>(tc.chunk) * kBM + row_in_tile;
+        dst_row = reinterpret_cast<uint8_t*>(p.rs_stage[tc.seg] + lrow * p.N);
+        if (p.bias_mode == kBiasFull)
+          bias_row = static_cast<const uint8_t*>(p.bias) + static_cast<long long>(grow) * p.ldbias * 2;
+      }
+
+#pragma unroll 1
+      for (int c = 0; c < BN / 32; ++c) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                               static_cast<uint32_t>(acc * BN + c * 32);
+        tmem_ld_32x32(taddr, r);
+        tmem_ld_wait();
+        const int col0 = tc.n0 + c * 32;
+        if (row_ok && col0 < p.N) {
+        float v[32];
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_scale;
+        if (p.scale_b != nullptr) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (col0 + j < p.N) v[j] *= p.scale_b[col0 + j];
+        }
+        if (bias_row != nullptr) {
+          // bias has the output dtype in store mode, bf16 in reduce-scatter mode
+          const int bt = (p.epi_mode == kEpiStore) ? p.out_type : kOutBf16;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            if (col0 + j < p.N) {
+              float b;
+              if (bt == kOutBf16)
+                b = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(bias_row)[col0 + j]);
+              else if (bt == kOutF16)
+                b = __half2float(reinterpret_cast<const __half*>(bias_row)[col0 + j]);
+              else
+                b = reinterpret_cast<const float*>(bias_row)[col0 + j];
+              v[j] += b;
+            }
+          }
+        }
+        if (p.epi_mode == kEpiRsPush || p.out_type == kOutF32) {
+          float* d = reinterpret_cast<float*>(dst_row) + col0;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (col0 + q * 4 + 4 <= p.N) {
+              *reinterpret_cast<float4*>(d + q * 4) =
+                  make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (col0 + q * 4 + j < p.N) d[q * 4 + j] = v[q * 4 + j];
+            }
+          }
+        } else {
+          uint16_t* d = reinterpret_cast<uint16_t*>(dst_row) + col0;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              w[j] = (p.out_type == kOutBf16) ? pack_bf16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1])
+                                              : pack_f16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+            if (col0 + q * 8 + 8 <= p.N) {
+              *reinterpret_cast<uint4*>(d + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                if (col0 + q * 8 + j < p.N)
+                  d[q * 8 + j] = static_cast<uint16_t>((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xFFFFu));
+            }
+          }
+        }
+        }  // row_ok && col0 < N
+        __syncwarp();
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar_tempty(acc));
+      if (p.epi_mode == kEpiRsPush) {
+        // this warp's 32 rows of the tile are stored: publish them to the owner. Each of
+        // the four epilogue warps adds 1, so a complete tile counts 4 per source rank.
+        // (No CTA-wide barrier here: a role that gave up must never strand the others.)
+        if (lane == 0) {
+          fence_acq_rel_sys();
+          red_add_release_sys(p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx, 1);
+        }
+      }
+    }
+  } else {
+    // ----------------------------------------------------------------- comm
+    if (p.ag_src != nullptr) {
+      const int ctid = threadIdx.x - 6 * 32;  // 0..127
+      const int chunks = (p.seg_rows + kBM - 1) / kBM;
+      const int nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+      const int per_dest = chunks * nslices;
+      const int total_units = p.world * per_dest;
+      for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
+        const int d = u / per_dest;
+        const int rem = u - d * per_dest;
+        const int chunk = rem / nslices;
+        const int ks = rem - chunk * nslices;
+        int dest = p.rank - d;  // self first, then the rank that needs this shard soonest
+        if (dest < 0) dest += p.world;
+        const int r0 = chunk * kBM;
+        const int r1 = imin(r0 + kBM, p.seg_rows);
+        const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
+        const long long b1 = (b0 + kCommSliceBytes < p.ag_row_bytes) ? b0 + kCommSliceBytes : p.ag_row_bytes;
+        const int vec_per_row = static_cast<int>((b1 - b0) >> 4);
+        const uint8_t* src = p.ag_src + static_cast<long long>(r0) * p.ag_row_bytes + b0;
+        uint8_t* dst = p.ag_dst[dest] +
+                       (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0;
+        // one 16-byte column of the slice per thread, 8 rows in flight
+        const int nrows = r1 - r0;
+        if (ctid < vec_per_row) {
+          const uint8_t* s0 = src + ctid * 16;
+          uint8_t* d0 = dst + ctid * 16;
+          for (int rr = 0; rr < nrows; rr += 8) {
+            uint4 val[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (rr + j < nrows)
+                val[j] = __ldg(reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes));
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (rr + j < nrows)
+                *reinterpret_cast<uint4*>(d0 + (rr + j) * p.ag_row_bytes) = val[j];
+          }
+        }
+        if (ks == 0 && p.ag_src_scale != nullptr) {
+          float* sd = p.ag_dst_scale[dest] + static_cast<long long>(p.rank) * p.seg_rows;
+          for (int rr = r0 + ctid; rr < r1; rr += 128) sd[rr] = p.ag_src_scale[rr];
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ctid == 0) {
+          fence_acq_rel_sys();
+          red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk, 1);
+        }
+      }
+    }
+  }
+
+  // ------------------------------------------------------------------ teardown
+  __syncthreads();
+  const int err = *s_abort;
+  if (err != 0) {
+    if (threadIdx.x == 0) {
+      *reinterpret_cast<volatile int*>(p.status) = err;
+      __threadfence_system();
+    }
+    // let copies and MMAs that are still in flight land before the CTA's memory goes away
+    __nanosleep(200000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    __syncwarp();
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+}  // namespace fluxb

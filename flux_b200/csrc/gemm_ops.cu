@@ -1,0 +1,514 @@
+// Host side of the dense ops: the launcher of the fused kernel, the plain
+// GEMM entry point, AG-GEMM and GEMM-RS (with the owner-side fp32 reduction).
+#include <string.h>
+
+#include "internal.h"
+
+namespace fluxb {
+
+// ---------------------------------------------------------------------------
+// launcher
+// ---------------------------------------------------------------------------
+template <int BN, int STAGES, int KIND>
+static int launch_inst(const GemmParams& p, uint32_t idesc, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES>;
+  static_assert(L::kTotal <= 232448, "shared memory budget exceeded");
+  auto kern = fused_gemm_kernel<BN, STAGES, KIND>;
+  static bool configured[64] = {};
+  int dev = 0;
+  FLUXB_CUDA(cudaGetDevice(&dev));
+  if (dev < 64 && !configured[dev]) {
+    FLUXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured[dev] = true;
+  }
+  kern<<<grid, kThreads, L::kTotal, stream>>>(p, idesc);
+  FLUXB_CUDA(cudaGetLastError());
+  return FLUXB_OK;
+}
+
+static int pick_block_n(long long m_tiles, int n, int ctas) {
+  // cost = waves * tile width, with a small penalty for narrow tiles (more
+  // operand traffic per flop); the candidate with the lowest cost wins.
+  const int cand[4] = {256, 192, 128, 64};
+  const double pen[4] = {1.00, 1.04, 1.10, 1.30};
+  int best = 256;
+  double best_cost = 1e30;
+  for (int i = 0; i < 4; ++i) {
+    const int bn = cand[i];
+    if (bn > 64 && n <= bn / 2) continue;
+    const long long tiles = m_tiles * ((n + bn - 1) / bn);
+    const long long waves = (tiles + ctas - 1) / ctas;
+    const double cost = static_cast<double>(waves) * bn * pen[i];
+    if (cost < best_cost) {
+      best_cost = cost;
+      best = bn;
+    }
+  }
+  return best;
+}
+
+int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tuning* tuning,
+                    long long m_tiles_hint) {
+  int bn = (tuning != nullptr) ? tuning->block_n : 0;
+  if (bn == 0) {
+    long long m_tiles = m_tiles_hint;
+    if (m_tiles <= 0) m_tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + kBM - 1) / kBM);
+    int ctas = (tuning != nullptr && tuning->num_ctas > 0) ? tuning->num_ctas : comm->sm_count;
+    bn = pick_block_n(m_tiles, p.N, ctas);
+  }
+  return bn;
+}
+
+int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
+                      const fluxb_tuning* tuning, cudaStream_t stream) {
+  const int bn = resolve_block_n(comm, p, tuning, p.g_tiles != nullptr ? 1024 : 0);
+  FLUXB_REQUIRE(bn == 64 || bn == 128 || bn == 192 || bn == 256, "block_n=%d not in {64,128,192,256}", bn);
+  int grid = comm->sm_count;
+  if (tuning != nullptr && tuning->num_ctas > 0) grid = tuning->num_ctas < grid ? tuning->num_ctas : grid;
+  if (p.g_tiles == nullptr) {
+    const long long tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + kBM - 1) / kBM) *
+                            ((p.N + bn - 1) / bn);
+    // the all-gather push is spread over every CTA's comm warps, so keep the full grid there
+    if (p.ag_src == nullptr && tiles < grid) grid = static_cast<int>(tiles);
+  }
+  if (grid < 1) grid = 1;
+  if (p.group_m <= 0) p.group_m = (tuning != nullptr && tuning->group_m > 0) ? tuning->group_m : 8;
+  p.status = comm->status_dev;
+  p.timeout_ns = comm->timeout_ns;
+  p.rank = comm->rank;
+  p.world = comm->world;
+  const int kind = is_fp8(in_dtype) ? 1 : 0;
+  uint32_t fmt;
+  switch (in_dtype) {
+    case FLUXB_BF16: fmt = 1; break;
+    case FLUXB_F16: fmt = 0; break;
+    case FLUXB_E4M3: fmt = 0; break;
+    case FLUXB_E5M2: fmt = 1; break;
+    default: FLUXB_FAIL(FLUXB_ERR_INVALID, "input dtype %d is not bf16/f16/e4m3/e5m2", in_dtype);
+  }
+  const uint32_t idesc = make_idesc(fmt, kBM, static_cast<uint32_t>(bn));
+#define FLUXB_LAUNCH(BN_, ST_)                                               \
+  (kind == 0 ? launch_inst<BN_, ST_, 0>(p, idesc, grid, stream)              \
+             : launch_inst<BN_, ST_, 1>(p, idesc, grid, stream))
+  switch (bn) {
+    case 256: return FLUXB_LAUNCH(256, 4);
+    case 192: return FLUXB_LAUNCH(192, 5);
+    case 128: return FLUXB_LAUNCH(128, 6);
+    default: return FLUXB_LAUNCH(64, 8);
+  }
+#undef FLUXB_LAUNCH
+}
+
+static int out_type_of(int out_dtype, int* ot) {
+  switch (out_dtype) {
+    case FLUXB_BF16: *ot = kOutBf16; return FLUXB_OK;
+    case FLUXB_F16: *ot = kOutF16; return FLUXB_OK;
+    case FLUXB_F32: *ot = kOutF32; return FLUXB_OK;
+    default: FLUXB_FAIL(FLUXB_ERR_INVALID, "output dtype %d is not bf16/f16/f32", out_dtype);
+  }
+}
+
+static int check_gemm_shapes(const char* who, int m, int n, int k, int in_dtype, int out_dtype) {
+  const int eb = dtype_bytes(in_dtype);
+  FLUXB_REQUIRE(is_16bit(in_dtype) || is_fp8(in_dtype), "%s: input dtype %d unsupported", who, in_dtype);
+  FLUXB_REQUIRE(m >= 1 && n >= 1 && k >= 1, "%s: empty problem m=%d n=%d k=%d", who, m, n, k);
+  FLUXB_REQUIRE((static_cast<long long>(k) * eb) % 16 == 0,
+                "%s: k=%d gives a row pitch of %lld bytes; it must be a multiple of 16", who, k,
+                static_cast<long long>(k) * eb);
+  FLUXB_REQUIRE(n % 8 == 0, "%s: n=%d must be a multiple of 8", who, n);
+  (void)out_dtype;
+  return FLUXB_OK;
+}
+
+static void zero_params(GemmParams& p) { memset(&p, 0, sizeof(p)); }
+
+// ---------------------------------------------------------------------------
+// owner-side reduction of GEMM-RS: out = sum over source ranks of the fp32
+// partial tiles, once every source has published the tile (4 arrivals per
+// source: one per epilogue warp). Counters are cleared after use.
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+rs_reduce_kernel(const float* __restrict__ stage, int* cnt, void* out, int out_type, int mpr, int n,
+                 int bn, int world, int* status, unsigned long long budget_ns) {
+  __shared__ int s_ok;
+  const int n_tiles = (n + bn - 1) / bn;
+  const int m_chunks = (mpr + kBM - 1) / kBM;
+  const int total = m_chunks * n_tiles;
+  const int vec_per_row = bn / 4;
+  const long long slot = static_cast<long long>(mpr) * n;
+  for (int t = blockIdx.x; t < total; t += gridDim.x) {
+    // same visiting order as the producers: chunk fastest inside a column block
+    const int c = t % m_chunks;
+    const int nt = t / m_chunks;
+    if (threadIdx.x == 0)
+      s_ok = flag_wait_eq(cnt + c * n_tiles + nt, 4 * world, nullptr, kStatusTimeoutReduce, budget_ns) ? 1 : 0;
+    __syncthreads();
+    if (!s_ok) {
+      if (threadIdx.x == 0) {
+        *reinterpret_cast<volatile int*>(status) = kStatusTimeoutReduce;
+        __threadfence_system();
+      }
+      return;
+    }
+    const int rows = imin(kBM, mpr - c * kBM);
+    const int n0 = nt * bn;
+    for (int i = threadIdx.x; i < rows * vec_per_row; i += blockDim.x) {
+      const int r = i / vec_per_row;
+      const int c4 = (i - r * vec_per_row) * 4;
+      const int col = n0 + c4;
+      if (col >= n) continue;
+      const long long off = static_cast<long long>(c * kBM + r) * n + col;
+      float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < world; ++s) {
+        const float4 v = *reinterpret_cast<const float4*>(stage + s * slot + off);
+        acc.x += v.x;
+        acc.y += v.y;
+        acc.z += v.z;
+        acc.w += v.w;
+      }
+      if (out_type == kOutF32) {
+        *reinterpret_cast<float4*>(static_cast<float*>(out) + off) = acc;
+      } else {
+        uint2 w;
+        if (out_type == kOutBf16) {
+          w.x = pack_bf16(acc.x, acc.y);
+          w.y = pack_bf16(acc.z, acc.w);
+        } else {
+          w.x = pack_f16(acc.x, acc.y);
+          w.y = pack_f16(acc.z, acc.w);
+        }
+        *reinterpret_cast<uint2*>(static_cast<uint16_t*>(out) + off) = w;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) cnt[c * n_tiles + nt] = 0;
+  }
+}
+
+}  // namespace fluxb
+
+using namespace fluxb;
+
+struct fluxb_ag_gemm {
+  fluxb_comm* comm;
+  int full_m, n_dim, k_dim, in_dtype, out_dtype;
+  int flag_stride;
+  uint8_t* gather[kMaxWorld];
+  int* flags[kMaxWorld];
+  float* scales[kMaxWorld];
+  bool has_scales;
+  unsigned long long calls;
+};
+
+struct fluxb_gemm_rs {
+  fluxb_comm* comm;
+  int max_m, n_dim, in_dtype, out_dtype;
+  float* stage[kMaxWorld];
+  int* cnt[kMaxWorld];
+  long long cnt_cap;
+  unsigned long long calls;
+};
+
+static int ag_flag_stride(int full_m, int world) {
+  const int per_rank = (full_m + world - 1) / world;
+  return (per_rank + kBM - 1) / kBM;
+}
+
+extern "C" {
+
+int fluxb_gemm(fluxb_comm_t comm, const void* a, const void* b, void* c, int m, int n, int k,
+               int in_dtype, int out_dtype, const void* bias, int bias_mode, const float* scale_a,
+               const float* scale_b, float alpha, const fluxb_tuning* tuning, fluxb_stream_t stream) {
+  FLUXB_REQUIRE(comm != nullptr && a != nullptr && b != nullptr && c != nullptr, "gemm: NULL argument");
+  int rc = check_gemm_shapes("gemm", m, n, k, in_dtype, out_dtype);
+  if (rc != FLUXB_OK) return rc;
+  FLUXB_REQUIRE(bias_mode == FLUXB_BIAS_NONE || bias != nullptr, "gemm: bias_mode set but bias is NULL");
+  GemmParams p;
+  zero_params(p);
+  const int eb = dtype_bytes(in_dtype);
+  rc = out_type_of(out_dtype, &p.out_type);
+  if (rc != FLUXB_OK) return rc;
+  p.M = m;
+  p.N = n;
+  p.K = k;
+  p.nseg = 1;
+  p.seg_rows = m;
+  p.seg_first = 0;
+  p.epi_mode = kEpiStore;
+  p.bias_mode = bias_mode;
+  p.out = c;
+  p.ldo = n;
+  p.bias = bias;
+  p.ldbias = n;
+  p.scale_a = scale_a;
+  p.scale_b = scale_b;
+  p.alpha = alpha;
+  const int bn = resolve_block_n(comm, p, tuning, 0);
+  rc = encode_tmap_2d(&p.tmap_a, a, in_dtype, m, k, static_cast<long long>(k) * eb, kBM);
+  if (rc != FLUXB_OK) return rc;
+  rc = encode_tmap_2d(&p.tmap_b, b, in_dtype, n, k, static_cast<long long>(k) * eb, bn);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  t.block_n = bn;
+  return launch_fused_gemm(comm, p, in_dtype, &t, static_cast<cudaStream_t>(stream));
+}
+
+// ------------------------------------------------------------------ AG-GEMM
+size_t fluxb_ag_gemm_gather_bytes(int full_m, int k_dim, int in_dtype) {
+  // two parities; one extra tile of rows so that a 128-row box never leaves the allocation
+  return 2ull * (static_cast<size_t>(full_m) + kBM) * k_dim * dtype_bytes(in_dtype);
+}
+size_t fluxb_ag_gemm_flag_bytes(int full_m, int world) {
+  return 2ull * world * ag_flag_stride(full_m, world) * sizeof(int);
+}
+size_t fluxb_ag_gemm_scale_bytes(int full_m) { return 2ull * full_m * sizeof(float); }
+
+int fluxb_ag_gemm_create(fluxb_comm_t comm, int full_m, int n_dim, int k_dim, int in_dtype,
+                         int out_dtype, void* const* gather_bufs, int* const* flag_bufs,
+                         float* const* scale_bufs, fluxb_ag_gemm_t* out) {
+  FLUXB_REQUIRE(comm != nullptr && out != nullptr, "ag_gemm_create: NULL argument");
+  FLUXB_REQUIRE(gather_bufs != nullptr && flag_bufs != nullptr, "ag_gemm_create: NULL buffer table");
+  FLUXB_REQUIRE(full_m >= comm->world, "ag_gemm_create: full_m=%d < world=%d", full_m, comm->world);
+  int rc = check_gemm_shapes("ag_gemm_create", full_m, n_dim, k_dim, in_dtype, out_dtype);
+  if (rc != FLUXB_OK) return rc;
+  int ot;
+  rc = out_type_of(out_dtype, &ot);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_ag_gemm* op = new fluxb_ag_gemm();
+  memset(op, 0, sizeof(*op));
+  op->comm = comm;
+  op->full_m = full_m;
+  op->n_dim = n_dim;
+  op->k_dim = k_dim;
+  op->in_dtype = in_dtype;
+  op->out_dtype = out_dtype;
+  op->flag_stride = ag_flag_stride(full_m, comm->world);
+  op->has_scales = scale_bufs != nullptr;
+  for (int r = 0; r < comm->world; ++r) {
+    if (gather_bufs[r] == nullptr || flag_bufs[r] == nullptr ||
+        (scale_bufs != nullptr && scale_bufs[r] == nullptr)) {
+      delete op;
+      FLUXB_FAIL(FLUXB_ERR_INVALID, "ag_gemm_create: buffer of rank %d is NULL", r);
+    }
+    op->gather[r] = static_cast<uint8_t*>(gather_bufs[r]);
+    op->flags[r] = flag_bufs[r];
+    op->scales[r] = scale_bufs != nullptr ? scale_bufs[r] : nullptr;
+  }
+  *out = op;
+  return FLUXB_OK;
+}
+
+int fluxb_ag_gemm_destroy(fluxb_ag_gemm_t op) {
+  delete op;
+  return FLUXB_OK;
+}
+
+int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, const void* b,
+                          int n, int k, void* c, const void* bias, int bias_mode,
+                          const float* scale_a_shard, const float* scale_b, float alpha,
+                          void* gathered_out, const fluxb_tuning* tuning, fluxb_stream_t stream_) {
+  FLUXB_REQUIRE(op != nullptr && a_shard != nullptr && b != nullptr && c != nullptr,
+                "ag_gemm_forward: NULL argument");
+  fluxb_comm* comm = op->comm;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int world = comm->world;
+  const long long m = static_cast<long long>(m_local) * world;
+  FLUXB_REQUIRE(m_local >= 1 && m <= op->full_m, "ag_gemm_forward: m_local=%d * world=%d exceeds full_m=%d",
+                m_local, world, op->full_m);
+  FLUXB_REQUIRE(k == op->k_dim, "ag_gemm_forward: k=%d differs from k_dim=%d", k, op->k_dim);
+  FLUXB_REQUIRE(n >= 1 && n <= op->n_dim, "ag_gemm_forward: n=%d exceeds n_dim=%d", n, op->n_dim);
+  int rc = check_gemm_shapes("ag_gemm_forward", static_cast<int>(m), n, k, op->in_dtype, op->out_dtype);
+  if (rc != FLUXB_OK) return rc;
+  FLUXB_REQUIRE(bias_mode == FLUXB_BIAS_NONE || bias != nullptr, "ag_gemm_forward: bias is NULL");
+  FLUXB_REQUIRE(scale_a_shard == nullptr || op->has_scales,
+                "ag_gemm_forward: per-row input scales need scale buffers at create time");
+  const int eb = dtype_bytes(op->in_dtype);
+  const long long row_bytes = static_cast<long long>(k) * eb;
+
+  if (world == 1) {
+    rc = fluxb_gemm(comm, a_shard, b, c, m_local, n, k, op->in_dtype, op->out_dtype, bias, bias_mode,
+                    scale_a_shard, scale_b, alpha, tuning, stream_);
+    if (rc != FLUXB_OK) return rc;
+    if (gathered_out != nullptr)
+      FLUXB_CUDA(cudaMemcpyAsync(gathered_out, a_shard, m_local * row_bytes, cudaMemcpyDeviceToDevice, stream));
+    return FLUXB_OK;
+  }
+
+  const int parity = static_cast<int>(op->calls & 1ull);
+  const size_t half_gather = (static_cast<size_t>(op->full_m) + kBM) * op->k_dim * eb;
+  const size_t half_flags = static_cast<size_t>(world) * op->flag_stride;
+  // The other parity's counters were consumed by the previous call and are next written by
+  // peers only after they have seen this call's pushes: clear them now.
+  FLUXB_CUDA(cudaMemsetAsync(op->flags[comm->rank] + (parity ^ 1) * half_flags, 0,
+                             half_flags * sizeof(int), stream));
+
+  GemmParams p;
+  zero_params(p);
+  rc = out_type_of(op->out_dtype, &p.out_type);
+  if (rc != FLUXB_OK) return rc;
+  p.M = static_cast<int>(m);
+  p.N = n;
+  p.K = k;
+  p.nseg = world;
+  p.seg_rows = m_local;
+  p.seg_first = comm->rank;
+  p.epi_mode = kEpiStore;
+  p.bias_mode = bias_mode;
+  p.out = c;
+  p.ldo = n;
+  p.bias = bias;
+  p.ldbias = n;
+  p.scale_b = scale_b;
+  p.alpha = alpha;
+  p.ag_flags = op->flags[comm->rank] + parity * half_flags;
+  p.ag_flag_stride = op->flag_stride;
+  p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+  p.ag_src = static_cast<const uint8_t*>(a_shard);
+  p.ag_row_bytes = row_bytes;
+  p.ag_src_scale = scale_a_shard;
+  for (int r = 0; r < world; ++r) {
+    p.ag_dst[r] = op->gather[r] + parity * half_gather;
+    p.ag_dst_flags[r] = op->flags[r] + parity * half_flags;
+    p.ag_dst_scale[r] = op->has_scales ? op->scales[r] + parity * op->full_m : nullptr;
+  }
+  if (scale_a_shard != nullptr) p.scale_a = op->scales[comm->rank] + parity * op->full_m;
+  const int tps = (m_local + kBM - 1) / kBM;
+  if (tuning == nullptr || tuning->group_m <= 0) p.group_m = tps > 8 ? tps : 8;
+  const int bn = resolve_block_n(comm, p, tuning, 0);
+  uint8_t* local_gather = op->gather[comm->rank] + parity * half_gather;
+  rc = encode_tmap_2d(&p.tmap_a, local_gather, op->in_dtype, m, k, row_bytes, kBM);
+  if (rc != FLUXB_OK) return rc;
+  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k, row_bytes, bn);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  t.block_n = bn;
+  rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
+  if (rc != FLUXB_OK) return rc;
+  op->calls += 1;
+  if (gathered_out != nullptr)
+    FLUXB_CUDA(cudaMemcpyAsync(gathered_out, local_gather, m * row_bytes, cudaMemcpyDeviceToDevice, stream));
+  return FLUXB_OK;
+}
+
+// ------------------------------------------------------------------ GEMM-RS
+static long long rs_cnt_cap(int max_m, int n_dim, int world) {
+  const int mpr = (max_m + world - 1) / world;
+  return static_cast<long long>((mpr + kBM - 1) / kBM) * ((n_dim + 63) / 64);
+}
+size_t fluxb_gemm_rs_stage_bytes(int max_m, int n_dim, int world) {
+  (void)world;
+  return 2ull * static_cast<size_t>(max_m) * n_dim * sizeof(float);
+}
+size_t fluxb_gemm_rs_cnt_bytes(int max_m, int n_dim, int world) {
+  return 2ull * rs_cnt_cap(max_m, n_dim, world) * sizeof(int);
+}
+
+int fluxb_gemm_rs_create(fluxb_comm_t comm, int max_m, int n_dim, int in_dtype, int out_dtype,
+                         float* const* stage_bufs, int* const* cnt_bufs, fluxb_gemm_rs_t* out) {
+  FLUXB_REQUIRE(comm != nullptr && out != nullptr, "gemm_rs_create: NULL argument");
+  FLUXB_REQUIRE(stage_bufs != nullptr && cnt_bufs != nullptr, "gemm_rs_create: NULL buffer table");
+  FLUXB_REQUIRE(max_m >= comm->world && n_dim >= 8 && n_dim % 8 == 0,
+                "gemm_rs_create: max_m=%d n_dim=%d invalid (n_dim must be a multiple of 8)", max_m, n_dim);
+  FLUXB_REQUIRE(is_16bit(in_dtype) || is_fp8(in_dtype), "gemm_rs_create: input dtype %d unsupported", in_dtype);
+  int ot;
+  int rc = out_type_of(out_dtype, &ot);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_gemm_rs* op = new fluxb_gemm_rs();
+  memset(op, 0, sizeof(*op));
+  op->comm = comm;
+  op->max_m = max_m;
+  op->n_dim = n_dim;
+  op->in_dtype = in_dtype;
+  op->out_dtype = out_dtype;
+  op->cnt_cap = rs_cnt_cap(max_m, n_dim, comm->world);
+  for (int r = 0; r < comm->world; ++r) {
+    if (stage_bufs[r] == nullptr || cnt_bufs[r] == nullptr) {
+      delete op;
+      FLUXB_FAIL(FLUXB_ERR_INVALID, "gemm_rs_create: buffer of rank %d is NULL", r);
+    }
+    op->stage[r] = stage_bufs[r];
+    op->cnt[r] = cnt_bufs[r];
+  }
+  *out = op;
+  return FLUXB_OK;
+}
+
+int fluxb_gemm_rs_destroy(fluxb_gemm_rs_t op) {
+  delete op;
+  return FLUXB_OK;
+}
+
+int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int m, int n,
+                          int k_local, void* out, const void* bias, int bias_mode,
+                          const float* scale_a, const float* scale_b, float alpha,
+                          const fluxb_tuning* tuning, fluxb_stream_t stream_) {
+  FLUXB_REQUIRE(op != nullptr && a != nullptr && b != nullptr && out != nullptr,
+                "gemm_rs_forward: NULL argument");
+  fluxb_comm* comm = op->comm;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int world = comm->world;
+  FLUXB_REQUIRE(m >= world && m <= op->max_m, "gemm_rs_forward: m=%d out of [%d, max_m=%d]", m, world, op->max_m);
+  FLUXB_REQUIRE(m % world == 0, "gemm_rs_forward: m=%d is not a multiple of world=%d", m, world);
+  FLUXB_REQUIRE(n == op->n_dim, "gemm_rs_forward: n=%d differs from n_dim=%d", n, op->n_dim);
+  int rc = check_gemm_shapes("gemm_rs_forward", m, n, k_local, op->in_dtype, op->out_dtype);
+  if (rc != FLUXB_OK) return rc;
+  FLUXB_REQUIRE(bias_mode == FLUXB_BIAS_NONE || bias != nullptr, "gemm_rs_forward: bias is NULL");
+  FLUXB_REQUIRE(bias_mode != FLUXB_BIAS_1N, "gemm_rs_forward: only [M,N] bias is supported");
+  if (world == 1)
+    return fluxb_gemm(comm, a, b, out, m, n, k_local, op->in_dtype, op->out_dtype, bias, bias_mode,
+                      scale_a, scale_b, alpha, tuning, stream_);
+  FLUXB_REQUIRE(bias_mode == FLUXB_BIAS_NONE || op->out_dtype == FLUXB_BF16,
+                "gemm_rs_forward: bias needs a bf16 output");
+
+  const int eb = dtype_bytes(op->in_dtype);
+  const int mpr = m / world;
+  const int parity = static_cast<int>(op->calls & 1ull);
+  GemmParams p;
+  zero_params(p);
+  int ot;
+  rc = out_type_of(op->out_dtype, &ot);
+  if (rc != FLUXB_OK) return rc;
+  p.M = m;
+  p.N = n;
+  p.K = k_local;
+  p.nseg = world;
+  p.seg_rows = mpr;
+  p.seg_first = (comm->rank + 1) % world;  // rows owned by peers first, own rows last
+  p.epi_mode = kEpiRsPush;
+  p.out_type = kOutF32;
+  p.bias_mode = bias_mode;
+  p.bias = bias;
+  p.ldbias = n;
+  p.scale_a = scale_a;
+  p.scale_b = scale_b;
+  p.alpha = alpha;
+  const size_t half_stage = static_cast<size_t>(op->max_m) * op->n_dim;
+  for (int r = 0; r < world; ++r) {
+    p.rs_stage[r] = op->stage[r] + parity * half_stage + static_cast<size_t>(comm->rank) * mpr * n;
+    p.rs_cnt[r] = op->cnt[r] + parity * op->cnt_cap;
+  }
+  const int tps = (mpr + kBM - 1) / kBM;
+  if (tuning == nullptr || tuning->group_m <= 0) p.group_m = tps > 8 ? tps : 8;
+  const int bn = resolve_block_n(comm, p, tuning, 0);
+  const long long row_bytes = static_cast<long long>(k_local) * eb;
+  rc = encode_tmap_2d(&p.tmap_a, a, op->in_dtype, m, k_local, row_bytes, kBM);
+  if (rc != FLUXB_OK) return rc;
+  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k_local, row_bytes, bn);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  t.block_n = bn;
+  rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
+  if (rc != FLUXB_OK) return rc;
+
+  const int n_tiles = (n + bn - 1) / bn;
+  int rgrid = tps * n_tiles;
+  if (rgrid > 2 * comm->sm_count) rgrid = 2 * comm->sm_count;
+  rs_reduce_kernel<<<rgrid, 256, 0, stream>>>(op->stage[comm->rank] + parity * half_stage,
+                                             op->cnt[comm->rank] + parity * op->cnt_cap, out, ot, mpr,
+                                             n, bn, world, comm->status_dev, comm->timeout_ns);
+  FLUXB_CUDA(cudaGetLastError());
+  op->calls += 1;
+  return FLUXB_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,78 @@
+// Host-side internals shared by the .cu files of the library: error
+// reporting, the communicator object, tensor-map encoding, launch helpers.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdio.h>
+
+#include <string>
+
+#include "../../include/fluxb.h"
+#include "gemm_kernel.cuh"
+
+namespace fluxb {
+
+void set_error(const char* fmt, ...);
+
+#define FLUXB_FAIL(code, ...)          \
+  do {                                 \
+    ::fluxb::set_error(__VA_ARGS__);   \
+    return (code);                     \
+  } while (0)
+
+#define FLUXB_REQUIRE(cond, ...)                        \
+  do {                                                  \
+    if (!(cond)) FLUXB_FAIL(FLUXB_ERR_INVALID, __VA_ARGS__); \
+  } while (0)
+
+#define FLUXB_CUDA(expr)                                                              \
+  do {                                                                                \
+    cudaError_t e_ = (expr);                                                          \
+    if (e_ != cudaSuccess)                                                            \
+      FLUXB_FAIL(FLUXB_ERR_CUDA, "%s failed: %s (%s:%d)", #expr, cudaGetErrorString(e_), \
+                 __FILE__, __LINE__);                                                 \
+  } while (0)
+
+inline int dtype_bytes(int dt) {
+  switch (dt) {
+    case FLUXB_BF16:
+    case FLUXB_F16:
+      return 2;
+    case FLUXB_F32:
+      return 4;
+    case FLUXB_E4M3:
+    case FLUXB_E5M2:
+      return 1;
+    default:
+      return 0;
+  }
+}
+inline bool is_fp8(int dt) { return dt == FLUXB_E4M3 || dt == FLUXB_E5M2; }
+inline bool is_16bit(int dt) { return dt == FLUXB_BF16 || dt == FLUXB_F16; }
+
+}  // namespace fluxb
+
+struct fluxb_comm {
+  int rank = 0;
+  int world = 1;
+  int device = 0;
+  int sm_count = 0;
+  int* status_host = nullptr;  // pinned + mapped; kernels write, host reads
+  int* status_dev = nullptr;   // device alias of status_host
+  unsigned long long timeout_ns = 10ull * 1000 * 1000 * 1000;
+  int barrier_epoch = 0;
+};
+
+namespace fluxb {
+
+// 2-D tensor map over a row-major [rows, k] matrix whose rows are `ld_bytes`
+// apart; box = 128 bytes of K x `box_rows` rows, 128-byte swizzle.
+int encode_tmap_2d(CUtensorMap* out, const void* base, int elt_dtype, long long rows, long long k,
+                   long long ld_bytes, int box_rows);
+
+// Fill the problem-independent fields and launch the fused kernel.
+int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
+                      const fluxb_tuning* tuning, cudaStream_t stream);
+
+}  // namespace fluxb

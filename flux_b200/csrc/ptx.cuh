@@ -1,0 +1,273 @@
+// Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the fused
+// kernels use: mbarrier, TMA (cp.async.bulk.tensor, never with cluster
+// multicast), tcgen05 (TMEM alloc, UMMA, commit, ld) and the system-scope
+// flag operations that order peer-GPU traffic.
+//
+// Every wait in this file is bounded: it polls, checks a CTA-wide abort word
+// and a wall-clock budget, and returns false instead of spinning forever.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fluxb {
+
+// ----------------------------------------------------------------------------
+// status codes written by kernels into the status word (0 = ok)
+// ----------------------------------------------------------------------------
+enum : int {
+  kStatusOk = 0,
+  kStatusTimeoutSmemFull = 1,   // MMA warp: operand stage never became full
+  kStatusTimeoutSmemEmpty = 2,  // TMA warp: operand stage never drained
+  kStatusTimeoutTmemFull = 3,   // epilogue: accumulator never completed
+  kStatusTimeoutTmemEmpty = 4,  // MMA warp: accumulator never drained
+  kStatusTimeoutFlag = 5,       // a peer's arrival flag never reached its value
+  kStatusTimeoutBarrier = 6,    // all-rank barrier kernel gave up
+  kStatusTimeoutReduce = 7,     // reduce-scatter tail: partial tiles missing
+  kStatusBadTable = 8,          // grouped GEMM: tile table is inconsistent
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+
+__device__ __forceinline__ uint64_t globaltimer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred = 0;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "elect.sync _|P, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
+// ----------------------------------------------------------------------------
+// mbarrier
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_init_fence() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
+               : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred P;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 P, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, P;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded mbarrier wait. `s_abort` is a CTA-shared word: non-zero means some
+// role has given up, and every other role must leave its loop too.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort,
+                                          int code, uint64_t budget_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t n = 0;
+  while (!mbar_try_wait(bar, parity)) {
+    if ((++n & 31u) == 0u) {
+      if (*s_abort != 0) return false;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        atomicCAS(const_cast<int*>(s_abort), 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ----------------------------------------------------------------------------
+// proxy / scope fences
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void fence_proxy_async() {
+  asm volatile("fence.proxy.async;" ::: "memory");
+}
+__device__ __forceinline__ void fence_acq_rel_sys() {
+  asm volatile("fence.acq_rel.sys;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------
+// system-scope flags (live in symmetric memory, written by peers)
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ int ld_acquire_sys(const int* p) {
+  int v;
+  asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ int ld_relaxed_sys(const int* p) {
+  int v;
+  asm volatile("ld.relaxed.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(int* p, int v) {
+  asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void red_add_release_sys(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+
+// Bounded wait until *flag == want (acquire, system scope).
+__device__ __forceinline__ bool flag_wait_eq(const int* flag, int want, volatile int* s_abort,
+                                             int code, uint64_t budget_ns) {
+  if (ld_acquire_sys(flag) == want) return true;
+  const uint64_t t0 = globaltimer_ns();
+  uint32_t n = 0;
+  while (ld_acquire_sys(flag) != want) {
+    __nanosleep(64);
+    if ((++n & 15u) == 0u) {
+      if (s_abort != nullptr && *s_abort != 0) return false;
+      if (globaltimer_ns() - t0 > budget_ns) {
+        if (s_abort != nullptr) atomicCAS(const_cast<int*>(s_abort), 0, code);
+        return false;
+      }
+    }
+  }
+  return true;
+}
+
+// ----------------------------------------------------------------------------
+// TMA (tiled tensor copies global -> shared). No multicast anywhere.
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
+}
+// x = innermost (element) coordinate, y = row coordinate.
+__device__ __forceinline__ void tma_load_2d(uint32_t smem_dst, const void* tmap, uint32_t bar,
+                                            int x, int y) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4}], [%2];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
+      : "memory");
+}
+// Four independent rows (y0..y3) of one 2-D tensor, `box_x` elements each,
+// land as four consecutive smem rows.
+__device__ __forceinline__ void tma_gather4_2d(uint32_t smem_dst, const void* tmap, uint32_t bar,
+                                               int x, int y0, int y1, int y2, int y3) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile::gather4.mbarrier::complete_tx::bytes"
+      " [%0], [%1, {%3, %4, %5, %6, %7}], [%2];"
+      :
+      : "r"(smem_dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y0), "r"(y1),
+        "r"(y2), "r"(y3)
+      : "memory");
+}
+
+// ----------------------------------------------------------------------------
+// tcgen05: tensor memory + UMMA
+// ----------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_dst),
+               "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+               : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() {
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+}
+__device__ __forceinline__ void tc_fence_after() {
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+}
+// arrives (count 1) on `bar` once every tcgen05.mma issued so far by this thread has retired
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                   bar)
+               : "memory");
+}
+// D[tmem] (+)= A[smem] * B[smem]^T, 16-bit inputs (f16/bf16), fp32 accumulate
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                         uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// same for 8-bit float inputs (e4m3/e5m2)
+__device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
+// 32 lanes x 32 consecutive fp32 columns: thread `lane` receives row
+// (taddr.lane + lane), columns taddr.col .. +31.
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() {
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ----------------------------------------------------------------------------
+// descriptors
+// ----------------------------------------------------------------------------
+// Shared-memory operand descriptor for a K-major tile whose rows are exactly
+// one 128-byte swizzle span (64 bf16 or 128 fp8): rows are 128 B apart,
+// groups of 8 rows are 1024 B apart (stride byte offset), the tile base is
+// 1024-byte aligned, and TMA wrote it with CU_TENSOR_MAP_SWIZZLE_128B.
+//   bits [0,14)  start address >> 4      bits [16,30) leading byte offset >> 4
+//   bits [32,46) stride byte offset >> 4 bits [46,48) descriptor version (1)
+//   bits [61,64) swizzle mode (2 = 128 B)
+__device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>(1) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
+// Instruction descriptor (dense, fp32 accumulate, both operands K-major).
+//   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format
+//   [15] A major (0 = K)       [16] B major (0 = K)
+//   [17,23) N >> 3             [24,29) M >> 4
+// A/B format: kind::f16 -> 0 = f16, 1 = bf16; kind::f8f6f4 -> 0 = e4m3, 1 = e5m2
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t m, uint32_t n) {
+  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
+}  // namespace fluxb
