@@ -1,0 +1,391 @@
+"""Torch-facing ops with the reference's names, arguments and error behaviour.
+
+Mirrors the pybind classes of the reference:
+  AGKernel  - src/pybind/ag_gemm.cc:31-103  (AllGatherGemmOp, src/ag_gemm/ths_op/all_gather_gemm_op.cc)
+  GemmRS    - src/pybind/gemm_rs.cc:30-102  (GemmRS, src/gemm_rs/ths_op/gemm_reduce_scatter.cc)
+  option / env carriers - src/pybind/ths_op.cc:94-179
+Each forward is one call into the C ABI (`include/fluxb.h`) on the current
+CUDA stream; tensors are only used for their device pointers and shapes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+import enum
+from typing import List, Optional
+
+import torch
+
+from . import _lib
+from .shm import Comm, SymmBuffer, fluxb_dtype, get_comm
+
+
+def _check(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def is_fp8_dtype(dt: torch.dtype) -> bool:
+    return dt in (getattr(torch, "float8_e4m3fn", None), getattr(torch, "float8_e5m2", None))
+
+
+def _cur_stream() -> C.c_void_p:
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _tuning(t) -> Optional[C.Array]:
+    if t is None:
+        return None
+    if isinstance(t, _lib.Tuning):
+        return C.byref(t)
+    return C.byref(_lib.Tuning(int(t.get("block_n", 0)), int(t.get("group_m", 0)), int(t.get("num_ctas", 0)), 0))
+
+
+class AGRingMode(enum.IntEnum):
+    """src/coll/ths_op/all_gather_types.h:26-30"""
+
+    All2All = 0
+    Ring1D = 1
+    Ring2D = 2
+
+
+class RingMode(enum.IntEnum):
+    """src/coll/ths_op/reduce_scatter_op.h:26-30"""
+
+    All2All = 0
+    Ring1D = 1
+    Ring2D = 2
+
+
+class AllGatherOption:
+    """All fields optional (src/coll/ths_op/all_gather_types.h:35-43). On an NVSwitch domain the
+    transfer is always an all-to-all push from the fused kernel; the PCIe-oriented knobs are
+    accepted and ignored."""
+
+    def __init__(self):
+        self.input_buffer_copied = None
+        self.use_cuda_core_local = None
+        self.use_cuda_core_ag = None
+        self.fuse_sync = None
+        self.use_read = None
+        self.mode = None
+
+    def __repr__(self):
+        return (
+            f"AllGatherOption(mode={self.mode}, fuse_sync={self.fuse_sync}, "
+            f"use_cuda_core_local={self.use_cuda_core_local}, use_cuda_core_ag={self.use_cuda_core_ag}, "
+            f"input_buffer_copied={self.input_buffer_copied}, use_read={self.use_read})"
+        )
+
+
+class ReduceScatterOption:
+    """All fields optional (src/coll/ths_op/reduce_scatter_op.h:35-46); PCIe-oriented, ignored by
+    the NVLink push epilogue, as they are by the reference's sm90 NVLink kernel."""
+
+    def __init__(self):
+        self.use_barrier_queue = None
+        self.use_1d_ring = None
+        self.use_p2p_read = None
+        self.use_cudaMemcpyAsync = None
+        self.use_gemmk = None
+        self.per_tile_flags = None
+        self.n_split = None
+        self.num_blocks = None
+        self.ring_mode = None
+
+
+class DistEnvTP:
+    """src/pybind/ths_op.cc:94-118 / include/flux/ths_op/ths_op.h:53-75"""
+
+    def __init__(self, tp_group, nnodes: int = 1):
+        comm = get_comm(tp_group)
+        self.tp_group = tp_group
+        self.nnodes = int(nnodes)
+        self.rank = comm.rank
+        self.world_size = comm.world
+        _check(self.nnodes == 1, "only nnodes == 1 (one NVSwitch domain) is supported")
+        self.local_world_size = self.world_size // self.nnodes
+        self.local_rank = self.rank % self.local_world_size
+
+
+class DistEnvTPWithEP(DistEnvTP):
+    """src/ths_op/ths_op.cc:334-346"""
+
+    def __init__(self, tp_group, nnodes: int = 1, ep_group=None):
+        super().__init__(tp_group, nnodes)
+        self.ep_group = ep_group
+        if ep_group is None:
+            self.ep_rank, self.ep_size = 0, 1
+        else:
+            import torch.distributed as dist
+
+            self.ep_rank, self.ep_size = dist.get_rank(ep_group), dist.get_world_size(ep_group)
+        self.ffn_tp_size = self.world_size // self.ep_size
+        self.ffn_tp_rank = self.rank % self.ffn_tp_size
+
+
+class MoeArguments:
+    """src/ths_op/ths_op.cc:348-375"""
+
+    def __init__(self, max_ntokens, hidden, ffn_hidden, nexperts, topk, input_dtype, output_dtype=None):
+        self.max_ntokens = int(max_ntokens)
+        self.hidden = int(hidden)
+        self.ffn_hidden = int(ffn_hidden)
+        self.nexperts = int(nexperts)
+        self.topk = int(topk)
+        self.input_dtype = input_dtype
+        self.output_dtype = output_dtype if output_dtype is not None else input_dtype
+
+
+class ProfilingContext:
+    """API-compatible carrier (src/ths_op/ths_op.cc:217-318); tile choice is a run-time table here."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.records: List[str] = []
+
+    def get_code(self) -> str:
+        return "\n".join(self.records)
+
+    def get_all_record_codes(self) -> List[str]:
+        return list(self.records)
+
+    def get_latest_record(self):
+        return self.records[-1] if self.records else None
+
+
+def _out_dtype(input_dtype: torch.dtype, output_dtype: Optional[torch.dtype]) -> torch.dtype:
+    # fp8 / int8 inputs produce bf16 (src/ag_gemm/ths_op/gemm_with_barrier.cc:184-185)
+    if output_dtype is not None:
+        return output_dtype
+    return torch.bfloat16 if is_fp8_dtype(input_dtype) else input_dtype
+
+
+def _expand_scale(s: Optional[torch.Tensor], n: int, what: str) -> Optional[torch.Tensor]:
+    """Scalar [1] scales (the reference's fp8 form) become a vector without a host sync; vectors
+    [n], [n,1] or [1,n] (the reference's int8 form) are used as they are."""
+    if s is None:
+        return None
+    _check(s.dtype == torch.float32, f"{what} must be float32")
+    if s.numel() == 1:
+        return s.reshape(1).expand(n).contiguous()
+    _check(s.numel() == n, f"{what} has {s.numel()} elements, expected 1 or {n}")
+    return s.reshape(n).contiguous()
+
+
+class AGKernel:
+    """`flux.AGKernel(tp_group, nnodes, full_m, n_dim, k_dim, input_dtype, output_dtype=None,
+    use_pdl=False)` - all-gather fused into the GEMM (src/pybind/ag_gemm.cc:31-62)."""
+
+    def __init__(self, tp_group, nnodes, full_m, n_dim, k_dim, input_dtype, output_dtype=None, use_pdl=False):
+        _check(int(nnodes) == 1, "AGKernel: only nnodes == 1 is supported")
+        self.comm: Comm = get_comm(tp_group)
+        self.full_m, self.n_dim, self.k_dim = int(full_m), int(n_dim), int(k_dim)
+        self.input_dtype = input_dtype
+        self.output_dtype = _out_dtype(input_dtype, output_dtype)
+        lib = _lib.load()
+        in_dt, out_dt = fluxb_dtype(input_dtype), fluxb_dtype(self.output_dtype)
+        w = self.comm.world
+        self._gather = SymmBuffer(self.comm, lib.fluxb_ag_gemm_gather_bytes(self.full_m, self.k_dim, in_dt))
+        self._flags = SymmBuffer(self.comm, lib.fluxb_ag_gemm_flag_bytes(self.full_m, w))
+        self._scales = SymmBuffer(self.comm, lib.fluxb_ag_gemm_scale_bytes(self.full_m))
+        h = C.c_void_p()
+        _lib.check(
+            lib.fluxb_ag_gemm_create(
+                self.comm.handle, self.full_m, self.n_dim, self.k_dim, in_dt, out_dt,
+                self._gather.table(), self._flags.table(), self._scales.table(), C.byref(h),
+            )
+        )
+        self._h = h
+        self.comm.host_barrier()  # every rank's buffers are zeroed and mapped before the first push
+
+    def __del__(self):
+        try:
+            _lib.load().fluxb_ag_gemm_destroy(self._h)
+        except Exception:
+            pass
+
+    def _prep(self, input, weight, bias, output, input_scale, weight_scale, output_scale, transpose_weight, world):
+        _check(input.is_cuda and weight.is_cuda, "AGKernel: tensors must be CUDA tensors")
+        _check(input.dim() == 2 and weight.dim() == 2, "AGKernel: input and weight must be 2-D")
+        _check(input.dtype == self.input_dtype and weight.dtype == self.input_dtype, "AGKernel: dtype mismatch")
+        _check(output_scale is None, "AGKernel: output_scale is not supported")
+        if transpose_weight:
+            # fp8 forbids transpose_weight (src/ag_gemm/ths_op/gemm_with_barrier.cc:188)
+            _check(not is_fp8_dtype(self.input_dtype), "AGKernel: fp8 does not support transpose_weight")
+            weight = weight.t()
+        _check(input.is_contiguous(), "AGKernel: input must be contiguous")
+        if not weight.is_contiguous():
+            weight = weight.contiguous()
+        m_local, k = input.shape
+        n = weight.shape[0]
+        _check(weight.shape[1] == k, f"AGKernel: weight K {weight.shape[1]} != input K {k}")
+        _check(k == self.k_dim, f"AGKernel: k={k} differs from k_dim={self.k_dim}")
+        m = m_local * world
+        _check(m <= self.full_m, f"AGKernel: M={m} exceeds full_m={self.full_m}")
+        if output is None:
+            output = torch.empty((m, n), dtype=self.output_dtype, device=input.device)
+        else:
+            _check(tuple(output.shape) == (m, n) and output.dtype == self.output_dtype and output.is_contiguous(),
+                   "AGKernel: output has the wrong shape, dtype or layout")
+        bias_mode = _lib.BIAS_NONE
+        if bias is not None:
+            _check(bias.dtype == self.output_dtype and bias.is_contiguous(), "AGKernel: bias dtype/layout")
+            if tuple(bias.shape) == (m, n):
+                bias_mode = _lib.BIAS_MN
+            elif tuple(bias.shape) == (1, n) or tuple(bias.shape) == (n,):
+                bias_mode = _lib.BIAS_1N
+            else:
+                raise RuntimeError(f"AGKernel: bias shape {tuple(bias.shape)} is neither [M,N] nor [1,N]")
+        return input, weight, output, bias_mode, m_local, n, k
+
+    def forward(self, input, weight, bias=None, output=None, input_scale=None, weight_scale=None,
+                output_scale=None, fast_accum=False, transpose_weight=False, all_gather_option=None,
+                gathered_input=None, tuning=None):
+        w = self.comm.world
+        input, weight, output, bias_mode, m_local, n, k = self._prep(
+            input, weight, bias, output, input_scale, weight_scale, output_scale, transpose_weight, w)
+        sa = _expand_scale(input_scale, m_local, "input_scale")
+        sb = _expand_scale(weight_scale, n, "weight_scale")
+        if gathered_input is not None:
+            _check(tuple(gathered_input.shape) == (m_local * w, k) and gathered_input.dtype == self.input_dtype
+                   and gathered_input.is_contiguous(), "AGKernel: gathered_input has the wrong shape, dtype or layout")
+        lib = _lib.load()
+        _lib.check(
+            lib.fluxb_ag_gemm_forward(
+                self._h, input.data_ptr(), m_local, weight.data_ptr(), n, k, output.data_ptr(), _ptr(bias),
+                bias_mode, _ptr(sa), _ptr(sb), 1.0, _ptr(gathered_input), _tuning(tuning), _cur_stream(),
+            )
+        )
+        return output
+
+    def gemm_only(self, input, weight, bias=None, output=None, input_scale=None, weight_scale=None,
+                  output_scale=None, fast_accum=False, transpose_weight=False, tuning=None):
+        """Same kernel without communication: `input` is the full [M,K] matrix
+        (src/ag_gemm/ths_op/all_gather_gemm_op.cc:166-194)."""
+        input, weight, output, bias_mode, m, n, k = self._prep(
+            input, weight, bias, output, input_scale, weight_scale, output_scale, transpose_weight, 1)
+        sa = _expand_scale(input_scale, m, "input_scale")
+        sb = _expand_scale(weight_scale, n, "weight_scale")
+        lib = _lib.load()
+        _lib.check(
+            lib.fluxb_gemm(
+                self.comm.handle, input.data_ptr(), weight.data_ptr(), output.data_ptr(), m, n, k,
+                fluxb_dtype(self.input_dtype), fluxb_dtype(self.output_dtype), _ptr(bias), bias_mode,
+                _ptr(sa), _ptr(sb), 1.0, _tuning(tuning), _cur_stream(),
+            )
+        )
+        return output
+
+    def profiling(self, input, weight, bias=None, output=None, input_scale=None, weight_scale=None,
+                  output_scale=None, fast_accum=False, transpose_weight=False, all_gather_option=None,
+                  gathered_input=None, prof_ctx=None):
+        return self.forward(input, weight, bias, output, input_scale, weight_scale, output_scale, fast_accum,
+                            transpose_weight, all_gather_option, gathered_input)
+
+
+class GemmRS:
+    """`flux.GemmRS(tp_group, nnodes, max_m, n_dim, input_dtype, output_dtype=None,
+    transpose_weight=False, fuse_reduction=False, ring_reduction=False)` - reduce-scatter fused into
+    the GEMM epilogue (src/pybind/gemm_rs.cc:30-60). Partials are exchanged and summed in fp32, so
+    `fuse_reduction` / `ring_reduction` (bf16 summation orders of the reference) have nothing to select."""
+
+    def __init__(self, tp_group, nnodes, max_m, n_dim, input_dtype, output_dtype=None, transpose_weight=False,
+                 fuse_reduction=False, ring_reduction=False):
+        _check(int(nnodes) == 1, "GemmRS: only nnodes == 1 is supported")
+        self.comm: Comm = get_comm(tp_group)
+        self.max_m, self.n_dim = int(max_m), int(n_dim)
+        self.input_dtype = input_dtype
+        self.output_dtype = _out_dtype(input_dtype, output_dtype)
+        self.transpose_weight = bool(transpose_weight)
+        lib = _lib.load()
+        w = self.comm.world
+        self._stage = SymmBuffer(self.comm, lib.fluxb_gemm_rs_stage_bytes(self.max_m, self.n_dim, w))
+        self._cnt = SymmBuffer(self.comm, lib.fluxb_gemm_rs_cnt_bytes(self.max_m, self.n_dim, w))
+        h = C.c_void_p()
+        _lib.check(
+            lib.fluxb_gemm_rs_create(
+                self.comm.handle, self.max_m, self.n_dim, fluxb_dtype(input_dtype), fluxb_dtype(self.output_dtype),
+                self._stage.table(), self._cnt.table(), C.byref(h),
+            )
+        )
+        self._h = h
+        self.comm.host_barrier()
+
+    def __del__(self):
+        try:
+            _lib.load().fluxb_gemm_rs_destroy(self._h)
+        except Exception:
+            pass
+
+    def forward(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
+                fast_accum=False, reduce_scatter_option=None, tuning=None):
+        _check(input.is_cuda and weight.is_cuda, "GemmRS: tensors must be CUDA tensors")
+        _check(input.dim() == 2 and weight.dim() == 2, "GemmRS: input and weight must be 2-D")
+        _check(input.dtype == self.input_dtype and weight.dtype == self.input_dtype, "GemmRS: dtype mismatch")
+        _check(output_scale is None, "GemmRS: output_scale is not supported")
+        if self.transpose_weight:
+            _check(not is_fp8_dtype(self.input_dtype), "GemmRS: fp8 does not support transpose_weight")
+            weight = weight.t()
+        if not weight.is_contiguous():
+            weight = weight.contiguous()
+        _check(input.is_contiguous(), "GemmRS: input must be contiguous")
+        m, k = input.shape
+        n = weight.shape[0]
+        w = self.comm.world
+        _check(weight.shape[1] == k, f"GemmRS: weight K {weight.shape[1]} != input K {k}")
+        # shape rules of src/gemm_rs/ths_op/gemm_reduce_scatter.cc:499-504
+        _check(m <= self.max_m, f"GemmRS: M={m} exceeds max_m={self.max_m}")
+        _check(n == self.n_dim, f"GemmRS: N={n} differs from n_dim={self.n_dim}")
+        _check(m % w == 0, f"GemmRS: M={m} is not a multiple of the world size {w}")
+        bias_mode = _lib.BIAS_NONE
+        if bias is not None:
+            # fp8 rejects bias (gemm_reduce_scatter.cc:601-603)
+            _check(not is_fp8_dtype(self.input_dtype), "GemmRS: fp8 does not support bias")
+            _check(tuple(bias.shape) == (m, n) and bias.dtype == self.output_dtype and bias.is_contiguous(),
+                   "GemmRS: bias must be a contiguous [M,N] tensor of the output dtype")
+            bias_mode = _lib.BIAS_MN
+        sa = _expand_scale(input_scale, m, "input_scale")
+        sb = _expand_scale(weight_scale, n, "weight_scale")
+        out = torch.empty((m // w, n), dtype=self.output_dtype, device=input.device)
+        lib = _lib.load()
+        _lib.check(
+            lib.fluxb_gemm_rs_forward(
+                self._h, input.data_ptr(), weight.data_ptr(), m, n, k, out.data_ptr(), _ptr(bias), bias_mode,
+                _ptr(sa), _ptr(sb), 1.0, _tuning(tuning), _cur_stream(),
+            )
+        )
+        return out
+
+    def forward_barrier(self, *args, **kwargs):
+        """Kept for API compatibility (src/pybind/gemm_rs.cc:61-75): the push epilogue needs no barrier."""
+        return None
+
+    def forward_reduce_scatter(self, *args, **kwargs):
+        raise RuntimeError("GemmRS.forward_reduce_scatter: the reduction is fused; call forward()")
+
+    def zero_buffers(self):
+        """Counters clear themselves after every call; nothing to zero (gemm_reduce_scatter.cc:654-657)."""
+        return None
+
+    def profiling(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
+                  fast_accum=False, prof_ctx=None, reduce_scatter_option=None):
+        return self.forward(input, weight, bias, input_scale, weight_scale, output_scale, fast_accum,
+                            reduce_scatter_option)
+
+
+def bitwise_check(a: torch.Tensor, b: torch.Tensor) -> bool:
+    """`flux.bitwise_check` (src/pybind/ths_op.cc:304-306): same shape, dtype and bits."""
+    if a.shape != b.shape or a.dtype != b.dtype:
+        return False
+    return bool(torch.equal(a.contiguous().view(torch.uint8), b.contiguous().view(torch.uint8)))
+
+
+def uniform_initialize(t: torch.Tensor, seed: int, lo: float, hi: float) -> None:
+    """`flux.uniform_initialize` (src/pybind/ths_op.cc:307-315)."""
+    g = torch.Generator(device=t.device).manual_seed(int(seed))
+    tmp = torch.empty(t.shape, dtype=torch.float32, device=t.device).uniform_(lo, hi, generator=g)
+    t.copy_(tmp.to(t.dtype))

@@ -1,0 +1,185 @@
+"""Generate the golden vectors under tests/golden/ from the reference's own code.
+
+Run in a checkout that has the reference mounted (default /root/reference):
+
+    python tests/golden/make_golden.py [--reference /path/to/flux]
+
+The reference's pure-torch golden helpers live in `python/flux/testing/*.py`,
+which `import flux` (the compiled extension, not buildable here). This script
+registers a stub module named `flux` that only supplies `is_fp8_dtype` and
+placeholder attributes, loads the helper files from the reference tree as they
+are, and runs them on seeded CPU inputs (2 gloo ranks where a collective is
+involved). Inputs and outputs are written to `tests/golden/*.pt`; the tests
+then check `oracle/golden.py` against them without needing the reference.
+Nothing from the reference is copied: only its outputs are stored.
+"""
+import argparse
+import importlib.util
+import os
+import socket
+import sys
+import types
+from pathlib import Path
+from unittest import mock
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+HERE = Path(__file__).resolve().parent
+
+
+def _install_stub():
+    flux = types.ModuleType("flux")
+    util = types.ModuleType("flux.util")
+
+    def is_fp8_dtype(dt):
+        return dt in (torch.float8_e4m3fn, torch.float8_e5m2)
+
+    util.is_fp8_dtype = is_fp8_dtype
+    flux.is_fp8_dtype = is_fp8_dtype
+    flux.util = util
+    # anything else the helper modules touch at import time is a placeholder
+    flux.__getattr__ = lambda name: mock.MagicMock(name=f"flux.{name}")
+    testing = types.ModuleType("flux.testing")
+    testing.__path__ = []
+    flux.testing = testing
+    sys.modules["flux"] = flux
+    sys.modules["flux.util"] = util
+    sys.modules["flux.testing"] = testing
+    return flux, testing
+
+
+def _load(ref_root: Path, name: str, testing_mod):
+    path = ref_root / "python" / "flux" / "testing" / f"{name}.py"
+    spec = importlib.util.spec_from_file_location(f"flux.testing.{name}", path)
+    mod = importlib.util.module_from_spec(spec)
+    sys.modules[f"flux.testing.{name}"] = mod
+    spec.loader.exec_module(mod)
+    for k, v in vars(mod).items():
+        if not k.startswith("_"):
+            setattr(testing_mod, k, v)
+    return mod
+
+
+def load_reference_helpers(ref_root: Path):
+    _, testing = _install_stub()
+    utils = _load(ref_root, "utils", testing)
+    moe_utils = _load(ref_root, "moe_utils", testing)
+    ag = _load(ref_root, "moe_ag_scatter_utils", testing)
+    rs = _load(ref_root, "moe_gather_rs_utils", testing)
+    return utils, moe_utils, ag, rs
+
+
+# ----------------------------------------------------------------------------- routing (integer)
+def gen_routing(moe_utils):
+    cases = []
+    for seed, (ntokens, topk, nexperts) in enumerate([(16, 2, 4), (64, 2, 8), (37, 3, 5), (128, 4, 32), (8, 1, 8)]):
+        g = torch.Generator().manual_seed(100 + seed)
+        scores = torch.rand(ntokens, nexperts, generator=g)
+        chosen = torch.topk(scores, topk, dim=-1).indices.to(torch.int32)
+        scatter = moe_utils.calc_scatter_index_stable(chosen)  # reference function
+        splits = torch.bincount(chosen.view(-1), minlength=nexperts).to(torch.int32)  # moe_utils.py:212-214
+        cases.append({"chosen": chosen, "nexperts": nexperts, "scatter_index": scatter, "splits": splits})
+    torch.save(cases, HERE / "routing.pt")
+    print("routing.pt:", len(cases), "cases")
+
+
+# ----------------------------------------------------------------------------- MoE layer 0 (scatter + grouped GEMM)
+def gen_moe_l0(ag, moe_utils):
+    cases = []
+    for seed, (ntokens, topk, nexperts, hidden, ffn, dtype) in enumerate(
+        [(32, 2, 4, 64, 48, torch.float32), (64, 2, 8, 128, 96, torch.bfloat16)]
+    ):
+        g = torch.Generator().manual_seed(200 + seed)
+        scores = torch.rand(ntokens, nexperts, generator=g)
+        chosen = torch.topk(scores, topk, dim=-1).indices.to(torch.int32)
+        scatter = moe_utils.calc_scatter_index_stable(chosen)
+        splits = torch.bincount(chosen.view(-1), minlength=nexperts).to(torch.int32)
+        inv = torch.empty(ntokens * topk, dtype=torch.int64)
+        inv[scatter.view(-1).long()] = torch.arange(ntokens * topk) // topk
+        tokens = torch.randn(ntokens, hidden, generator=g).to(dtype)
+        weights = (torch.randn(nexperts, ffn, hidden, generator=g) * 0.05).to(dtype)
+        out_scale = torch.rand(nexperts, generator=g) + 0.5
+        ctx = types.SimpleNamespace(
+            inputs=tokens, scatter_inputs=torch.zeros(ntokens * topk, hidden, dtype=dtype), gather_index=inv,
+            is_s8=False, input_scale=None, weight_groups=1, nexperts_ep=nexperts, ep_rank=0,
+            splits_cpu=splits, outputs=[torch.zeros(ntokens * topk, ffn, dtype=dtype)], weights=[weights],
+            fast_accum=False, bias=None, output_scale=[out_scale],
+        )
+        ag.MoeAgScatterWithTorch.scatter_impl(ctx)  # reference functions
+        ag.MoeAgScatterWithTorch.gemm_impl(ctx, None)
+        cases.append({"tokens": tokens, "weights": weights, "splits": splits, "scatter_index": scatter,
+                      "output_scale": out_scale, "out": ctx.outputs[0].clone()})
+    torch.save(cases, HERE / "moe_l0.pt")
+    print("moe_l0.pt:", len(cases), "cases")
+
+
+# ----------------------------------------------------------------------------- MoE layer 1 (2 gloo ranks)
+def _l1_inputs(rank, case):
+    ntokens, topk, nexperts, kloc, n, dtype = case
+    g = torch.Generator().manual_seed(300)  # routing is global: same on every rank
+    scores = torch.rand(ntokens, nexperts, generator=g)
+    chosen = torch.topk(scores, topk, dim=-1).indices.to(torch.int32)
+    gr = torch.Generator().manual_seed(310 + rank)
+    x = torch.randn(ntokens * topk, kloc, generator=gr).to(dtype)
+    w = (torch.randn(nexperts, n, kloc, generator=gr) * 0.05).to(dtype)
+    vec = torch.rand(ntokens * topk, generator=gr) + 0.25
+    return chosen, x, w, vec
+
+
+def _l1_worker(rank, world, port, ref_root, case, out_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _, moe_utils, _, rs = load_reference_helpers(Path(ref_root))
+    ntokens, topk, nexperts, kloc, n, dtype = case
+    chosen, x, w, vec = _l1_inputs(rank, case)
+    scatter = moe_utils.calc_scatter_index_stable(chosen)
+    splits = torch.bincount(chosen.view(-1), minlength=nexperts).to(torch.int32)
+    order = chosen.flatten().sort(stable=True).indices  # calc_gather_index_stable (moe_utils.py:87-93) on CPU
+    token_index = (order // topk).to(torch.int32)
+    topk_index = torch.arange(topk, dtype=torch.int32).repeat(ntokens)[order]
+    # reference golden; do_all_reduce=True keeps every tensor on the CPU (the reduce-scatter branch
+    # allocates on CUDA); the reduce-scattered result is the row slice of the all-reduced one.
+    full = rs.moe_gather_rs_forward_torch(
+        dist.group.WORLD, ntokens * topk, 0, 0, ntokens * topk, x, w, splits, token_index, topk_index, topk,
+        torch.ones(1), torch.ones(nexperts), vec, do_all_reduce=True,
+    )
+    tpr = ntokens // world
+    mine = {"x": x, "w": w, "vec": vec, "out": full[rank * tpr:(rank + 1) * tpr].clone()}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
+    if rank == 0:
+        torch.save({"case": case, "chosen": chosen, "scatter_index": scatter, "splits": splits, "ranks": gathered},
+                   out_path)
+    dist.destroy_process_group()
+
+
+def gen_moe_l1(ref_root):
+    outs = []
+    for i, case in enumerate([(16, 2, 4, 32, 24, torch.float32), (32, 2, 8, 64, 48, torch.bfloat16)]):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        tmp = HERE / f"_l1_{i}.pt"
+        mp.spawn(_l1_worker, args=(2, port, str(ref_root), case, str(tmp)), nprocs=2, join=True)
+        outs.append(torch.load(tmp, weights_only=False))
+        tmp.unlink()
+    torch.save(outs, HERE / "moe_l1.pt")
+    print("moe_l1.pt:", len(outs), "cases")
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    ref_root = Path(args.reference)
+    _, moe_utils, ag, _ = load_reference_helpers(ref_root)
+    gen_routing(moe_utils)
+    gen_moe_l0(ag, moe_utils)
+    gen_moe_l1(ref_root)
+
+
+if __name__ == "__main__":
+    main()
