@@ -1,0 +1,412 @@
+#!/usr/bin/env python
+"""Headline benchmark: the dense tensor-parallel MLP of the reference's performance table
+(docs/performance.md:13-20) - layer 0 = AG-GEMM (M=4096, N=49152, K=12288), layer 1 = GEMM-RS
+(M=4096, N=12288, K=49152), bf16, TP = number of GPUs. One step = AGKernel.forward followed by
+GemmRS.forward on its output. Global (M, N, K) are fixed, so N GPUs split the same work ("strong").
+
+    python bench.py --gpus 1 --steps 20 --warmup 5
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 20 --warmup 5
+    python bench.py --impl reference ...     # the reference's torch golden path on the host cores
+
+Prints ONE JSON line on rank 0. `value` = aggregate TFLOP/s over all GPUs with inputs resident in HBM;
+`e2e` = the same through host buffers (H2D of the activations and D2H of the result inside the timed
+region); `roofline` = the fused kernel against the measured bf16 tensor peak; `unfused` = cuBLAS + NCCL
+on the same box; `cpu_baseline` = the oracle on the host cores (a baseline, not the target).
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+M, N0, K0 = 4096, 49152, 12288  # layer 0: C0[M, N0/TP] = all_gather(A)[M, K0] . B0[N0/TP, K0]^T
+N1, K1 = 12288, 49152           # layer 1: out[M/TP, N1] = reduce_scatter(C0[M, K1/TP] . B1[N1, K1/TP]^T)
+SEED = 1234
+FALLBACK_BF16_TFLOPS = 1590.0   # earlier measurement on this pool, used only if MEASURED_PEAKS.json is absent
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), float(d["bf16_tflops"]), "measured"
+    return FALLBACK_BF16_TFLOPS, FALLBACK_BF16_TFLOPS, "fallback"
+
+
+def _env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", str(rank)))
+    return rank, world, local
+
+
+def _flops_per_gpu(world):
+    return 2.0 * M * (N0 // world) * K0 + 2.0 * M * N1 * (K1 // world)
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                 "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.proc = None
+
+    def stop(self):
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.f.flush()
+        rows = [l.strip().split(", ") for l in open(self.f.name) if l.strip()]
+        os.unlink(self.f.name)
+        sm, reasons, mx = [], set(), None
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1]))
+                mx = float(r[2])
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+                if val.strip().lower().startswith("active"):
+                    reasons.add(name)
+        if sm:
+            # under load = upper half of the samples (the sampler also sees the idle edges)
+            sm.sort()
+            out["sm_mhz"] = statistics.median(sm[len(sm) // 2:])
+            out["sm_max_mhz"] = mx
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def _max_over_ranks(x, world):
+    if world == 1:
+        return x
+    t = torch.tensor([x], dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def _make_inputs(rank, world):
+    """Seeded synthetic tensors with the shapes and distributions of the reference's dense MLP test
+    (A ~ N(0,1), weights ~ N(0,0.02), seed = base + rank); generated on the GPU for speed."""
+    g = torch.Generator(device="cuda").manual_seed(SEED + rank)
+    a = torch.randn(M // world, K0, generator=g, device="cuda").to(torch.bfloat16)
+    b0 = (torch.randn(N0 // world, K0, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    b1 = (torch.randn(N1, K1 // world, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    return a, b0, b1
+
+
+def _sampled_check(a, b0, b1, c0, out, rank, world):
+    """Cheap live parity guard: a few output entries of layer 0 against fp64 dot products (rows of the
+    local shard only, so no communication is needed). The full parity suite is tests/ -m gpu."""
+    m_local = M // world
+    rows = torch.arange(0, m_local, max(1, m_local // 8), device="cuda")[:8]
+    cols = torch.arange(0, N0 // world, max(1, (N0 // world) // 8), device="cuda")[:8]
+    exact = a[rows].double() @ b0[cols].double().t()
+    got = c0[rank * m_local + rows][:, cols].double()
+    return float((got - exact).abs().max() / exact.abs().max().clamp_min(1e-30))
+
+
+def run_ours(args):
+    rank, world, local = _env()
+    assert world == args.gpus, f"--gpus {args.gpus} but WORLD_SIZE={world}"
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+        group = dist.group.WORLD
+    import flux_b200 as flux
+    from flux_b200 import _lib
+
+    loaded = str(_lib.lib_path())
+    flux.init_flux_shm(group)
+    comm = flux.get_comm(group)
+    a, b0, b1 = _make_inputs(rank, world)
+    ag = flux.AGKernel(group, 1, M, N0 // world, K0, torch.bfloat16)
+    rs = flux.GemmRS(group, 1, M, N1, torch.bfloat16)
+    c0 = torch.empty((M, N0 // world), dtype=torch.bfloat16, device="cuda")
+
+    def step():
+        ag.forward(a, b0, output=c0)
+        return rs.forward(c0, b1)
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        out = step()
+    barrier()
+    comm.check_status()
+    sampled_err = _sampled_check(a, b0, b1, c0, out, rank, world)
+
+    # ---- timed region: K steps, per-op split from extra events on the same stream
+    sampler = ClockSampler(local) if rank == 0 else None
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    barrier()
+    t_wall = time.perf_counter()
+    for i in range(args.steps):
+        ev[i][0].record()
+        ag.forward(a, b0, output=c0)
+        ev[i][1].record()
+        out = rs.forward(c0, b1)
+        ev[i][2].record()
+    end = torch.cuda.Event(enable_timing=True)
+    end.record()
+    barrier()
+    wall_ms = (time.perf_counter() - t_wall) * 1e3
+    clocks = sampler.stop() if sampler else None
+    comm.check_status()
+    total_ms = ev[0][0].elapsed_time(end)
+    ag_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    rs_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    ms_per_step = _max_over_ranks(total_ms / args.steps, world)
+    ag_ms = _max_over_ranks(ag_ms, world)
+    rs_ms = _max_over_ranks(rs_ms, world)
+
+    # ---- unfused sequence on the same box: NCCL all_gather + cuBLAS, cuBLAS + NCCL reduce_scatter
+    full_a = torch.empty((M, K0), dtype=torch.bfloat16, device="cuda")
+    rs_out = torch.empty((M // world, N1), dtype=torch.bfloat16, device="cuda")
+
+    def unfused_step():
+        if world > 1:
+            dist.all_gather_into_tensor(full_a, a)
+            x = full_a
+        else:
+            x = a
+        h = torch.matmul(x, b0.t())
+        full = torch.matmul(h, b1.t())
+        if world > 1:
+            dist.reduce_scatter_tensor(rs_out, full)
+            return rs_out
+        return full
+
+    for _ in range(3):
+        unfused_step()
+    barrier()
+    u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    u0.record()
+    for _ in range(args.steps):
+        uo = unfused_step()
+    u1.record()
+    barrier()
+    unfused_ms = _max_over_ranks(u0.elapsed_time(u1) / args.steps, world)
+    agree = float((uo.float() - out.float()).abs().max() / uo.float().abs().max().clamp_min(1e-30))
+
+    # ---- end to end through host buffers: H2D of this rank's activations, both ops, D2H of the result
+    a_host = a.cpu().pin_memory()
+    out_host = torch.empty((M // world, N1), dtype=torch.bfloat16).pin_memory()
+    a_dev = torch.empty_like(a)
+
+    def e2e_step():
+        a_dev.copy_(a_host, non_blocking=True)
+        ag.forward(a_dev, b0, output=c0)
+        o = rs.forward(c0, b1)
+        out_host.copy_(o, non_blocking=True)
+
+    for _ in range(3):
+        e2e_step()
+    barrier()
+    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    e2e_ms = _max_over_ranks(s0.elapsed_time(s1) / args.steps, world)
+    comm.check_status()
+
+    flops_gpu = _flops_per_gpu(world)
+    total_flops = flops_gpu * world
+    sustained, burst, peak_src = _peaks()
+    ag_flops = 2.0 * M * (N0 // world) * K0
+    ag_tflops = ag_flops / (ag_ms * 1e-3) / 1e12
+    rs_tflops = (2.0 * M * N1 * (K1 // world)) / (rs_ms * 1e-3) / 1e12
+
+    if rank == 0:
+        line = {
+            "metric": "dense TP MLP (AG-GEMM + GEMM-RS) aggregate TFLOP/s",
+            "value": total_flops / (ms_per_step * 1e-3) / 1e12,
+            "unit": "TFLOP/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": max(args.warmup, 3),
+            "ms_per_step": ms_per_step,
+            "higher_is_better": True,
+            "scaling": "strong",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic (seeded N(0,1) activations, N(0,0.02) weights; shapes of the reference's dense MLP test)",
+            "config": {
+                "workload": f"D0 AG-GEMM M={M} N={N0} K={K0} then D1 GEMM-RS M={M} N={N1} K={K1}, bf16, TP={world}",
+                "parallelism": f"tp{world}",
+                "l2": "weights per rank (>= 302 MB) exceed the 126 MB L2 between iterations; no explicit flush",
+            },
+            "tflops_per_gpu": flops_gpu / (ms_per_step * 1e-3) / 1e12,
+            "ag_gemm": {"ms": ag_ms, "tflops_per_gpu": ag_tflops},
+            "gemm_rs": {"ms": rs_ms, "tflops_per_gpu": rs_tflops},
+            "unfused": {"what": "NCCL all_gather + cuBLAS matmul, cuBLAS matmul + NCCL reduce_scatter (torch)",
+                        "ms_per_step": unfused_ms, "tflops_per_gpu": flops_gpu / (unfused_ms * 1e-3) / 1e12,
+                        "max_rel_diff_vs_fused": agree},
+            "speedup_vs_unfused": unfused_ms / ms_per_step,
+            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+                    "h2d_bytes_per_step": a.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world},
+            "gpu_launches": args.steps * (2 if world == 1 else 3),
+            "roofline": {"bound": "tensor", "achieved": ag_tflops, "peak": sustained, "unit": "TFLOP/s",
+                         "frac": ag_tflops / sustained, "frac_of_burst_peak": ag_tflops / burst,
+                         "peak_source": f"{peak_src} cuBLAS bf16, sustained (kernel timed inside a long step)",
+                         "kernel": "fused_gemm_kernel (AG-GEMM launch)", "traffic": None},
+            "clocks": clocks,
+            "sampled_max_rel_err": sampled_err,
+            "wall_ms_timed_region": wall_ms,
+            "native_library": loaded,
+        }
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(budget_s=args.cpu_seconds)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def run_kernel_only(args):
+    """Small single-GPU case for profiler captures: the fused kernel alone at the per-rank shape of
+    D0 at TP=8 (M=4096, N=6144, K=12288; 302 MB of operands, larger than L2)."""
+    torch.cuda.set_device(0)
+    import flux_b200 as flux
+
+    flux.init_flux_shm(None)
+    m, n, k = M, N0 // 8, K0
+    g = torch.Generator(device="cuda").manual_seed(SEED)
+    a = torch.randn(m, k, generator=g, device="cuda").to(torch.bfloat16)
+    b = (torch.randn(n, k, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
+    op = flux.AGKernel(None, 1, m, n, k, torch.bfloat16)
+    c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    for _ in range(args.warmup):
+        op.gemm_only(a, b, output=c)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        op.gemm_only(a, b, output=c)
+    e1.record()
+    torch.cuda.synchronize()
+    op.comm.check_status()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"case": "kernel-only", "m": m, "n": n, "k": k, "ms": ms,
+                      "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12}), flush=True)
+
+
+def _cpu_sample_run(m_s, n_s, k_s, iters=1):
+    """The oracle's AG-GEMM + GEMM-RS sequence on the host cores for a slice of the workload."""
+    from oracle import golden
+
+    g = torch.Generator().manual_seed(SEED)
+    a = torch.randn(m_s, k_s, generator=g).to(torch.bfloat16)
+    b0 = (torch.randn(n_s, k_s, generator=g) * 0.02).to(torch.bfloat16)
+    b1 = (torch.randn(k_s, n_s, generator=g) * 0.02).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        h, _ = golden.ag_gemm_single([a], b0)
+        golden.gemm_rs_single([h], [b1])
+    dt = (time.perf_counter() - t0) / iters
+    return dt, 2.0 * m_s * n_s * k_s * 2
+
+
+def cpu_baseline(budget_s=15.0):
+    cores = torch.get_num_threads()
+    dt, fl = _cpu_sample_run(128, 512, 2048)
+    rate = fl / dt
+    # a 1/8 slice of the workload per pass (shrunk on slow hosts), repeated to about `budget_s` seconds
+    m_s, n_s, k_s = 512, 6144, 12288
+    while 2.0 * m_s * n_s * k_s * 2 / rate > budget_s and n_s > 384:
+        n_s //= 2
+    dt1, fl = _cpu_sample_run(m_s, n_s, k_s)
+    iters = max(1, min(200, int(budget_s / max(dt1, 1e-3))))
+    dt, fl = _cpu_sample_run(m_s, n_s, k_s, iters=iters)
+    return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
+            "sample": f"oracle AG-GEMM + GEMM-RS on a slice M={m_s} N={n_s} K={k_s} (bf16, torch CPU), "
+                      f"{iters} passes, {dt * iters:.1f} s"}
+
+
+def run_reference(args):
+    """The reference's torch golden path (all_gather + matmul, matmul + reduce_scatter) on the host
+    cores: the oracle restatement, single process with every host thread; rank 0 only."""
+    rank, world, _ = _env()
+    if rank != 0:
+        return
+    cores = torch.get_num_threads()
+    dt, fl = _cpu_sample_run(128, 512, 2048)
+    rate = fl / dt
+    m_s, n_s, k_s = 512, 6144, 12288
+    per_step_budget = max(1.0, 120.0 / max(1, args.steps + args.warmup))
+    while 2.0 * m_s * n_s * k_s * 2 / rate > per_step_budget and n_s > 96:
+        n_s //= 2
+    for _ in range(args.warmup):
+        _cpu_sample_run(m_s, n_s, k_s)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        _, fl = _cpu_sample_run(m_s, n_s, k_s)
+    dt = (time.perf_counter() - t0) / args.steps
+    val = fl / dt / 1e12
+    sample = f"oracle AG-GEMM + GEMM-RS on a slice M={m_s} N={n_s} K={k_s} per step (bf16, torch CPU)"
+    print(json.dumps({
+        "impl": "reference",
+        "metric": "dense TP MLP (AG-GEMM + GEMM-RS) aggregate TFLOP/s",
+        "value": val, "unit": "TFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"D0 AG-GEMM M={M} N={N0} K={K0} then D1 GEMM-RS M={M} N={N1} K={K1}, bf16 "
+                               f"(bounded sample per step)", "parallelism": "host cores"},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--cpu-seconds", type=float, default=15.0)
+    ap.add_argument("--kernel-only", action="store_true", help="small single-GPU case for profiler captures")
+    args = ap.parse_args()
+    if args.kernel_only:
+        run_kernel_only(args)
+    elif args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
