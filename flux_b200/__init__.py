@@ -23,7 +23,8 @@ from .ops import (
     is_fp8_dtype,
     uniform_initialize,
 )
-from .shm import GroupBarrier, flux_create_tensor_list, get_comm, init_flux_shm
+from .moe import GemmGroupedV3AGScatter, GemmGroupedV3GatherRS, calc_gather_index, calc_scatter_index
+from .shm import GroupBarrier, default_comm, flux_create_tensor_list, get_comm, init_flux_shm
 from .util import bench_func, get_arch, group_profile, torch_allclose, with_torch_deterministic
 
 create_tensor_list = flux_create_tensor_list
@@ -32,5 +33,6 @@ __all__ = [
     "AGKernel", "AGRingMode", "AllGatherOption", "DistEnvTP", "DistEnvTPWithEP", "GemmRS", "MoeArguments",
     "ProfilingContext", "ReduceScatterOption", "RingMode", "bitwise_check", "is_fp8_dtype", "uniform_initialize",
     "GroupBarrier", "flux_create_tensor_list", "create_tensor_list", "get_comm", "init_flux_shm", "bench_func",
-    "get_arch", "group_profile", "torch_allclose", "with_torch_deterministic", "FluxbError", "Tuning", "util",
+    "get_arch", "group_profile", "GemmGroupedV3AGScatter", "GemmGroupedV3GatherRS", "calc_scatter_index",
+    "calc_gather_index", "default_comm", "torch_allclose", "with_torch_deterministic", "FluxbError", "Tuning", "util",
 ]

@@ -70,6 +70,7 @@ struct GemmParams {
   const float* scale_a;  // per output row (may be null)
   const float* scale_b;  // per output column (may be null)
   float alpha;
+  const float* alpha_ptr;  // optional device scalar multiplied into alpha
   // all-gather: consumer side
   const int* ag_flags;  // [nseg][ag_flag_stride], null = no waits
   int ag_flag_stride;
@@ -88,7 +89,7 @@ struct GemmParams {
   // grouped mode
   const GroupTile* g_tiles;  // null = dense
   const int* g_num_tiles;    // device scalar
-  const int* g_gather;       // sorted row -> source row of A
+  const int* g_gather;       // sorted row -> source row of A (null: A rows are already sorted)
   int g_rows_per_expert_b;   // rows of B per expert (= N)
   const float* g_expert_scale;  // optional per-expert alpha
   const int* g_scatter_rows;    // optional: sorted row -> output row (null = identity)
@@ -264,7 +265,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             break;
           }
           mbar_arrive_expect_tx(bar_full(stage), L::kStageBytes);
-          if (p.g_tiles == nullptr) {
+          if (p.g_gather == nullptr) {
             tma_load_2d(smem_a(stage), &p.tmap_a, bar_full(stage), kb * BKE, tc.row0);
           } else {
             // 32 gather4 copies of 4 rows each; rows past the tile end re-read row 0 of the tile
@@ -342,6 +343,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       const bool row_ok = row_in_tile < tc.rows;
       const int grow = tc.row0 + row_in_tile;  // global / sorted row
       float row_scale = p.alpha;
+      if (p.alpha_ptr != nullptr) row_scale *= *p.alpha_ptr;
       if (p.scale_a != nullptr && row_ok) row_scale *= p.scale_a[grow];
       if (p.g_expert_scale != nullptr) row_scale *= p.g_expert_scale[tc.expert];
 

@@ -71,6 +71,11 @@ namespace fluxb {
 int encode_tmap_2d(CUtensorMap* out, const void* base, int elt_dtype, long long rows, long long k,
                    long long ld_bytes, int box_rows);
 
+// Output tile width for a problem: the caller's choice, else a wave-quantisation heuristic.
+// `m_tiles_hint` > 0 overrides the M-tile count derived from the segments (grouped problems).
+int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tuning* tuning,
+                    long long m_tiles_hint);
+
 // Fill the problem-independent fields and launch the fused kernel.
 int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
                       const fluxb_tuning* tuning, cudaStream_t stream);

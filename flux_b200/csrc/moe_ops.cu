@@ -1,15 +1,571 @@
-// MoE grouped ops (placeholder while the dense path is brought up).
+// MoE grouped ops on top of the fused kernel's grouped mode.
+//
+// Layer 0 (all-gather + scatter + grouped GEMM) replaces
+// src/moe_ag_scatter/ths_op/gemm_grouped_v3_ag_scatter.cc:227-447: the token
+// shard is pushed to every peer by the kernel's comm warps, the routing tables
+// (inverse permutation, per-expert M tiles, which source ranks a tile reads)
+// are built on the device - no device-to-host copy or host scheduling per call
+// (the reference does both, :323-363) - and A rows are fetched by token index
+// with TMA gather4, so the gathered-and-permuted activation matrix is never
+// materialised.
+//
+// Layer 1 (grouped GEMM + top-k gather + reduce-scatter) replaces
+// src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:595-820: grouped GEMM
+// into a local [rows, N] buffer with the per-row / per-expert scales applied in
+// the epilogue, then every token's top-k rows are summed in fp32 and pushed to
+// the token's owner, which sums the per-source partials in fp32.
+#include <string.h>
+
+#include <vector>
+
 #include "internal.h"
-using namespace fluxb;
-extern "C" {
-size_t fluxb_moe_ag_scatter_workspace_bytes(int, int, int) { return 0; }
-int fluxb_moe_ag_scatter_create(fluxb_comm_t, int, int, int, int, int, int, int, void* const*, int* const*, void*, fluxb_moe_ag_scatter_t*) { FLUXB_FAIL(FLUXB_ERR_UNSUPPORTED, "not built yet"); }
-int fluxb_moe_ag_scatter_destroy(fluxb_moe_ag_scatter_t) { return FLUXB_OK; }
-int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t, const void*, int, const void*, const int*, const int*, const float*, void*, void*, const fluxb_tuning*, fluxb_stream_t) { FLUXB_FAIL(FLUXB_ERR_UNSUPPORTED, "not built yet"); }
-size_t fluxb_moe_gather_rs_workspace_bytes(int, int, int, int) { return 0; }
-size_t fluxb_moe_gather_rs_stage_bytes(int, int, int, int) { return 0; }
-size_t fluxb_moe_gather_rs_cnt_bytes(int, int, int) { return 0; }
-int fluxb_moe_gather_rs_create(fluxb_comm_t, int, int, int, int, int, int, float* const*, int* const*, void*, fluxb_moe_gather_rs_t*) { FLUXB_FAIL(FLUXB_ERR_UNSUPPORTED, "not built yet"); }
-int fluxb_moe_gather_rs_destroy(fluxb_moe_gather_rs_t) { return FLUXB_OK; }
-int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t, const void*, int, int, const void*, const int*, const int*, const float*, const float*, const float*, void*, const fluxb_tuning*, fluxb_stream_t) { FLUXB_FAIL(FLUXB_ERR_UNSUPPORTED, "not built yet"); }
+
+namespace fluxb {
+
+constexpr int kTokBlock = 8;  // tokens per push / reduce work item of layer 1
+
+struct MoeTables {
+  GroupTile* tiles;
+  int* num_tiles;
+  int* expert_off;  // [E+1]
+  int* tile_base;   // [E+1]
+  int* gather;      // [max_rows]
+};
+
+static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+static size_t tables_bytes(long long max_rows, int nexperts) {
+  size_t b = 0;
+  b += align_up((max_rows / kBM + nexperts + 1) * sizeof(GroupTile), 256);
+  b += 256;                                                 // num_tiles
+  b += align_up((nexperts + 1) * sizeof(int), 256) * 2;     // expert_off, tile_base
+  b += align_up(static_cast<size_t>(max_rows) * sizeof(int), 256);  // gather
+  return b;
 }
+
+static MoeTables carve_tables(void* ws, long long max_rows, int nexperts) {
+  uint8_t* p = static_cast<uint8_t*>(ws);
+  MoeTables t;
+  t.tiles = reinterpret_cast<GroupTile*>(p);
+  p += align_up((max_rows / kBM + nexperts + 1) * sizeof(GroupTile), 256);
+  t.num_tiles = reinterpret_cast<int*>(p);
+  p += 256;
+  t.expert_off = reinterpret_cast<int*>(p);
+  p += align_up((nexperts + 1) * sizeof(int), 256);
+  t.tile_base = reinterpret_cast<int*>(p);
+  p += align_up((nexperts + 1) * sizeof(int), 256);
+  t.gather = reinterpret_cast<int*>(p);
+  return t;
+}
+
+// One block. Prefix sums over the experts, then each expert writes its tiles.
+__global__ void __launch_bounds__(1024)
+moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_rows, int max_tiles,
+                       MoeTables t, int* status) {
+  __shared__ int ok;
+  if (threadIdx.x == 0) {
+    int off = 0, tb = 0;
+    for (int e = 0; e < nexperts; ++e) {
+      t.expert_off[e] = off;
+      t.tile_base[e] = tb;
+      const int n = splits[e] < 0 ? 0 : splits[e];
+      off += n;
+      tb += (n + kBM - 1) / kBM;
+    }
+    t.expert_off[nexperts] = off;
+    t.tile_base[nexperts] = tb;
+    ok = (off == total_rows && tb <= max_tiles) ? 1 : 0;
+    *t.num_tiles = ok ? tb : 0;
+    if (!ok) {
+      *reinterpret_cast<volatile int*>(status) = kStatusBadTable;
+      __threadfence_system();
+    }
+  }
+  __syncthreads();
+  if (!ok) return;
+  for (int e = threadIdx.x; e < nexperts; e += blockDim.x) {
+    const int off = t.expert_off[e];
+    const int n = t.expert_off[e + 1] - off;
+    const int tb = t.tile_base[e];
+    for (int c = 0; c * kBM < n; ++c) {
+      GroupTile g;
+      g.a_row0 = off + c * kBM;
+      g.rows = imin(kBM, n - c * kBM);
+      g.expert = e;
+      g.need_mask = 0;
+      t.tiles[tb + c] = g;
+    }
+  }
+}
+
+// One thread per (token, k): inverse permutation and the source-rank mask of the row's tile.
+__global__ void moe_route_rows_kernel(const int* __restrict__ scatter_index, int total, int topk,
+                                      int tokens_per_rank, int nexperts, MoeTables t) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total || *t.num_tiles == 0) return;
+  const int row = scatter_index[i];
+  if (row < 0 || row >= total) return;
+  const int token = i / topk;
+  t.gather[row] = token;
+  int lo = 0, hi = nexperts;  // largest e with expert_off[e] <= row
+  while (hi - lo > 1) {
+    const int mid = (lo + hi) >> 1;
+    if (t.expert_off[mid] <= row) lo = mid; else hi = mid;
+  }
+  const int tile = t.tile_base[lo] + (row - t.expert_off[lo]) / kBM;
+  atomicOr(&t.tiles[tile].need_mask, 1 << (token / tokens_per_rank));
+}
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+struct PushTargets {
+  void* stage[kMaxWorld];  // owner o's staging slot of this source rank: [tokens_per_rank][n]
+  int* cnt[kMaxWorld];     // owner o's per-token-block counters
+};
+
+// For every token: sum its top-k rows of `inter` in fp32, round once, store into the owner's
+// staging slot; one counter increment per finished block of kTokBlock tokens. Owners are visited
+// starting with rank+1 so that at any time the ranks push to different owners.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_topk_push_kernel(const T* __restrict__ inter, const int* __restrict__ scatter_index, int topk, int n,
+                     int tokens_per_rank, int rank, int world, PushTargets tg) {
+  const int blocks_per_owner = (tokens_per_rank + kTokBlock - 1) / kTokBlock;
+  const int total = world * blocks_per_owner;
+  const int nvec = n / 8;
+  for (int w = blockIdx.x; w < total; w += gridDim.x) {
+    const int oi = w / blocks_per_owner;
+    const int blk = w - oi * blocks_per_owner;
+    const int owner = (rank + 1 + oi) % world;
+    const int t0 = blk * kTokBlock;
+    const int t1 = imin(t0 + kTokBlock, tokens_per_rank);
+    T* dst = static_cast<T*>(tg.stage[owner]);
+    for (int tl = t0; tl < t1; ++tl) {
+      const int token = owner * tokens_per_rank + tl;
+      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int k = 0; k < topk; ++k) {
+          const int row = scatter_index[token * topk + k];
+          const uint4 raw = *reinterpret_cast<const uint4*>(inter + static_cast<long long>(row) * n + v * 8);
+          const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
+        }
+        uint4 outv;
+        T* o = reinterpret_cast<T*>(&outv);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(acc[j]);
+        *reinterpret_cast<uint4*>(dst + static_cast<long long>(tl) * n + v * 8) = outv;
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      fence_acq_rel_sys();
+      red_add_release_sys(tg.cnt[owner] + blk, 1);
+    }
+  }
+}
+
+// Owner side: once every source has published a token block, sum the per-source partials in fp32.
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_rs_reduce_kernel(const T* __restrict__ stage, int* cnt, T* out, int n, int tokens_per_rank, int world,
+                     int* status, unsigned long long budget_ns) {
+  __shared__ int s_ok;
+  const int blocks = (tokens_per_rank + kTokBlock - 1) / kTokBlock;
+  const int nvec = n / 8;
+  const long long slot = static_cast<long long>(tokens_per_rank) * n;
+  for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
+    if (threadIdx.x == 0)
+      s_ok = flag_wait_eq(cnt + blk, world, nullptr, kStatusTimeoutReduce, budget_ns) ? 1 : 0;
+    __syncthreads();
+    if (!s_ok) {
+      if (threadIdx.x == 0) {
+        *reinterpret_cast<volatile int*>(status) = kStatusTimeoutReduce;
+        __threadfence_system();
+      }
+      return;
+    }
+    const int t0 = blk * kTokBlock;
+    const int t1 = imin(t0 + kTokBlock, tokens_per_rank);
+    for (int i = threadIdx.x; i < (t1 - t0) * nvec; i += blockDim.x) {
+      const int tl = t0 + i / nvec;
+      const int v = i % nvec;
+      const long long off = static_cast<long long>(tl) * n + v * 8;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int s = 0; s < world; ++s) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(stage + s * slot + off);
+        const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
+      }
+      uint4 outv;
+      T* o = reinterpret_cast<T*>(&outv);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(acc[j]);
+      *reinterpret_cast<uint4*>(out + off) = outv;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) cnt[blk] = 0;
+  }
+}
+
+}  // namespace fluxb
+
+using namespace fluxb;
+
+struct fluxb_moe_ag_scatter {
+  fluxb_comm* comm;
+  int max_ntokens, hidden, ffn_local, nexperts, topk, in_dtype, out_dtype;
+  int flag_stride;
+  uint8_t* gather[kMaxWorld];
+  int* flags[kMaxWorld];
+  void* workspace;
+  unsigned long long calls;
+  int last_parity;      // parity of the buffers the last push filled
+  int last_ntokens;     // tokens gathered by the last push
+};
+
+struct fluxb_moe_gather_rs {
+  fluxb_comm* comm;
+  int nexperts, max_m, n_dim, topk, in_dtype, out_dtype;
+  void* stage[kMaxWorld];
+  int* cnt[kMaxWorld];
+  void* workspace;
+  long long cnt_cap;
+  unsigned long long calls;
+};
+
+static int flag_stride_of(int full_m, int world) {
+  const int per_rank = (full_m + world - 1) / world;
+  return (per_rank + kBM - 1) / kBM;
+}
+
+extern "C" {
+
+// ------------------------------------------------------------------ layer 0
+size_t fluxb_moe_ag_scatter_workspace_bytes(int max_ntokens, int topk, int nexperts) {
+  return tables_bytes(static_cast<long long>(max_ntokens) * topk, nexperts);
+}
+
+int fluxb_moe_ag_scatter_create(fluxb_comm_t comm, int max_ntokens, int hidden, int ffn_local,
+                                int nexperts, int topk, int in_dtype, int out_dtype,
+                                void* const* gather_bufs, int* const* flag_bufs, void* workspace,
+                                fluxb_moe_ag_scatter_t* out) {
+  FLUXB_REQUIRE(comm != nullptr && out != nullptr && workspace != nullptr, "moe_ag_scatter_create: NULL argument");
+  FLUXB_REQUIRE(gather_bufs != nullptr && flag_bufs != nullptr, "moe_ag_scatter_create: NULL buffer table");
+  FLUXB_REQUIRE(is_16bit(in_dtype) || is_fp8(in_dtype), "moe_ag_scatter_create: input dtype %d unsupported", in_dtype);
+  FLUXB_REQUIRE(out_dtype == FLUXB_BF16 || out_dtype == FLUXB_F16, "moe_ag_scatter_create: output dtype %d unsupported", out_dtype);
+  FLUXB_REQUIRE(max_ntokens >= comm->world && max_ntokens % comm->world == 0,
+                "moe_ag_scatter_create: max_ntokens=%d must be a positive multiple of world=%d", max_ntokens, comm->world);
+  FLUXB_REQUIRE(nexperts >= 1 && nexperts <= 1024 && topk >= 1, "moe_ag_scatter_create: nexperts=%d topk=%d invalid", nexperts, topk);
+  FLUXB_REQUIRE(ffn_local % 8 == 0 && ffn_local >= 8, "moe_ag_scatter_create: ffn_local=%d must be a multiple of 8", ffn_local);
+  FLUXB_REQUIRE((static_cast<long long>(hidden) * dtype_bytes(in_dtype)) % 16 == 0,
+                "moe_ag_scatter_create: hidden=%d gives a row pitch that is not a multiple of 16 bytes", hidden);
+  fluxb_moe_ag_scatter* op = new fluxb_moe_ag_scatter();
+  memset(op, 0, sizeof(*op));
+  op->comm = comm;
+  op->max_ntokens = max_ntokens;
+  op->hidden = hidden;
+  op->ffn_local = ffn_local;
+  op->nexperts = nexperts;
+  op->topk = topk;
+  op->in_dtype = in_dtype;
+  op->out_dtype = out_dtype;
+  op->flag_stride = flag_stride_of(max_ntokens, comm->world);
+  op->workspace = workspace;
+  op->last_parity = -1;
+  for (int r = 0; r < comm->world; ++r) {
+    if (gather_bufs[r] == nullptr || flag_bufs[r] == nullptr) {
+      delete op;
+      FLUXB_FAIL(FLUXB_ERR_INVALID, "moe_ag_scatter_create: buffer of rank %d is NULL", r);
+    }
+    op->gather[r] = static_cast<uint8_t*>(gather_bufs[r]);
+    op->flags[r] = flag_bufs[r];
+  }
+  *out = op;
+  return FLUXB_OK;
+}
+
+int fluxb_moe_ag_scatter_destroy(fluxb_moe_ag_scatter_t op) {
+  delete op;
+  return FLUXB_OK;
+}
+
+// tokens_shard == NULL: reuse the tokens gathered by the previous call (further weight groups
+// of the same layer, forward_multiple_weights in the reference).
+int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_shard,
+                                 int ntokens_local, const void* weights, const int* splits_dev,
+                                 const int* scatter_index_dev, const float* out_scale, void* out,
+                                 void* gathered_out, const fluxb_tuning* tuning,
+                                 fluxb_stream_t stream_) {
+  FLUXB_REQUIRE(op != nullptr && weights != nullptr && splits_dev != nullptr && scatter_index_dev != nullptr &&
+                    out != nullptr, "moe_ag_scatter_forward: NULL argument");
+  fluxb_comm* comm = op->comm;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int world = comm->world;
+  const long long ntokens = static_cast<long long>(ntokens_local) * world;
+  FLUXB_REQUIRE(ntokens_local >= 1 && ntokens <= op->max_ntokens,
+                "moe_ag_scatter_forward: ntokens_local=%d * world=%d exceeds max_ntokens=%d", ntokens_local, world, op->max_ntokens);
+  const bool reuse = tokens_shard == nullptr;
+  FLUXB_REQUIRE(!reuse || (op->last_parity >= 0 && op->last_ntokens == ntokens_local),
+                "moe_ag_scatter_forward: no gathered tokens of this size to reuse");
+  const int eb = dtype_bytes(op->in_dtype);
+  const long long row_bytes = static_cast<long long>(op->hidden) * eb;
+  const long long rows = ntokens * op->topk;
+  const long long max_rows = static_cast<long long>(op->max_ntokens) * op->topk;
+  const int max_tiles = static_cast<int>(max_rows / kBM + op->nexperts + 1);
+
+  MoeTables tb = carve_tables(op->workspace, max_rows, op->nexperts);
+  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, op->nexperts, static_cast<int>(rows), max_tiles, tb,
+                                                comm->status_dev);
+  FLUXB_CUDA(cudaGetLastError());
+  moe_route_rows_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, stream>>>(
+      scatter_index_dev, static_cast<int>(rows), op->topk, ntokens_local, op->nexperts, tb);
+  FLUXB_CUDA(cudaGetLastError());
+
+  const size_t half_gather = (static_cast<size_t>(op->max_ntokens) + kBM) * op->hidden * eb;
+  const size_t half_flags = static_cast<size_t>(world) * op->flag_stride;
+  int parity;
+  if (reuse) {
+    parity = op->last_parity;
+  } else {
+    parity = static_cast<int>(op->calls & 1ull);
+    if (world > 1)
+      FLUXB_CUDA(cudaMemsetAsync(op->flags[comm->rank] + (parity ^ 1) * half_flags, 0, half_flags * sizeof(int), stream));
+  }
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.out_type = op->out_dtype == FLUXB_BF16 ? kOutBf16 : kOutF16;
+  p.M = static_cast<int>(rows);
+  p.N = op->ffn_local;
+  p.K = op->hidden;
+  p.nseg = world;
+  p.seg_rows = ntokens_local;
+  p.seg_first = comm->rank;
+  p.epi_mode = kEpiStore;
+  p.out = out;
+  p.ldo = op->ffn_local;
+  p.alpha = 1.0f;
+  p.g_tiles = tb.tiles;
+  p.g_num_tiles = tb.num_tiles;
+  p.g_gather = tb.gather;
+  p.g_rows_per_expert_b = op->ffn_local;
+  p.g_expert_scale = out_scale;
+  p.g_rows_per_rank = ntokens_local;
+  const uint8_t* a_base;
+  if (world == 1 && !reuse) {
+    a_base = static_cast<const uint8_t*>(tokens_shard);  // nothing to gather: read the caller's tokens in place
+  } else {
+    a_base = op->gather[comm->rank] + parity * half_gather;
+  }
+  if (world > 1 && !reuse) {
+    p.ag_flags = op->flags[comm->rank] + parity * half_flags;
+    p.ag_flag_stride = op->flag_stride;
+    p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+    p.ag_src = static_cast<const uint8_t*>(tokens_shard);
+    p.ag_row_bytes = row_bytes;
+    for (int r = 0; r < world; ++r) {
+      p.ag_dst[r] = op->gather[r] + parity * half_gather;
+      p.ag_dst_flags[r] = op->flags[r] + parity * half_flags;
+    }
+  }
+  if (world == 1 && reuse) a_base = op->gather[0] + parity * half_gather;
+  const int bn = resolve_block_n(comm, p, tuning, max_tiles);
+  int rc = encode_tmap_2d(&p.tmap_a, a_base, op->in_dtype, ntokens, op->hidden, row_bytes, 1);
+  if (rc != FLUXB_OK) return rc;
+  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * op->ffn_local,
+                      op->hidden, row_bytes, bn);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  t.block_n = bn;
+  rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
+  if (rc != FLUXB_OK) return rc;
+  if (!reuse) {
+    if (world == 1) {
+      // keep a copy so that further weight groups and `gathered_out` see the same tokens
+      FLUXB_CUDA(cudaMemcpyAsync(op->gather[0] + parity * half_gather, tokens_shard, ntokens * row_bytes,
+                                 cudaMemcpyDeviceToDevice, stream));
+    }
+    op->last_parity = parity;
+    op->last_ntokens = ntokens_local;
+    op->calls += 1;
+  }
+  if (gathered_out != nullptr)
+    FLUXB_CUDA(cudaMemcpyAsync(gathered_out, op->gather[comm->rank] + parity * half_gather, ntokens * row_bytes,
+                               cudaMemcpyDeviceToDevice, stream));
+  return FLUXB_OK;
+}
+
+// ------------------------------------------------------------------ layer 1
+size_t fluxb_moe_gather_rs_workspace_bytes(int max_m, int n_dim, int topk, int nexperts) {
+  (void)topk;
+  return align_up(static_cast<size_t>(max_m) * n_dim * 2, 256) + tables_bytes(max_m, nexperts);
+}
+size_t fluxb_moe_gather_rs_stage_bytes(int max_m, int n_dim, int topk, int world) {
+  (void)world;
+  return 2ull * (static_cast<size_t>(max_m) / topk) * n_dim * 2;
+}
+size_t fluxb_moe_gather_rs_cnt_bytes(int max_m, int topk, int world) {
+  const long long tpr = (static_cast<long long>(max_m) / topk + world - 1) / world;
+  return 2ull * ((tpr + kTokBlock - 1) / kTokBlock) * sizeof(int);
+}
+
+int fluxb_moe_gather_rs_create(fluxb_comm_t comm, int nexperts, int max_m, int n_dim, int topk,
+                               int in_dtype, int out_dtype, float* const* stage_bufs,
+                               int* const* cnt_bufs, void* workspace, fluxb_moe_gather_rs_t* out) {
+  FLUXB_REQUIRE(comm != nullptr && out != nullptr && workspace != nullptr, "moe_gather_rs_create: NULL argument");
+  FLUXB_REQUIRE(stage_bufs != nullptr && cnt_bufs != nullptr, "moe_gather_rs_create: NULL buffer table");
+  FLUXB_REQUIRE(is_16bit(in_dtype) || is_fp8(in_dtype), "moe_gather_rs_create: input dtype %d unsupported", in_dtype);
+  FLUXB_REQUIRE(out_dtype == FLUXB_BF16 || out_dtype == FLUXB_F16, "moe_gather_rs_create: output dtype %d unsupported", out_dtype);
+  FLUXB_REQUIRE(nexperts >= 1 && nexperts <= 1024 && topk >= 1, "moe_gather_rs_create: nexperts=%d topk=%d invalid", nexperts, topk);
+  // max_m % (topk * world) == 0 (src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:580-581)
+  FLUXB_REQUIRE(max_m >= topk * comm->world && max_m % (topk * comm->world) == 0,
+                "moe_gather_rs_create: max_m=%d must be a positive multiple of topk*world=%d", max_m, topk * comm->world);
+  FLUXB_REQUIRE(n_dim >= 8 && n_dim % 8 == 0, "moe_gather_rs_create: n_dim=%d must be a multiple of 8", n_dim);
+  fluxb_moe_gather_rs* op = new fluxb_moe_gather_rs();
+  memset(op, 0, sizeof(*op));
+  op->comm = comm;
+  op->nexperts = nexperts;
+  op->max_m = max_m;
+  op->n_dim = n_dim;
+  op->topk = topk;
+  op->in_dtype = in_dtype;
+  op->out_dtype = out_dtype;
+  op->workspace = workspace;
+  op->cnt_cap = static_cast<long long>(fluxb_moe_gather_rs_cnt_bytes(max_m, topk, comm->world) / (2 * sizeof(int)));
+  for (int r = 0; r < comm->world; ++r) {
+    if (stage_bufs[r] == nullptr || cnt_bufs[r] == nullptr) {
+      delete op;
+      FLUXB_FAIL(FLUXB_ERR_INVALID, "moe_gather_rs_create: buffer of rank %d is NULL", r);
+    }
+    op->stage[r] = stage_bufs[r];
+    op->cnt[r] = cnt_bufs[r];
+  }
+  *out = op;
+  return FLUXB_OK;
+}
+
+int fluxb_moe_gather_rs_destroy(fluxb_moe_gather_rs_t op) {
+  delete op;
+  return FLUXB_OK;
+}
+
+int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, int k_local,
+                                const void* weights, const int* splits_host,
+                                const int* routing_idx_dev, const float* in_scale,
+                                const float* w_scale, const float* vec_scale, void* out,
+                                const fluxb_tuning* tuning, fluxb_stream_t stream_) {
+  FLUXB_REQUIRE(op != nullptr && x != nullptr && weights != nullptr && splits_host != nullptr &&
+                    routing_idx_dev != nullptr && out != nullptr, "moe_gather_rs_forward: NULL argument");
+  fluxb_comm* comm = op->comm;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  const int world = comm->world;
+  const int topk = op->topk;
+  const int n = op->n_dim;
+  FLUXB_REQUIRE(m >= topk * world && m <= op->max_m && m % (topk * world) == 0,
+                "moe_gather_rs_forward: m=%d must be a multiple of topk*world=%d within max_m=%d", m, topk * world, op->max_m);
+  const int eb = dtype_bytes(op->in_dtype);
+  FLUXB_REQUIRE(k_local >= 8 && (static_cast<long long>(k_local) * eb) % 16 == 0,
+                "moe_gather_rs_forward: k_local=%d gives a row pitch that is not a multiple of 16 bytes", k_local);
+  const int ntokens = m / topk;
+  const int tpr = ntokens / world;
+
+  // tile table from the host-side splits (the reference also packs its problem list on the host
+  // and uploads it, gemm_grouped_v3_gather_rs.cc:245-416)
+  std::vector<GroupTile> tiles;
+  long long off = 0;
+  for (int e = 0; e < op->nexperts; ++e) {
+    const int cnt = splits_host[e];
+    FLUXB_REQUIRE(cnt >= 0, "moe_gather_rs_forward: splits[%d]=%d is negative", e, cnt);
+    for (int c = 0; c * kBM < cnt; ++c) {
+      GroupTile g;
+      g.a_row0 = static_cast<int>(off) + c * kBM;
+      g.rows = cnt - c * kBM < kBM ? cnt - c * kBM : kBM;
+      g.expert = e;
+      g.need_mask = 0;
+      tiles.push_back(g);
+    }
+    off += cnt;
+  }
+  FLUXB_REQUIRE(off == m, "moe_gather_rs_forward: splits sum to %lld, expected m=%d", off, m);
+  uint8_t* ws = static_cast<uint8_t*>(op->workspace);
+  void* inter = ws;
+  MoeTables tb = carve_tables(ws + align_up(static_cast<size_t>(op->max_m) * n * 2, 256), op->max_m, op->nexperts);
+  const int num_tiles = static_cast<int>(tiles.size());
+  FLUXB_CUDA(cudaMemcpyAsync(tb.tiles, tiles.data(), tiles.size() * sizeof(GroupTile), cudaMemcpyHostToDevice, stream));
+  FLUXB_CUDA(cudaMemcpyAsync(tb.num_tiles, &num_tiles, sizeof(int), cudaMemcpyHostToDevice, stream));
+
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.out_type = op->out_dtype == FLUXB_BF16 ? kOutBf16 : kOutF16;
+  p.M = m;
+  p.N = n;
+  p.K = k_local;
+  p.nseg = 1;
+  p.seg_rows = m;
+  p.epi_mode = kEpiStore;
+  p.out = inter;
+  p.ldo = n;
+  p.alpha = 1.0f;
+  // scales follow python/flux/testing/moe_gather_rs_utils.py:76-79,99: weight_scale[e] * input_scale, then the row vector
+  p.alpha_ptr = (in_scale != nullptr && w_scale != nullptr) ? in_scale : nullptr;
+  p.g_expert_scale = (in_scale != nullptr && w_scale != nullptr) ? w_scale : nullptr;
+  p.scale_a = vec_scale;
+  p.g_tiles = tb.tiles;
+  p.g_num_tiles = tb.num_tiles;
+  p.g_gather = nullptr;
+  p.g_rows_per_expert_b = n;
+  const long long row_bytes = static_cast<long long>(k_local) * eb;
+  const int bn = resolve_block_n(comm, p, tuning, num_tiles > 0 ? num_tiles : 1);
+  int rc = encode_tmap_2d(&p.tmap_a, x, op->in_dtype, m, k_local, row_bytes, kBM);
+  if (rc != FLUXB_OK) return rc;
+  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * n, k_local, row_bytes, bn);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  t.block_n = bn;
+  rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
+  if (rc != FLUXB_OK) return rc;
+
+  const int parity = static_cast<int>(op->calls & 1ull);
+  const size_t half_stage_elems = (static_cast<size_t>(op->max_m) / topk) * n;
+  PushTargets tg;
+  memset(&tg, 0, sizeof(tg));
+  for (int r = 0; r < world; ++r) {
+    tg.stage[r] = static_cast<uint8_t*>(op->stage[r]) +
+                  (parity * half_stage_elems + static_cast<size_t>(comm->rank) * tpr * n) * 2;
+    tg.cnt[r] = op->cnt[r] + parity * op->cnt_cap;
+  }
+  const int blocks_per_owner = (tpr + kTokBlock - 1) / kTokBlock;
+  int pgrid = world * blocks_per_owner;
+  if (pgrid > 4 * comm->sm_count) pgrid = 4 * comm->sm_count;
+  int rgrid = blocks_per_owner < 2 * comm->sm_count ? blocks_per_owner : 2 * comm->sm_count;
+  const void* local_stage = static_cast<uint8_t*>(op->stage[comm->rank]) + parity * half_stage_elems * 2;
+  int* local_cnt = op->cnt[comm->rank] + parity * op->cnt_cap;
+  if (op->out_dtype == FLUXB_BF16) {
+    moe_topk_push_kernel<__nv_bfloat16><<<pgrid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(inter), routing_idx_dev, topk, n, tpr, comm->rank, world, tg);
+    FLUXB_CUDA(cudaGetLastError());
+    moe_rs_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(local_stage), local_cnt, static_cast<__nv_bfloat16*>(out), n, tpr, world,
+        comm->status_dev, comm->timeout_ns);
+  } else {
+    moe_topk_push_kernel<__half><<<pgrid, 256, 0, stream>>>(static_cast<const __half*>(inter), routing_idx_dev, topk,
+                                                           n, tpr, comm->rank, world, tg);
+    FLUXB_CUDA(cudaGetLastError());
+    moe_rs_reduce_kernel<__half><<<rgrid, 256, 0, stream>>>(static_cast<const __half*>(local_stage), local_cnt,
+                                                           static_cast<__half*>(out), n, tpr, world, comm->status_dev,
+                                                           comm->timeout_ns);
+  }
+  FLUXB_CUDA(cudaGetLastError());
+  op->calls += 1;
+  return FLUXB_OK;
+}
+
+}  // extern "C"

@@ -160,6 +160,7 @@ class Comm:
 
 
 _COMMS: Dict[int, Comm] = {}
+_LAST: List[Comm] = []
 
 
 def get_comm(group) -> Comm:
@@ -168,7 +169,16 @@ def get_comm(group) -> Comm:
     if c is None:
         c = Comm(group)
         _COMMS[key] = c
+    _LAST[:] = [c]
     return c
+
+
+def default_comm() -> Comm:
+    """Communicator of the most recent `init_flux_shm` / `get_comm` call (ops whose constructor takes
+    no process group bind to it, as the reference binds to its global NVSHMEM state)."""
+    if not _LAST:
+        raise RuntimeError("call flux.init_flux_shm(process_group) first")
+    return _LAST[0]
 
 
 def init_flux_shm(pg) -> None:

@@ -75,3 +75,56 @@ def gemm_rs_case(rank, world, shapes, dtype_name, with_bias, tuning):
         comm.check_status()
         err = golden.max_rel_err(out, ref)
         assert err <= 1e-2, f"rank {rank} call {it} shape {(m, n, k_local)}: max rel err {err}"
+
+
+def moe_case(rank, world, cfgs, dtype_name):
+    """MoE layer 0 (AG + scatter + grouped GEMM) and layer 1 (grouped GEMM + gather + RS) vs the gloo oracle."""
+    import flux_b200 as flux
+    from oracle import golden
+
+    dtype = getattr(torch, dtype_name)
+    group = dist.group.WORLD
+    flux.init_flux_shm(group)
+    comm = flux.get_comm(group)
+    comm.set_timeout_ms(5000)
+    for ci, (ntokens, topk, nexperts, hidden, ffn, calls) in enumerate(cfgs):
+        ffn_local = ffn // world
+        env = flux.DistEnvTPWithEP(group, 1, None)
+        margs = flux.MoeArguments(ntokens, hidden, ffn, nexperts, topk, dtype)
+        l0 = flux.GemmGroupedV3AGScatter(env, margs)
+        l1 = flux.GemmGroupedV3GatherRS(nexperts, ntokens * topk, hidden, topk, rank, world, world, 1, input_dtype=dtype)
+        for it in range(calls):
+            g = torch.Generator().manual_seed(1234 + 31 * ci + it)  # routing is global: same seed on every rank
+            logits = torch.randn(ntokens, nexperts, generator=g)
+            if it == 1:
+                logits[:, 0] = -1e9  # an expert that receives no tokens
+            chosen, rw = golden.topk_routing(logits, topk)
+            si = golden.calc_scatter_index_stable(chosen)
+            splits = golden.calc_splits(chosen, nexperts)
+            gi, ti = golden.calc_gather_index(si)
+            gr = torch.Generator().manual_seed(999 + rank + 7 * it)
+            tok = torch.randn(ntokens // world, hidden, generator=gr).to(dtype)
+            w0 = (torch.randn(nexperts, ffn_local, hidden, generator=gr) * 0.02).to(dtype)
+            w1 = (torch.randn(nexperts, hidden, ffn_local, generator=gr) * 0.02).to(dtype)
+            oscale = torch.rand(nexperts, generator=gr) + 0.5
+            # ---- layer 0
+            shards = [torch.empty_like(tok) for _ in range(world)]
+            dist.all_gather(shards, tok, group=group)
+            ref0, ref_g = golden.moe_ag_scatter_single(shards, w0, splits, si, oscale)
+            gathered = torch.empty((ntokens, hidden), dtype=dtype, device="cuda")
+            out0 = l0.forward(tok.cuda(), w0.cuda(), splits.cuda(), si.cuda(), output_scale=oscale.cuda(),
+                              allgather_output=gathered)
+            torch.cuda.synchronize()
+            comm.check_status()
+            err0 = golden.max_rel_err(out0, ref0)
+            assert err0 <= 1e-2, f"rank {rank} cfg {ci} call {it}: layer 0 max rel err {err0}"
+            assert torch.equal(gathered.cpu().view(torch.int16), ref_g.view(torch.int16))
+            # ---- layer 1 (input = the oracle's layer-0 output so that errors do not compound)
+            vec = rw.reshape(-1)[(gi.long() * topk + ti.long())].contiguous()
+            ref1 = golden.moe_gather_rs_dist(group, ref0, w1, splits, si, topk, output_vec_scale=vec)
+            out1 = l1.forward_gather_rs(ref0.cuda(), w1.cuda(), splits, si.reshape(-1).cuda(), output_vec_scale=vec.cuda())
+            torch.cuda.synchronize()
+            comm.check_status()
+            # tolerance of the reference's own test for bf16 (test_moe_gather_rs.py:397-411): 2e-2
+            err1 = golden.max_rel_err(out1, ref1)
+            assert err1 <= 2e-2, f"rank {rank} cfg {ci} call {it}: layer 1 max rel err {err1}"
