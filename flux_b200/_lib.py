@@ -36,7 +36,7 @@ STATUS_NAMES = {
 
 
 class Tuning(C.Structure):
-    _fields_ = [("block_n", C.c_int), ("group_m", C.c_int), ("num_ctas", C.c_int), ("reserved", C.c_int)]
+    _fields_ = [("block_n", C.c_int), ("group_m", C.c_int), ("num_ctas", C.c_int), ("cta_group", C.c_int)]
 
 
 class FluxbError(RuntimeError):

@@ -21,6 +21,12 @@
 //
 // Warp roles (320 threads): warp 0 TMA producer, warp 1 UMMA issuer + TMEM
 // owner, warps 2-5 epilogue (one TMEM lane quadrant each), warps 6-9 comm.
+//
+// Two tile shapes: one CTA per 128 x BN tile (cta_group::1), or a CTA pair
+// (cluster of 2) per 256 x BN tile (cta_group::2): each CTA of the pair loads
+// its own 128 rows of A and half of the B tile, the even CTA issues the UMMAs
+// for both, each CTA drains its own 128 accumulator rows. The pair form needs
+// a third less operand traffic per flop and buys two more pipeline stages.
 #pragma once
 #include <cuda.h>
 #include <cuda_bf16.h>
@@ -94,38 +100,46 @@ struct GemmParams {
   const float* g_expert_scale;  // optional per-expert alpha
   const int* g_scatter_rows;    // optional: sorted row -> output row (null = identity)
   int g_rows_per_rank;          // tokens per source rank (for need_mask -> flags)
+  int g_ntokens;                // rows of the gathered A matrix
   // status / bounded waits
   int* status;
   unsigned long long timeout_ns;
 };
 
-template <int BN, int STAGES>
+template <int BN, int STAGES, bool CTA2>
 struct SmemLayout {
   static constexpr int kABytes = kBM * kRowBytes;
-  static constexpr int kBBytes = BN * kRowBytes;
+  static constexpr int kBRows = CTA2 ? BN / 2 : BN;
+  static constexpr int kBBytes = kBRows * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  static constexpr int kBarOffset = STAGES * kStageBytes;
+  // epilogue staging: per epilogue warp 32 rows x (32 fp32 + 16 B pad)
+  static constexpr int kEpiPitch = 144;
+  static constexpr int kEpiWarpBytes = 32 * kEpiPitch;
+  static constexpr int kEpiOffset = STAGES * kStageBytes;
+  static constexpr int kBarOffset = kEpiOffset + 4 * kEpiWarpBytes;
   static constexpr int kNumBars = 2 * STAGES + 4;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kTotal = kMiscOffset + 64 + 1024;  // + slack for 1024-byte alignment
 };
 
 struct TileCoord {
-  int row0;        // first A row (global row, or sorted row in grouped mode)
-  int rows;        // valid rows
+  int row0;        // first A row of THIS CTA (global row, or sorted row in grouped mode)
+  int rows;        // valid rows of this CTA (0..128)
   int n0;          // first output column
   int seg, chunk;  // segment and 128-row chunk inside it (dense)
-  int b_row0;      // first B row
+  int b_row0;      // first B row of the tile
   int n_idx;
   int need_mask;
   int expert;
 };
 
 __device__ __forceinline__ int imin(int a, int b) { return a < b ? a : b; }
+__device__ __forceinline__ int imax(int a, int b) { return a > b ? a : b; }
 
-template <int BN>
+// TILE_M = 128 (one CTA) or 256 (CTA pair, `half` = rank of this CTA inside the pair)
+template <int BN, int TILE_M>
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_tiles, int n_tiles,
-                                            int tps, TileCoord& tc) {
+                                            int tps, int half, TileCoord& tc) {
   const int gmn = p.group_m * n_tiles;
   const int band = t / gmn;
   const int r = t - band * gmn;
@@ -139,10 +153,11 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_ti
     const int c = m_idx - sp * tps;
     int seg = p.seg_first + sp;
     if (seg >= p.nseg) seg -= p.nseg;
+    const int off = c * TILE_M + half * kBM;  // row offset inside the segment
     tc.seg = seg;
-    tc.chunk = c;
-    tc.row0 = seg * p.seg_rows + c * kBM;
-    tc.rows = imin(kBM, p.seg_rows - c * kBM);
+    tc.chunk = off / kBM;
+    tc.row0 = seg * p.seg_rows + off;
+    tc.rows = imax(0, imin(kBM, p.seg_rows - off));
     tc.b_row0 = tc.n0;
     tc.need_mask = 0;
     tc.expert = 0;
@@ -150,8 +165,8 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_ti
     const GroupTile g = p.g_tiles[m_idx];
     tc.seg = 0;
     tc.chunk = m_idx;
-    tc.row0 = g.a_row0;
-    tc.rows = g.rows;
+    tc.row0 = g.a_row0 + half * kBM;
+    tc.rows = imax(0, imin(kBM, g.rows - half * kBM));
     tc.expert = g.expert;
     tc.b_row0 = g.expert * p.g_rows_per_expert_b + tc.n0;
     tc.need_mask = g.need_mask;
@@ -167,17 +182,20 @@ __device__ __forceinline__ uint32_t pack_f16(float a, float b) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// KIND: 0 = 16-bit inputs (bf16/f16 chosen by `ab_format`), 1 = fp8
-template <int BN, int STAGES, int KIND>
+// KIND: 0 = 16-bit inputs (bf16/f16 chosen by the instruction descriptor), 1 = fp8
+// CTA2: false = one CTA per 128-row tile, true = CTA pair per 256-row tile (launch with cluster 2x1x1)
+template <int BN, int STAGES, int KIND, bool CTA2>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, CTA2>;
   constexpr int ELT = (KIND == 0) ? 2 : 1;
-  constexpr int BKE = kRowBytes / ELT;            // K elements per stage
+  constexpr int BKE = kRowBytes / ELT;  // K elements per stage
+  constexpr int TILE_M = CTA2 ? 2 * kBM : kBM;
   constexpr uint32_t TMEM_COLS = (2 * BN <= 32) ? 32 : (2 * BN <= 64) ? 64 : (2 * BN <= 128) ? 128
                                  : (2 * BN <= 256) ? 256 : 512;
   static_assert(2 * BN <= 512, "two accumulators must fit in tensor memory");
   static_assert(BN % 32 == 0, "epilogue reads 32 columns at a time");
+  static_assert(L::kTotal <= 232448, "shared memory budget exceeded");
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -198,6 +216,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const uint64_t budget = p.timeout_ns;
+  const int half = CTA2 ? static_cast<int>(cluster_ctarank()) : 0;  // rank inside the CTA pair
+  const bool leader = half == 0;
+  const int tile_first = CTA2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
+  const int tile_step = CTA2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
   if (threadIdx.x == 0) {
     *s_abort = 0;
@@ -207,25 +229,30 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull(a), 1);
-      mbar_init(bar_tempty(a), 4);
+      mbar_init(bar_tempty(a), CTA2 ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
     }
     mbar_init_fence();
     tma_prefetch_desc(&p.tmap_a);
     tma_prefetch_desc(&p.tmap_b);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
-    tmem_relinquish();
+    if (CTA2) {
+      tmem_alloc_2cta(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish_2cta();
+    } else {
+      tmem_alloc(smem_u32(tmem_holder), TMEM_COLS);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
-  __syncthreads();
+  if (CTA2) cluster_sync_all(); else __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
 
   const int n_tiles = (p.N + BN - 1) / BN;
   int tps = 1, m_tiles;
   if (p.g_tiles == nullptr) {
-    tps = (p.seg_rows + kBM - 1) / kBM;
+    tps = (p.seg_rows + TILE_M - 1) / TILE_M;
     m_tiles = p.nseg * tps;
   } else {
     m_tiles = *p.g_num_tiles;
@@ -239,13 +266,14 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x) {
+      for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
         TileCoord tc;
-        decode_tile<BN>(p, t, m_tiles, n_tiles, tps, tc);
+        decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
         if (p.ag_flags != nullptr) {
           if (p.g_tiles == nullptr) {
-            ok = flag_wait_eq(p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk, p.ag_expected,
-                              s_abort, kStatusTimeoutFlag, budget);
+            if (tc.rows > 0)
+              ok = flag_wait_eq(p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk, p.ag_expected,
+                                s_abort, kStatusTimeoutFlag, budget);
           } else {
             // grouped: wait for every chunk of every source rank the tile touches
             const int chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
@@ -264,23 +292,36 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             ok = false;
             break;
           }
-          mbar_arrive_expect_tx(bar_full(stage), L::kStageBytes);
-          if (p.g_gather == nullptr) {
-            tma_load_2d(smem_a(stage), &p.tmap_a, bar_full(stage), kb * BKE, tc.row0);
+          // Pair mode: both CTAs' copies are credited to the leader's barrier, which the leader
+          // arms for the bytes of both.
+          uint32_t fb = bar_full(stage);
+          if (CTA2) {
+            if (leader) mbar_arrive_expect_tx(fb, 2 * L::kStageBytes);
+            fb = mapa_u32(fb, 0);
           } else {
-            // 32 gather4 copies of 4 rows each; rows past the tile end re-read row 0 of the tile
-            const int* gi = p.g_gather + tc.row0;
+            mbar_arrive_expect_tx(fb, L::kStageBytes);
+          }
+          if (p.g_gather == nullptr) {
+            if (CTA2) tma_load_2d_2cta(smem_a(stage), &p.tmap_a, fb, kb * BKE, tc.row0);
+            else tma_load_2d(smem_a(stage), &p.tmap_a, fb, kb * BKE, tc.row0);
+          } else {
+            // 32 gather4 copies of 4 rows each; rows past the tile end re-read a valid row
+            const int* gi = p.g_gather + (tc.rows > 0 ? tc.row0 : 0);
+            const int nr = tc.rows > 0 ? tc.rows : 1;
             for (int q = 0; q < kBM / 4; ++q) {
               const int r0 = q * 4;
-              const int i0 = gi[r0 < tc.rows ? r0 : 0];
-              const int i1 = gi[r0 + 1 < tc.rows ? r0 + 1 : 0];
-              const int i2 = gi[r0 + 2 < tc.rows ? r0 + 2 : 0];
-              const int i3 = gi[r0 + 3 < tc.rows ? r0 + 3 : 0];
-              tma_gather4_2d(smem_a(stage) + q * 4 * kRowBytes, &p.tmap_a, bar_full(stage),
-                             kb * BKE, i0, i1, i2, i3);
+              const int i0 = gi[r0 < nr ? r0 : 0];
+              const int i1 = gi[r0 + 1 < nr ? r0 + 1 : 0];
+              const int i2 = gi[r0 + 2 < nr ? r0 + 2 : 0];
+              const int i3 = gi[r0 + 3 < nr ? r0 + 3 : 0];
+              if (CTA2)
+                tma_gather4_2d_2cta(smem_a(stage) + q * 4 * kRowBytes, &p.tmap_a, fb, kb * BKE, i0, i1, i2, i3);
+              else
+                tma_gather4_2d(smem_a(stage) + q * 4 * kRowBytes, &p.tmap_a, fb, kb * BKE, i0, i1, i2, i3);
             }
           }
-          tma_load_2d(smem_b(stage), &p.tmap_b, bar_full(stage), kb * BKE, tc.b_row0);
+          if (CTA2) tma_load_2d_2cta(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0 + half * (BN / 2));
+          else tma_load_2d(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0);
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -290,12 +331,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------------- UMMA
-    if (lane == 0) {
+    if (lane == 0 && leader) {
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = blockIdx.x; ok && t < total_tiles; t += gridDim.x, ++it) {
+      for (int t = tile_first; ok && t < total_tiles; t += tile_step, ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(bar_tempty(acc), acc_phase ^ 1u, s_abort, kStatusTimeoutTmemEmpty, budget))
@@ -314,30 +355,36 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           for (int k = 0; k < 4; ++k) {
             // each UMMA consumes 32 bytes of K: advance the start address by 32 B (>>4 = 2)
             const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-            if (KIND == 0)
-              umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
-            else
-              umma_f8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+            if (CTA2) {
+              if (KIND == 0) umma_f16_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+              else umma_f8_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+            } else {
+              if (KIND == 0) umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+              else umma_f8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+            }
           }
-          umma_commit(bar_empty(stage));
+          if (CTA2) umma_commit_2cta(bar_empty(stage), 3); else umma_commit(bar_empty(stage));
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
           }
         }
-        if (ok) umma_commit(bar_tfull(acc));
+        if (ok) {
+          if (CTA2) umma_commit_2cta(bar_tfull(acc), 3); else umma_commit(bar_tfull(acc));
+        }
       }
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------- epilogue
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
+    const uint32_t stage_row = smem_base + L::kEpiOffset + (warp - 2) * L::kEpiWarpBytes + lane * L::kEpiPitch;
     int it = 0;
-    for (int t = blockIdx.x; t < total_tiles; t += gridDim.x, ++it) {
+    for (int t = tile_first; t < total_tiles; t += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       TileCoord tc;
-      decode_tile<BN>(p, t, m_tiles, n_tiles, tps, tc);
+      decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
       if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget)) break;
       tc_fence_after();
       const bool row_ok = row_in_tile < tc.rows;
@@ -375,16 +422,16 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         tmem_ld_32x32(taddr, r);
         tmem_ld_wait();
         const int col0 = tc.n0 + c * 32;
-        if (row_ok && col0 < p.N) {
+        const bool active = row_ok && col0 < p.N;
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_scale;
-        if (p.scale_b != nullptr) {
+        if (active && p.scale_b != nullptr) {
 #pragma unroll
           for (int j = 0; j < 32; ++j)
             if (col0 + j < p.N) v[j] *= p.scale_b[col0 + j];
         }
-        if (bias_row != nullptr) {
+        if (active && bias_row != nullptr) {
           // bias has the output dtype in store mode, bf16 in reduce-scatter mode
           const int bt = (p.epi_mode == kEpiStore) ? p.out_type : kOutBf16;
 #pragma unroll
@@ -401,49 +448,70 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             }
           }
         }
-        if (p.epi_mode == kEpiRsPush || p.out_type == kOutF32) {
-          float* d = reinterpret_cast<float*>(dst_row) + col0;
+        if (p.epi_mode == kEpiRsPush) {
+          // Each lane owns one row: park its 32 fp32 values in shared memory and push them to the
+          // owner as one 128-byte bulk copy (a full NVLink payload instead of eight 16-byte stores).
+          bulk_wait_read();  // the previous copy out of this lane's staging row has been read
+          if (active) {
 #pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            if (col0 + q * 4 + 4 <= p.N) {
-              *reinterpret_cast<float4*>(d + q * 4) =
-                  make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
-            } else {
+            for (int q = 0; q < 8; ++q)
+              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + q * 16), "f"(v[q * 4]),
+                           "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                           : "memory");
+            fence_proxy_async_smem();
+            const int ncols = imin(32, p.N - col0);
+            bulk_store(reinterpret_cast<float*>(dst_row) + col0, stage_row, static_cast<uint32_t>(ncols) * 4u);
+          }
+          bulk_commit();
+        } else if (active) {
+          if (p.out_type == kOutF32) {
+            float* d = reinterpret_cast<float*>(dst_row) + col0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              if (col0 + q * 4 + 4 <= p.N) {
+                *reinterpret_cast<float4*>(d + q * 4) =
+                    make_float4(v[q * 4], v[q * 4 + 1], v[q * 4 + 2], v[q * 4 + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  if (col0 + q * 4 + j < p.N) d[q * 4 + j] = v[q * 4 + j];
+              }
+            }
+          } else {
+            uint16_t* d = reinterpret_cast<uint16_t*>(dst_row) + col0;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              uint32_t w[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                if (col0 + q * 4 + j < p.N) d[q * 4 + j] = v[q * 4 + j];
-            }
-          }
-        } else {
-          uint16_t* d = reinterpret_cast<uint16_t*>(dst_row) + col0;
+                w[j] = (p.out_type == kOutBf16) ? pack_bf16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1])
+                                                : pack_f16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+              if (col0 + q * 8 + 8 <= p.N) {
+                *reinterpret_cast<uint4*>(d + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
+              } else {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint32_t w[4];
-#pragma unroll
-            for (int j = 0; j < 4; ++j)
-              w[j] = (p.out_type == kOutBf16) ? pack_bf16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1])
-                                              : pack_f16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
-            if (col0 + q * 8 + 8 <= p.N) {
-              *reinterpret_cast<uint4*>(d + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j)
-                if (col0 + q * 8 + j < p.N)
-                  d[q * 8 + j] = static_cast<uint16_t>((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xFFFFu));
+                for (int j = 0; j < 8; ++j)
+                  if (col0 + q * 8 + j < p.N)
+                    d[q * 8 + j] = static_cast<uint16_t>((j & 1) ? (w[j >> 1] >> 16) : (w[j >> 1] & 0xFFFFu));
+              }
             }
           }
         }
-        }  // row_ok && col0 < N
         __syncwarp();
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar_tempty(acc));
+      if (lane == 0) {
+        if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
+        else mbar_arrive(bar_tempty(acc));
+      }
       if (p.epi_mode == kEpiRsPush) {
-        // this warp's 32 rows of the tile are stored: publish them to the owner. Each of
-        // the four epilogue warps adds 1, so a complete tile counts 4 per source rank.
-        // (No CTA-wide barrier here: a role that gave up must never strand the others.)
-        if (lane == 0) {
+        // This warp's 32 rows of the tile are on their way: wait until the copies are complete, then
+        // publish them to the owner. Each epilogue warp adds 1, so a complete 128-row tile counts 4
+        // per source rank. (No CTA-wide barrier here: a role that gave up must never strand the others.)
+        bulk_wait_all();
+        __syncwarp();
+        if (lane == 0 && tc.rows > 0) {
           fence_acq_rel_sys();
           red_add_release_sys(p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx, 1);
         }
@@ -503,7 +571,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   }
 
   // ------------------------------------------------------------------ teardown
-  __syncthreads();
+  if (CTA2) cluster_sync_all(); else __syncthreads();
   const int err = *s_abort;
   if (err != 0) {
     if (threadIdx.x == 0) {
@@ -512,12 +580,11 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     }
     // let copies and MMAs that are still in flight land before the CTA's memory goes away
     __nanosleep(200000);
-    __syncthreads();
   }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
+    if (CTA2) tmem_dealloc_2cta(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 

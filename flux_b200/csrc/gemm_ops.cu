@@ -9,20 +9,46 @@ namespace fluxb {
 // ---------------------------------------------------------------------------
 // launcher
 // ---------------------------------------------------------------------------
-template <int BN, int STAGES, int KIND>
-static int launch_inst(const GemmParams& p, uint32_t idesc, int grid, cudaStream_t stream) {
-  using L = SmemLayout<BN, STAGES>;
-  static_assert(L::kTotal <= 232448, "shared memory budget exceeded");
-  auto kern = fused_gemm_kernel<BN, STAGES, KIND>;
+template <int BN, int STAGES, int KIND, bool CTA2>
+static int launch_inst(const fluxb_comm* comm, const GemmParams& p, uint32_t idesc, int grid, cudaStream_t stream) {
+  using L = SmemLayout<BN, STAGES, CTA2>;
+  auto kern = fused_gemm_kernel<BN, STAGES, KIND, CTA2>;
   static bool configured[64] = {};
+  static int max_clusters[64] = {};
   int dev = 0;
   FLUXB_CUDA(cudaGetDevice(&dev));
-  if (dev < 64 && !configured[dev]) {
+  FLUXB_REQUIRE(dev < 64, "device index %d not supported", dev);
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = CTA2 ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  if (!configured[dev]) {
     FLUXB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    if (CTA2) {
+      // how many CTA pairs can be resident at once: the persistent grid must not exceed it
+      cfg.gridDim = dim3(comm->sm_count & ~1, 1, 1);
+      int n = 0;
+      FLUXB_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      FLUXB_REQUIRE(n >= 1, "no CTA pair of the fused kernel fits on this device");
+      max_clusters[dev] = n;
+    }
     configured[dev] = true;
   }
-  kern<<<grid, kThreads, L::kTotal, stream>>>(p, idesc);
-  FLUXB_CUDA(cudaGetLastError());
+  if (CTA2) {
+    grid &= ~1;
+    if (grid > 2 * max_clusters[dev]) grid = 2 * max_clusters[dev];
+    if (grid < 2) grid = 2;
+  }
+  cfg.gridDim = dim3(grid, 1, 1);
+  FLUXB_CUDA(cudaLaunchKernelEx(&cfg, kern, p, idesc));
   return FLUXB_OK;
 }
 
@@ -47,27 +73,38 @@ static int pick_block_n(long long m_tiles, int n, int ctas) {
   return best;
 }
 
+int resolve_cta_group(const GemmParams& p, const fluxb_tuning* tuning) {
+  if (tuning != nullptr && (tuning->cta_group == 1 || tuning->cta_group == 2)) return tuning->cta_group;
+  if (p.g_tiles != nullptr) return 1;
+  // a CTA pair works on 256 rows of one segment: worth it once segments are at least that tall
+  return p.seg_rows >= 256 ? 2 : 1;
+}
+
 int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tuning* tuning,
                     long long m_tiles_hint) {
   int bn = (tuning != nullptr) ? tuning->block_n : 0;
   if (bn == 0) {
+    const int cg = resolve_cta_group(p, tuning);
+    const int tile_m = cg == 2 ? 2 * kBM : kBM;
     long long m_tiles = m_tiles_hint;
-    if (m_tiles <= 0) m_tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + kBM - 1) / kBM);
+    if (m_tiles <= 0) m_tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + tile_m - 1) / tile_m);
     int ctas = (tuning != nullptr && tuning->num_ctas > 0) ? tuning->num_ctas : comm->sm_count;
-    bn = pick_block_n(m_tiles, p.N, ctas);
+    bn = pick_block_n(m_tiles, p.N, cg == 2 ? ctas / 2 : ctas);
   }
   return bn;
 }
 
 int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
                       const fluxb_tuning* tuning, cudaStream_t stream) {
+  const int cg = resolve_cta_group(p, tuning);
   const int bn = resolve_block_n(comm, p, tuning, p.g_tiles != nullptr ? 1024 : 0);
   FLUXB_REQUIRE(bn == 64 || bn == 128 || bn == 192 || bn == 256, "block_n=%d not in {64,128,192,256}", bn);
   int grid = comm->sm_count;
   if (tuning != nullptr && tuning->num_ctas > 0) grid = tuning->num_ctas < grid ? tuning->num_ctas : grid;
   if (p.g_tiles == nullptr) {
-    const long long tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + kBM - 1) / kBM) *
-                            ((p.N + bn - 1) / bn);
+    const int tile_m = cg == 2 ? 2 * kBM : kBM;
+    const long long tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + tile_m - 1) / tile_m) *
+                            ((p.N + bn - 1) / bn) * (cg == 2 ? 2 : 1);
     // the all-gather push is spread over every CTA's comm warps, so keep the full grid there
     if (p.ag_src == nullptr && tiles < grid) grid = static_cast<int>(tiles);
   }
@@ -86,15 +123,17 @@ int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
     case FLUXB_E5M2: fmt = 1; break;
     default: FLUXB_FAIL(FLUXB_ERR_INVALID, "input dtype %d is not bf16/f16/e4m3/e5m2", in_dtype);
   }
-  const uint32_t idesc = make_idesc(fmt, kBM, static_cast<uint32_t>(bn));
-#define FLUXB_LAUNCH(BN_, ST_)                                               \
-  (kind == 0 ? launch_inst<BN_, ST_, 0>(p, idesc, grid, stream)              \
-             : launch_inst<BN_, ST_, 1>(p, idesc, grid, stream))
+  const uint32_t idesc = make_idesc(fmt, cg == 2 ? 2 * kBM : kBM, static_cast<uint32_t>(bn));
+#define FLUXB_LAUNCH(BN_, ST1_, ST2_)                                                              \
+  (cg == 2 ? (kind == 0 ? launch_inst<BN_, ST2_, 0, true>(comm, p, idesc, grid, stream)            \
+                        : launch_inst<BN_, ST2_, 1, true>(comm, p, idesc, grid, stream))           \
+           : (kind == 0 ? launch_inst<BN_, ST1_, 0, false>(comm, p, idesc, grid, stream)           \
+                        : launch_inst<BN_, ST1_, 1, false>(comm, p, idesc, grid, stream)))
   switch (bn) {
-    case 256: return FLUXB_LAUNCH(256, 4);
-    case 192: return FLUXB_LAUNCH(192, 5);
-    case 128: return FLUXB_LAUNCH(128, 6);
-    default: return FLUXB_LAUNCH(64, 8);
+    case 256: return FLUXB_LAUNCH(256, 4, 6);
+    case 192: return FLUXB_LAUNCH(192, 5, 7);
+    case 128: return FLUXB_LAUNCH(128, 6, 8);
+    default: return FLUXB_LAUNCH(64, 8, 8);
   }
 #undef FLUXB_LAUNCH
 }
@@ -246,7 +285,8 @@ int fluxb_gemm(fluxb_comm_t comm, const void* a, const void* b, void* c, int m, 
   const int bn = resolve_block_n(comm, p, tuning, 0);
   rc = encode_tmap_2d(&p.tmap_a, a, in_dtype, m, k, static_cast<long long>(k) * eb, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, b, in_dtype, n, k, static_cast<long long>(k) * eb, bn);
+  rc = encode_tmap_2d(&p.tmap_b, b, in_dtype, n, k, static_cast<long long>(k) * eb,
+                      resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;
@@ -378,7 +418,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   uint8_t* local_gather = op->gather[comm->rank] + parity * half_gather;
   rc = encode_tmap_2d(&p.tmap_a, local_gather, op->in_dtype, m, k, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k, row_bytes, bn);
+  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k, row_bytes, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;
@@ -493,7 +533,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   const long long row_bytes = static_cast<long long>(k_local) * eb;
   rc = encode_tmap_2d(&p.tmap_a, a, op->in_dtype, m, k_local, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k_local, row_bytes, bn);
+  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k_local, row_bytes, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;

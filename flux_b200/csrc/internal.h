@@ -76,6 +76,9 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elt_dtype, long long 
 int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tuning* tuning,
                     long long m_tiles_hint);
 
+// 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile (the caller's choice or a heuristic).
+int resolve_cta_group(const GemmParams& p, const fluxb_tuning* tuning);
+
 // Fill the problem-independent fields and launch the fused kernel.
 int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
                       const fluxb_tuning* tuning, cudaStream_t stream);

@@ -61,7 +61,7 @@ static MoeTables carve_tables(void* ws, long long max_rows, int nexperts) {
 // One block. Prefix sums over the experts, then each expert writes its tiles.
 __global__ void __launch_bounds__(1024)
 moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_rows, int max_tiles,
-                       MoeTables t, int* status) {
+                       int tile_m, MoeTables t, int* status) {
   __shared__ int ok;
   if (threadIdx.x == 0) {
     int off = 0, tb = 0;
@@ -70,7 +70,7 @@ moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_r
       t.tile_base[e] = tb;
       const int n = splits[e] < 0 ? 0 : splits[e];
       off += n;
-      tb += (n + kBM - 1) / kBM;
+      tb += (n + tile_m - 1) / tile_m;
     }
     t.expert_off[nexperts] = off;
     t.tile_base[nexperts] = tb;
@@ -87,10 +87,10 @@ moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_r
     const int off = t.expert_off[e];
     const int n = t.expert_off[e + 1] - off;
     const int tb = t.tile_base[e];
-    for (int c = 0; c * kBM < n; ++c) {
+    for (int c = 0; c * tile_m < n; ++c) {
       GroupTile g;
-      g.a_row0 = off + c * kBM;
-      g.rows = imin(kBM, n - c * kBM);
+      g.a_row0 = off + c * tile_m;
+      g.rows = imin(tile_m, n - c * tile_m);
       g.expert = e;
       g.need_mask = 0;
       t.tiles[tb + c] = g;
@@ -100,7 +100,7 @@ moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_r
 
 // One thread per (token, k): inverse permutation and the source-rank mask of the row's tile.
 __global__ void moe_route_rows_kernel(const int* __restrict__ scatter_index, int total, int topk,
-                                      int tokens_per_rank, int nexperts, MoeTables t) {
+                                      int tokens_per_rank, int nexperts, int tile_m, MoeTables t) {
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total || *t.num_tiles == 0) return;
   const int row = scatter_index[i];
@@ -112,7 +112,7 @@ __global__ void moe_route_rows_kernel(const int* __restrict__ scatter_index, int
     const int mid = (lo + hi) >> 1;
     if (t.expert_off[mid] <= row) lo = mid; else hi = mid;
   }
-  const int tile = t.tile_base[lo] + (row - t.expert_off[lo]) / kBM;
+  const int tile = t.tile_base[lo] + (row - t.expert_off[lo]) / tile_m;
   atomicOr(&t.tiles[tile].need_mask, 1 << (token / tokens_per_rank));
 }
 
@@ -322,11 +322,16 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   const int max_tiles = static_cast<int>(max_rows / kBM + op->nexperts + 1);
 
   MoeTables tb = carve_tables(op->workspace, max_rows, op->nexperts);
-  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, op->nexperts, static_cast<int>(rows), max_tiles, tb,
-                                                comm->status_dev);
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.g_tiles = tb.tiles;
+  const int cg = resolve_cta_group(p, tuning);
+  const int tile_m = cg == 2 ? 2 * kBM : kBM;
+  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, op->nexperts, static_cast<int>(rows), max_tiles, tile_m,
+                                                tb, comm->status_dev);
   FLUXB_CUDA(cudaGetLastError());
   moe_route_rows_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, stream>>>(
-      scatter_index_dev, static_cast<int>(rows), op->topk, ntokens_local, op->nexperts, tb);
+      scatter_index_dev, static_cast<int>(rows), op->topk, ntokens_local, op->nexperts, tile_m, tb);
   FLUXB_CUDA(cudaGetLastError());
 
   const size_t half_gather = (static_cast<size_t>(op->max_ntokens) + kBM) * op->hidden * eb;
@@ -340,8 +345,6 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
       FLUXB_CUDA(cudaMemsetAsync(op->flags[comm->rank] + (parity ^ 1) * half_flags, 0, half_flags * sizeof(int), stream));
   }
 
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
   p.out_type = op->out_dtype == FLUXB_BF16 ? kOutBf16 : kOutF16;
   p.M = static_cast<int>(rows);
   p.N = op->ffn_local;
@@ -359,6 +362,7 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   p.g_rows_per_expert_b = op->ffn_local;
   p.g_expert_scale = out_scale;
   p.g_rows_per_rank = ntokens_local;
+  p.g_ntokens = static_cast<int>(ntokens);
   const uint8_t* a_base;
   if (world == 1 && !reuse) {
     a_base = static_cast<const uint8_t*>(tokens_shard);  // nothing to gather: read the caller's tokens in place
@@ -381,10 +385,11 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   int rc = encode_tmap_2d(&p.tmap_a, a_base, op->in_dtype, ntokens, op->hidden, row_bytes, 1);
   if (rc != FLUXB_OK) return rc;
   rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * op->ffn_local,
-                      op->hidden, row_bytes, bn);
+                      op->hidden, row_bytes, cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;
+  t.cta_group = cg;
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;
   if (!reuse) {
@@ -479,15 +484,20 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
 
   // tile table from the host-side splits (the reference also packs its problem list on the host
   // and uploads it, gemm_grouped_v3_gather_rs.cc:245-416)
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.g_tiles = reinterpret_cast<const GroupTile*>(op->workspace);  // grouped problem (pointer set for real below)
+  const int cg = resolve_cta_group(p, tuning);
+  const int tile_m = cg == 2 ? 2 * kBM : kBM;
   std::vector<GroupTile> tiles;
   long long off = 0;
   for (int e = 0; e < op->nexperts; ++e) {
     const int cnt = splits_host[e];
     FLUXB_REQUIRE(cnt >= 0, "moe_gather_rs_forward: splits[%d]=%d is negative", e, cnt);
-    for (int c = 0; c * kBM < cnt; ++c) {
+    for (int c = 0; c * tile_m < cnt; ++c) {
       GroupTile g;
-      g.a_row0 = static_cast<int>(off) + c * kBM;
-      g.rows = cnt - c * kBM < kBM ? cnt - c * kBM : kBM;
+      g.a_row0 = static_cast<int>(off) + c * tile_m;
+      g.rows = cnt - c * tile_m < tile_m ? cnt - c * tile_m : tile_m;
       g.expert = e;
       g.need_mask = 0;
       tiles.push_back(g);
@@ -502,8 +512,6 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   FLUXB_CUDA(cudaMemcpyAsync(tb.tiles, tiles.data(), tiles.size() * sizeof(GroupTile), cudaMemcpyHostToDevice, stream));
   FLUXB_CUDA(cudaMemcpyAsync(tb.num_tiles, &num_tiles, sizeof(int), cudaMemcpyHostToDevice, stream));
 
-  GemmParams p;
-  memset(&p, 0, sizeof(p));
   p.out_type = op->out_dtype == FLUXB_BF16 ? kOutBf16 : kOutF16;
   p.M = m;
   p.N = n;
@@ -526,10 +534,12 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   const int bn = resolve_block_n(comm, p, tuning, num_tiles > 0 ? num_tiles : 1);
   int rc = encode_tmap_2d(&p.tmap_a, x, op->in_dtype, m, k_local, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * n, k_local, row_bytes, bn);
+  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * n, k_local, row_bytes,
+                      cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;
+  t.cta_group = cg;
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;
 

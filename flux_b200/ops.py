@@ -41,7 +41,7 @@ def _tuning(t) -> Optional[C.Array]:
         return None
     if isinstance(t, _lib.Tuning):
         return C.byref(t)
-    return C.byref(_lib.Tuning(int(t.get("block_n", 0)), int(t.get("group_m", 0)), int(t.get("num_ctas", 0)), 0))
+    return C.byref(_lib.Tuning(int(t.get("block_n", 0)), int(t.get("group_m", 0)), int(t.get("num_ctas", 0)), int(t.get("cta_group", 0))))
 
 
 class AGRingMode(enum.IntEnum):

@@ -58,7 +58,7 @@ typedef struct fluxb_tuning {
   int block_n;  /* output tile width: 64, 128, 192 or 256             */
   int group_m;  /* rasterisation band height, in 128-row tiles         */
   int num_ctas; /* persistent grid size (<= SM count)                  */
-  int reserved;
+  int cta_group; /* 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile */
 } fluxb_tuning;
 
 const char* fluxb_last_error(void);
