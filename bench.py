@@ -309,18 +309,19 @@ def run_kernel_only(args):
     b = (torch.randn(n, k, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
     op = flux.AGKernel(None, 1, m, n, k, torch.bfloat16)
     c = torch.empty((m, n), dtype=torch.bfloat16, device="cuda")
+    tuning = {"block_n": args.block_n, "group_m": args.group_m, "cta_group": args.cta_group}
     for _ in range(args.warmup):
-        op.gemm_only(a, b, output=c)
+        op.gemm_only(a, b, output=c, tuning=tuning)
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        op.gemm_only(a, b, output=c)
+        op.gemm_only(a, b, output=c, tuning=tuning)
     e1.record()
     torch.cuda.synchronize()
     op.comm.check_status()
     ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({"case": "kernel-only", "m": m, "n": n, "k": k, "ms": ms,
+    print(json.dumps({"case": "kernel-only", "m": m, "n": n, "k": k, "tuning": tuning, "ms": ms,
                       "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12}), flush=True)
 
 
@@ -399,6 +400,9 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--kernel-only", action="store_true", help="small single-GPU case for profiler captures")
+    ap.add_argument("--block-n", type=int, default=0, help="kernel-only: output tile width (0 = library default)")
+    ap.add_argument("--group-m", type=int, default=0, help="kernel-only: rasterisation band height (0 = default)")
+    ap.add_argument("--cta-group", type=int, default=0, help="kernel-only: 1 or 2 CTAs per tile (0 = default)")
     args = ap.parse_args()
     if args.kernel_only:
         run_kernel_only(args)

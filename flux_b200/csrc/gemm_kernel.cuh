@@ -90,8 +90,14 @@ struct GemmParams {
   long long ag_row_bytes;
   int rank, world;
   // reduce-scatter push
+  CUtensorMap tmap_rs[kMaxWorld];  // fp32 [rows_per_owner, N] view of this rank's slot at owner o, 32x32 boxes
   float* rs_stage[kMaxWorld];  // rs_stage[o] = slot of this rank inside owner o's staging
   int* rs_cnt[kMaxWorld];      // per-tile counters at owner o: [tiles_per_seg][n_tiles]
+  // reduce-scatter: owner side (comm warps sum the partial tiles of this rank's rows)
+  const float* rs_local_stage;  // [world][seg_rows][N] fp32 partials received by this rank
+  int* rs_local_cnt;            // this rank's counters
+  void* rs_out;                 // [seg_rows, N] result, type rs_out_type
+  int rs_out_type;
   // grouped mode
   const GroupTile* g_tiles;  // null = dense
   const int* g_num_tiles;    // device scalar
@@ -112,8 +118,8 @@ struct SmemLayout {
   static constexpr int kBRows = CTA2 ? BN / 2 : BN;
   static constexpr int kBBytes = kBRows * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // epilogue staging: per epilogue warp 32 rows x (32 fp32 + 16 B pad)
-  static constexpr int kEpiPitch = 144;
+  // epilogue staging: per epilogue warp one 32 x 32 fp32 block, 128-byte rows, 128-byte swizzle
+  static constexpr int kEpiPitch = 128;
   static constexpr int kEpiWarpBytes = 32 * kEpiPitch;
   static constexpr int kEpiOffset = STAGES * kStageBytes;
   static constexpr int kBarOffset = kEpiOffset + 4 * kEpiWarpBytes;
@@ -288,7 +294,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           fence_proxy_async();
         }
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_empty(stage), phase ^ 1u, s_abort, kStatusTimeoutSmemEmpty, budget)) {
+          if (!mbar_wait(bar_empty(stage), phase ^ 1u, s_abort, kStatusTimeoutSmemEmpty, budget, 40)) {
             ok = false;
             break;
           }
@@ -378,14 +384,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     // ------------------------------------------------------------- epilogue
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
-    const uint32_t stage_row = smem_base + L::kEpiOffset + (warp - 2) * L::kEpiWarpBytes + lane * L::kEpiPitch;
+    const uint32_t stage_blk = smem_base + L::kEpiOffset + (warp - 2) * L::kEpiWarpBytes;
+    const uint32_t stage_row = stage_blk + lane * L::kEpiPitch;
     int it = 0;
     for (int t = tile_first; t < total_tiles; t += tile_step, ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       TileCoord tc;
       decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
-      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget)) break;
+      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget, 500)) break;
       tc_fence_after();
       const bool row_ok = row_in_tile < tc.rows;
       const int grow = tc.row0 + row_in_tile;  // global / sorted row
@@ -449,20 +456,24 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           }
         }
         if (p.epi_mode == kEpiRsPush) {
-          // Each lane owns one row: park its 32 fp32 values in shared memory and push them to the
-          // owner as one 128-byte bulk copy (a full NVLink payload instead of eight 16-byte stores).
-          bulk_wait_read();  // the previous copy out of this lane's staging row has been read
-          if (active) {
+          // Park the warp's 32 x 32 fp32 block in shared memory (lane = row, 16-byte pieces XOR-swizzled
+          // by row so that the writes spread over all banks and match the tensor map's 128-byte swizzle),
+          // then push it to the owner with one tiled store: 4 KB per operation over NVLink, rows and
+          // columns outside the owner's slot are clipped by the tensor map.
+          if (lane == 0) bulk_wait_read();  // the previous store out of this block has been read
+          __syncwarp();
 #pragma unroll
-            for (int q = 0; q < 8; ++q)
-              asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + q * 16), "f"(v[q * 4]),
-                           "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
-                           : "memory");
-            fence_proxy_async_smem();
-            const int ncols = imin(32, p.N - col0);
-            bulk_store(reinterpret_cast<float*>(dst_row) + col0, stage_row, static_cast<uint32_t>(ncols) * 4u);
+          for (int q = 0; q < 8; ++q)
+            asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + ((q ^ (lane & 7)) << 4)),
+                         "f"(v[q * 4]), "f"(v[q * 4 + 1]), "f"(v[q * 4 + 2]), "f"(v[q * 4 + 3])
+                         : "memory");
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (tc.rows > quad * 32 && col0 < p.N)
+              tma_store_2d(&p.tmap_rs[tc.seg], stage_blk, col0, tc.chunk * kBM + quad * 32);
+            bulk_commit();
           }
-          bulk_commit();
         } else if (active) {
           if (p.out_type == kOutF32) {
             float* d = reinterpret_cast<float*>(dst_row) + col0;
@@ -509,7 +520,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         // This warp's 32 rows of the tile are on their way: wait until the copies are complete, then
         // publish them to the owner. Each epilogue warp adds 1, so a complete 128-row tile counts 4
         // per source rank. (No CTA-wide barrier here: a role that gave up must never strand the others.)
-        bulk_wait_all();
+        if (lane == 0) bulk_wait_all();
         __syncwarp();
         if (lane == 0 && tc.rows > 0) {
           fence_acq_rel_sys();
@@ -566,6 +577,76 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           fence_acq_rel_sys();
           red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk, 1);
         }
+      }
+    }
+      if (p.epi_mode == kEpiRsPush && p.rs_out != nullptr) {
+      // Owner-side reduction: for every 128 x BN tile of this rank's rows, wait (bounded) until all
+      // ranks have published their partial (4 arrivals per source: one per epilogue warp), sum the
+      // partials in fp32 in rank order, round once, clear the counter. Runs beside the GEMM roles.
+      const int ctid = threadIdx.x - 6 * 32;  // 0..127
+      const int m_chunks = (p.seg_rows + kBM - 1) / kBM;
+      const int total_r = m_chunks * n_tiles;
+      const int vec_per_row = BN / 4;
+      const long long slot = static_cast<long long>(p.seg_rows) * p.N;
+      volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
+      for (int rt = blockIdx.x; rt < total_r; rt += gridDim.x) {
+        const int c = rt % m_chunks;  // chunk fastest: the order in which the last band is produced
+        const int nt = rt / m_chunks;
+        int* cnt = p.rs_local_cnt + c * n_tiles + nt;
+        if (ctid == 0)
+          *s_flag = flag_wait_eq(cnt, 4 * p.world, s_abort, kStatusTimeoutReduce, budget) ? 1 : 0;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        const int okr = *s_flag;
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (!okr) break;
+        const int rows = imin(kBM, p.seg_rows - c * kBM);
+        const int n0 = nt * BN;
+        const int nvec = rows * vec_per_row;
+        for (int i0 = ctid; i0 < nvec; i0 += 4 * 128) {
+          float4 acc[4];
+          long long off[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = i0 + u * 128;
+            const int r = i / vec_per_row;
+            const int col = n0 + (i - r * vec_per_row) * 4;
+            off[u] = (i < nvec && col < p.N) ? static_cast<long long>(c * kBM + r) * p.N + col : -1;
+            acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+          }
+          for (int sr = 0; sr < p.world; ++sr) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (off[u] >= 0) v[u] = *reinterpret_cast<const float4*>(p.rs_local_stage + sr * slot + off[u]);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+              if (off[u] >= 0) {
+                acc[u].x += v[u].x;
+                acc[u].y += v[u].y;
+                acc[u].z += v[u].z;
+                acc[u].w += v[u].w;
+              }
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (off[u] < 0) continue;
+            if (p.rs_out_type == kOutF32) {
+              *reinterpret_cast<float4*>(static_cast<float*>(p.rs_out) + off[u]) = acc[u];
+            } else {
+              uint2 w;
+              if (p.rs_out_type == kOutBf16) {
+                w.x = pack_bf16(acc[u].x, acc[u].y);
+                w.y = pack_bf16(acc[u].z, acc[u].w);
+              } else {
+                w.x = pack_f16(acc[u].x, acc[u].y);
+                w.y = pack_f16(acc[u].z, acc[u].w);
+              }
+              *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.rs_out) + off[u]) = w;
+            }
+          }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ctid == 0) *cnt = 0;
       }
     }
   }

@@ -71,6 +71,9 @@ namespace fluxb {
 int encode_tmap_2d(CUtensorMap* out, const void* base, int elt_dtype, long long rows, long long k,
                    long long ld_bytes, int box_rows);
 
+// fp32 [rows, n] row-major matrix, 32 x 32 element boxes, 128-byte swizzle (reduce-scatter pushes)
+int encode_tmap_f32_store(CUtensorMap* out, const void* base, long long rows, long long n);
+
 // Output tile width for a problem: the caller's choice, else a wave-quantisation heuristic.
 // `m_tiles_hint` > 0 overrides the M-tile count derived from the segments (grouped problems).
 int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tuning* tuning,

@@ -77,12 +77,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 
 // Bounded mbarrier wait. `s_abort` is a CTA-shared word: non-zero means some
 // role has given up, and every other role must leave its loop too.
+// `backoff_ns` > 0 sleeps between polls: for waits that normally last many microseconds (an
+// accumulator that is still being computed), so that idle warps do not burn issue slots and power.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort,
-                                          int code, uint64_t budget_ns) {
+                                          int code, uint64_t budget_ns, uint32_t backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
   uint32_t n = 0;
   while (!mbar_try_wait(bar, parity)) {
+    if (backoff_ns != 0) __nanosleep(backoff_ns);
     if ((++n & 31u) == 0u) {
       if (*s_abort != 0) return false;
       if (globaltimer_ns() - t0 > budget_ns) {
@@ -334,6 +337,13 @@ __device__ __forceinline__ void tma_gather4_2d_2cta(uint32_t smem_dst, const voi
 __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src),
                "r"(bytes)
+               : "memory");
+}
+// 2-D tiled store shared -> global (tensor map decides box and swizzle; out-of-range parts are clipped)
+__device__ __forceinline__ void tma_store_2d(const void* tmap, uint32_t smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                   reinterpret_cast<uint64_t>(tmap)),
+               "r"(smem_src), "r"(x), "r"(y)
                : "memory");
 }
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
