@@ -64,7 +64,7 @@ class ClockSampler:
         self.proc = None
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "50",
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(gpu_index)], stdout=self.f, stderr=subprocess.DEVNULL)
         except Exception:
             self.proc = None
@@ -278,7 +278,7 @@ def run_ours(args):
             "speedup_vs_unfused": unfused_ms / ms_per_step,
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
                     "h2d_bytes_per_step": a.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world},
-            "gpu_launches": args.steps * (2 if world == 1 else 3),
+            "gpu_launches": args.steps * 2,
             "roofline": {"bound": "tensor", "achieved": ag_tflops, "peak": sustained, "unit": "TFLOP/s",
                          "frac": ag_tflops / sustained, "frac_of_burst_peak": ag_tflops / burst,
                          "peak_source": f"{peak_src} cuBLAS bf16, sustained (kernel timed inside a long step)",

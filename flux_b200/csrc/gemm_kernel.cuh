@@ -62,6 +62,8 @@ struct GroupTile {
 struct GemmParams {
   CUtensorMap tmap_a;
   CUtensorMap tmap_b;
+  CUtensorMap tmap_a_own;  // all-gather: this rank's own shard, read in place (valid if a_own_valid)
+  int a_own_valid;
   int M, N, K;
   // M segmentation: nseg segments of seg_rows rows; tiles never straddle a
   // segment; segments are visited (seg_first + i) % nseg.
@@ -93,9 +95,12 @@ struct GemmParams {
   CUtensorMap tmap_rs[kMaxWorld];  // fp32 [rows_per_owner, N] view of this rank's slot at owner o, 32x32 boxes
   float* rs_stage[kMaxWorld];  // rs_stage[o] = slot of this rank inside owner o's staging
   int* rs_cnt[kMaxWorld];      // per-tile counters at owner o: [tiles_per_seg][n_tiles]
-  // reduce-scatter: owner side (comm warps sum the partial tiles of this rank's rows)
+  // reduce-scatter: owner side. The comm warps sum the partial tiles the peers pushed for this
+  // rank's rows into this rank's own (otherwise unused) slot and raise a per-tile ready flag; the
+  // epilogue of this rank's own tiles adds that sum to its accumulator and writes the result.
   const float* rs_local_stage;  // [world][seg_rows][N] fp32 partials received by this rank
-  int* rs_local_cnt;            // this rank's counters
+  int* rs_local_cnt;            // this rank's arrival counters, [tiles]
+  int* rs_local_ready;          // this rank's "remote partials summed" flags, [tiles]
   void* rs_out;                 // [seg_rows, N] result, type rs_out_type
   int rs_out_type;
   // grouped mode
@@ -240,6 +245,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     mbar_init_fence();
     tma_prefetch_desc(&p.tmap_a);
     tma_prefetch_desc(&p.tmap_b);
+    if (p.a_own_valid) tma_prefetch_desc(&p.tmap_a_own);
   }
   if (warp == 1) {
     if (CTA2) {
@@ -277,7 +283,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
         if (p.ag_flags != nullptr) {
           if (p.g_tiles == nullptr) {
-            if (tc.rows > 0)
+            if (tc.rows > 0 && !(p.a_own_valid && tc.seg == p.rank))
               ok = flag_wait_eq(p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk, p.ag_expected,
                                 s_abort, kStatusTimeoutFlag, budget);
           } else {
@@ -308,8 +314,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             mbar_arrive_expect_tx(fb, L::kStageBytes);
           }
           if (p.g_gather == nullptr) {
-            if (CTA2) tma_load_2d_2cta(smem_a(stage), &p.tmap_a, fb, kb * BKE, tc.row0);
-            else tma_load_2d(smem_a(stage), &p.tmap_a, fb, kb * BKE, tc.row0);
+            // tiles of this rank's own shard read the caller's tensor in place
+            const bool own_a = p.a_own_valid && p.g_tiles == nullptr && tc.seg == p.rank;
+            const void* ta = own_a ? &p.tmap_a_own : &p.tmap_a;
+            const int arow = own_a ? tc.row0 - p.rank * p.seg_rows : tc.row0;
+            if (CTA2) tma_load_2d_2cta(smem_a(stage), ta, fb, kb * BKE, arow);
+            else tma_load_2d(smem_a(stage), ta, fb, kb * BKE, arow);
           } else {
             // 32 gather4 copies of 4 rows each; rows past the tile end re-read a valid row
             const int* gi = p.g_gather + (tc.rows > 0 ? tc.row0 : 0);
@@ -401,10 +411,31 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       if (p.scale_a != nullptr && row_ok) row_scale *= p.scale_a[grow];
       if (p.g_expert_scale != nullptr) row_scale *= p.g_expert_scale[tc.expert];
 
+      // Reduce-scatter, tiles of this rank's own rows: the peers' partials have been summed by the comm
+      // warps; wait (bounded) for that, then add the sum to the accumulator and write the final rows.
+      const bool own = p.epi_mode == kEpiRsPush && tc.seg == p.rank;
+      const float* sum_row = nullptr;
+      if (own) {
+        int okw = 1;
+        if (lane == 0)
+          okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 1, s_abort, kStatusTimeoutReduce,
+                             budget) ? 1 : 0;
+        okw = __shfl_sync(0xffffffffu, okw, 0);
+        if (!okw) break;
+      }
+      const int otype = own ? p.rs_out_type : p.out_type;
+
       // destination row pointer
       uint8_t* dst_row = nullptr;
       const uint8_t* bias_row = nullptr;
-      if (p.epi_mode == kEpiStore) {
+      if (own) {
+        const long long lrow = static_cast<long long>(tc.chunk) * kBM + row_in_tile;
+        const int osz = (otype == kOutF32) ? 4 : 2;
+        dst_row = static_cast<uint8_t*>(p.rs_out) + lrow * p.N * osz;
+        sum_row = p.rs_local_stage + static_cast<long long>(p.rank) * p.seg_rows * p.N + lrow * p.N;
+        if (p.bias_mode == kBiasFull)
+          bias_row = static_cast<const uint8_t*>(p.bias) + static_cast<long long>(grow) * p.ldbias * 2;
+      } else if (p.epi_mode == kEpiStore) {
         long long orow = grow;
         if (p.g_scatter_rows != nullptr && row_ok) orow = p.g_scatter_rows[grow];
         const int osz = (p.out_type == kOutF32) ? 4 : 2;
@@ -440,7 +471,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         }
         if (active && bias_row != nullptr) {
           // bias has the output dtype in store mode, bf16 in reduce-scatter mode
-          const int bt = (p.epi_mode == kEpiStore) ? p.out_type : kOutBf16;
+          const int bt = (p.epi_mode == kEpiStore) ? p.out_type : kOutBf16;  // own tiles included
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (col0 + j < p.N) {
@@ -455,7 +486,19 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             }
           }
         }
-        if (p.epi_mode == kEpiRsPush) {
+        if (own && active) {
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            if (col0 + q * 4 + 4 <= p.N) {
+              const float4 sv = *reinterpret_cast<const float4*>(sum_row + col0 + q * 4);
+              v[q * 4] += sv.x;
+              v[q * 4 + 1] += sv.y;
+              v[q * 4 + 2] += sv.z;
+              v[q * 4 + 3] += sv.w;
+            }
+          }
+        }
+        if (p.epi_mode == kEpiRsPush && !own) {
           // Park the warp's 32 x 32 fp32 block in shared memory (lane = row, 16-byte pieces XOR-swizzled
           // by row so that the writes spread over all banks and match the tensor map's 128-byte swizzle),
           // then push it to the owner with one tiled store: 4 KB per operation over NVLink, rows and
@@ -475,7 +518,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             bulk_commit();
           }
         } else if (active) {
-          if (p.out_type == kOutF32) {
+          if (otype == kOutF32) {
             float* d = reinterpret_cast<float*>(dst_row) + col0;
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -495,7 +538,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
               uint32_t w[4];
 #pragma unroll
               for (int j = 0; j < 4; ++j)
-                w[j] = (p.out_type == kOutBf16) ? pack_bf16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1])
+                w[j] = (otype == kOutBf16) ? pack_bf16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1])
                                                 : pack_f16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
               if (col0 + q * 8 + 8 <= p.N) {
                 *reinterpret_cast<uint4*>(d + q * 8) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -516,7 +559,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
         else mbar_arrive(bar_tempty(acc));
       }
-      if (p.epi_mode == kEpiRsPush) {
+      if (p.epi_mode == kEpiRsPush && !own) {
         // This warp's 32 rows of the tile are on their way: wait until the copies are complete, then
         // publish them to the owner. Each epilogue warp adds 1, so a complete 128-row tile counts 4
         // per source rank. (No CTA-wide barrier here: a role that gave up must never strand the others.)
@@ -553,7 +596,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
                        (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0;
         // one 16-byte column of the slice per thread, 8 rows in flight
         const int nrows = r1 - r0;
-        if (ctid < vec_per_row) {
+        const bool skip_data = p.a_own_valid && dest == p.rank;  // own tiles read the caller's tensor
+        if (ctid < vec_per_row && !skip_data) {
           const uint8_t* s0 = src + ctid * 16;
           uint8_t* d0 = dst + ctid * 16;
           for (int rr = 0; rr < nrows; rr += 8) {
@@ -573,28 +617,31 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           for (int rr = r0 + ctid; rr < r1; rr += 128) sd[rr] = p.ag_src_scale[rr];
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ctid == 0) {
+        if (ctid == 0 && !skip_data) {
           fence_acq_rel_sys();
           red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk, 1);
         }
       }
     }
-      if (p.epi_mode == kEpiRsPush && p.rs_out != nullptr) {
-      // Owner-side reduction: for every 128 x BN tile of this rank's rows, wait (bounded) until all
-      // ranks have published their partial (4 arrivals per source: one per epilogue warp), sum the
-      // partials in fp32 in rank order, round once, clear the counter. Runs beside the GEMM roles.
+      if (p.epi_mode == kEpiRsPush) {
+      // Owner side of the reduce-scatter: for every 128 x BN tile of this rank's rows wait (bounded)
+      // until every peer has published its partial (4 arrivals per peer: one per epilogue warp), sum
+      // the peers' partials in fp32 in rank order into this rank's own slot, and raise the tile's
+      // ready flag for the epilogue. The peers compute this rank's rows before their own, so this
+      // work is spread over the kernel and finished before the own tiles are.
       const int ctid = threadIdx.x - 6 * 32;  // 0..127
       const int m_chunks = (p.seg_rows + kBM - 1) / kBM;
       const int total_r = m_chunks * n_tiles;
       const int vec_per_row = BN / 4;
       const long long slot = static_cast<long long>(p.seg_rows) * p.N;
+      float* sum_base = p.rs_stage[p.rank];  // this rank's slot in its own staging
       volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
       for (int rt = blockIdx.x; rt < total_r; rt += gridDim.x) {
-        const int c = rt % m_chunks;  // chunk fastest: the order in which the last band is produced
+        const int c = rt % m_chunks;
         const int nt = rt / m_chunks;
-        int* cnt = p.rs_local_cnt + c * n_tiles + nt;
+        const int tix = c * n_tiles + nt;
         if (ctid == 0)
-          *s_flag = flag_wait_eq(cnt, 4 * p.world, s_abort, kStatusTimeoutReduce, budget) ? 1 : 0;
+          *s_flag = flag_wait_eq(p.rs_local_cnt + tix, 4 * (p.world - 1), s_abort, kStatusTimeoutReduce, budget) ? 1 : 0;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int okr = *s_flag;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -614,6 +661,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
           }
           for (int sr = 0; sr < p.world; ++sr) {
+            if (sr == p.rank) continue;
             float4 v[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u)
@@ -628,25 +676,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
               }
           }
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
-            if (off[u] < 0) continue;
-            if (p.rs_out_type == kOutF32) {
-              *reinterpret_cast<float4*>(static_cast<float*>(p.rs_out) + off[u]) = acc[u];
-            } else {
-              uint2 w;
-              if (p.rs_out_type == kOutBf16) {
-                w.x = pack_bf16(acc[u].x, acc[u].y);
-                w.y = pack_bf16(acc[u].z, acc[u].w);
-              } else {
-                w.x = pack_f16(acc[u].x, acc[u].y);
-                w.y = pack_f16(acc[u].z, acc[u].w);
-              }
-              *reinterpret_cast<uint2*>(static_cast<uint16_t*>(p.rs_out) + off[u]) = w;
-            }
-          }
+          for (int u = 0; u < 4; ++u)
+            if (off[u] >= 0) *reinterpret_cast<float4*>(sum_base + off[u]) = acc[u];
         }
+        __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ctid == 0) *cnt = 0;
+        if (ctid == 0) {
+          __threadfence();
+          st_release_sys(p.rs_local_ready + tix, 1);
+        }
       }
     }
   }

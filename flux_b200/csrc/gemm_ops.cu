@@ -359,6 +359,11 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   uint8_t* local_gather = op->gather[comm->rank] + parity * half_gather;
   rc = encode_tmap_2d(&p.tmap_a, local_gather, op->in_dtype, m, k, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
+  rc = encode_tmap_2d(&p.tmap_a_own, a_shard, op->in_dtype, m_local, k, row_bytes, kBM);
+  if (rc != FLUXB_OK) return rc;
+  // per-row scales travel through the scale buffer under the same flags as the data: keep the
+  // flagged path for the own shard too in that case
+  p.a_own_valid = scale_a_shard == nullptr ? 1 : 0;
   rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k, row_bytes, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
@@ -366,8 +371,12 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;
   op->calls += 1;
-  if (gathered_out != nullptr)
+  if (gathered_out != nullptr) {
+    // peers' shards come from the gather buffer, this rank's own shard from the caller's tensor
     FLUXB_CUDA(cudaMemcpyAsync(gathered_out, local_gather, m * row_bytes, cudaMemcpyDeviceToDevice, stream));
+    FLUXB_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(gathered_out) + static_cast<size_t>(comm->rank) * m_local * row_bytes,
+                               a_shard, m_local * row_bytes, cudaMemcpyDeviceToDevice, stream));
+  }
   return FLUXB_OK;
 }
 
@@ -381,7 +390,8 @@ size_t fluxb_gemm_rs_stage_bytes(int max_m, int n_dim, int world) {
   return 2ull * static_cast<size_t>(max_m) * n_dim * sizeof(float);
 }
 size_t fluxb_gemm_rs_cnt_bytes(int max_m, int n_dim, int world) {
-  return 2ull * rs_cnt_cap(max_m, n_dim, world) * sizeof(int);
+  // two parities x (arrival counters + ready flags)
+  return 2ull * 2ull * rs_cnt_cap(max_m, n_dim, world) * sizeof(int);
 }
 
 int fluxb_gemm_rs_create(fluxb_comm_t comm, int max_m, int n_dim, int in_dtype, int out_dtype,
@@ -444,6 +454,10 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   const int eb = dtype_bytes(op->in_dtype);
   const int mpr = m / world;
   const int parity = static_cast<int>(op->calls & 1ull);
+  // The other parity's counters and flags were consumed by the previous call and are next written by
+  // peers only after they have seen this call's pushes: clear them now.
+  FLUXB_CUDA(cudaMemsetAsync(op->cnt[comm->rank] + (parity ^ 1) * 2 * op->cnt_cap, 0,
+                             2 * op->cnt_cap * sizeof(int), stream));
   GemmParams p;
   zero_params(p);
   int ot;
@@ -466,7 +480,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   const size_t half_stage = static_cast<size_t>(op->max_m) * op->n_dim;
   for (int r = 0; r < world; ++r) {
     p.rs_stage[r] = op->stage[r] + parity * half_stage + static_cast<size_t>(comm->rank) * mpr * n;
-    p.rs_cnt[r] = op->cnt[r] + parity * op->cnt_cap;
+    p.rs_cnt[r] = op->cnt[r] + parity * 2 * op->cnt_cap;
     rc = encode_tmap_f32_store(&p.tmap_rs[r], p.rs_stage[r], mpr, n);
     if (rc != FLUXB_OK) return rc;
   }
@@ -486,7 +500,8 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   t.block_n = bn;
   // the owner-side reduction runs in the same kernel (comm warps)
   p.rs_local_stage = op->stage[comm->rank] + parity * half_stage;
-  p.rs_local_cnt = op->cnt[comm->rank] + parity * op->cnt_cap;
+  p.rs_local_cnt = op->cnt[comm->rank] + parity * 2 * op->cnt_cap;
+  p.rs_local_ready = p.rs_local_cnt + op->cnt_cap;
   p.rs_out = out;
   p.rs_out_type = ot;
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
