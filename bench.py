@@ -55,9 +55,11 @@ def _flops_per_gpu(world):
 
 
 class ClockSampler:
-    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
-             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
-             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    """nvidia-smi in loop mode, started well before the timed region (it takes a while to come up on a
+    multi-GPU box); samples are selected afterwards by their timestamps."""
+    QUERY = ("timestamp,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, gpu_index):
         self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
@@ -69,7 +71,9 @@ class ClockSampler:
         except Exception:
             self.proc = None
 
-    def stop(self):
+    def stop(self, t_begin, t_end):
+        import datetime
+
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
         if self.proc is None:
             return out
@@ -81,23 +85,27 @@ class ClockSampler:
         self.f.flush()
         rows = [l.strip().split(", ") for l in open(self.f.name) if l.strip()]
         os.unlink(self.f.name)
-        sm, reasons, mx = [], set(), None
+        sm, pw, reasons, mx = [], [], set(), None
         for r in rows:
-            if len(r) < 9:
+            if len(r) < 8:
                 continue
             try:
-                sm.append(float(r[1]))
-                mx = float(r[2])
+                ts = datetime.datetime.strptime(r[0], "%Y/%m/%d %H:%M:%S.%f").timestamp()
+                clk, mxv, watts = float(r[1]), float(r[2]), float(r[3])
             except ValueError:
                 continue
-            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[5:9]):
+            if ts < t_begin - 0.02 or ts > t_end + 0.02:
+                continue
+            sm.append(clk)
+            pw.append(watts)
+            mx = mxv
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[4:8]):
                 if val.strip().lower().startswith("active"):
                     reasons.add(name)
         if sm:
-            # under load = upper half of the samples (the sampler also sees the idle edges)
-            sm.sort()
-            out["sm_mhz"] = statistics.median(sm[len(sm) // 2:])
+            out["sm_mhz"] = statistics.median(sm)
             out["sm_max_mhz"] = mx
+            out["power_w"] = statistics.median(pw)
             out["samples"] = len(sm)
         out["reasons"] = sorted(reasons)
         return out
@@ -138,6 +146,7 @@ def run_ours(args):
     torch.cuda.set_device(local)
     group = None
     if world > 1:
+        os.environ.pop("NCCL_DEBUG", None)  # keep stdout to the one JSON line
         dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
         group = dist.group.WORLD
     import flux_b200 as flux
@@ -161,37 +170,16 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    sampler = ClockSampler(local) if rank == 0 else None
     for _ in range(max(args.warmup, 3)):
         out = step()
     barrier()
     comm.check_status()
     sampled_err = _sampled_check(a, b0, b1, c0, out, rank, world)
 
-    # ---- timed region: K steps, per-op split from extra events on the same stream
-    sampler = ClockSampler(local) if rank == 0 else None
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
-    barrier()
-    t_wall = time.perf_counter()
-    for i in range(args.steps):
-        ev[i][0].record()
-        ag.forward(a, b0, output=c0)
-        ev[i][1].record()
-        out = rs.forward(c0, b1)
-        ev[i][2].record()
-    end = torch.cuda.Event(enable_timing=True)
-    end.record()
-    barrier()
-    wall_ms = (time.perf_counter() - t_wall) * 1e3
-    clocks = sampler.stop() if sampler else None
-    comm.check_status()
-    total_ms = ev[0][0].elapsed_time(end)
-    ag_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
-    rs_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
-    ms_per_step = _max_over_ranks(total_ms / args.steps, world)
-    ag_ms = _max_over_ranks(ag_ms, world)
-    rs_ms = _max_over_ranks(rs_ms, world)
-
-    # ---- unfused sequence on the same box: NCCL all_gather + cuBLAS, cuBLAS + NCCL reduce_scatter
+    # ---- unfused sequence on the same box: NCCL all_gather + cuBLAS, cuBLAS + NCCL reduce_scatter.
+    # Timed once before and once after the fused region, so that neither arm is favoured by the
+    # power / thermal state it inherits.
     full_a = torch.empty((M, K0), dtype=torch.bfloat16, device="cuda")
     rs_out = torch.empty((M // world, N1), dtype=torch.bfloat16, device="cuda")
 
@@ -208,17 +196,50 @@ def run_ours(args):
             return rs_out
         return full
 
+    def time_unfused():
+        for _ in range(3):
+            unfused_step()
+        barrier()
+        u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        u0.record()
+        for _ in range(args.steps):
+            uo_ = unfused_step()
+        u1.record()
+        barrier()
+        return _max_over_ranks(u0.elapsed_time(u1) / args.steps, world), uo_
+
+    unfused_before, _ = time_unfused()
     for _ in range(3):
-        unfused_step()
+        out = step()
+
+    # ---- timed region: K steps, per-op split from extra events on the same stream
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     barrier()
-    u0, u1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    u0.record()
-    for _ in range(args.steps):
-        uo = unfused_step()
-    u1.record()
+    t_begin = time.time()
+    t_wall = time.perf_counter()
+    for i in range(args.steps):
+        ev[i][0].record()
+        ag.forward(a, b0, output=c0)
+        ev[i][1].record()
+        out = rs.forward(c0, b1)
+        ev[i][2].record()
+    end = torch.cuda.Event(enable_timing=True)
+    end.record()
     barrier()
-    unfused_ms = _max_over_ranks(u0.elapsed_time(u1) / args.steps, world)
+    wall_ms = (time.perf_counter() - t_wall) * 1e3
+    t_end = time.time()
+    comm.check_status()
+    total_ms = ev[0][0].elapsed_time(end)
+    ag_ms = statistics.mean(e[0].elapsed_time(e[1]) for e in ev)
+    rs_ms = statistics.mean(e[1].elapsed_time(e[2]) for e in ev)
+    ms_per_step = _max_over_ranks(total_ms / args.steps, world)
+    ag_ms = _max_over_ranks(ag_ms, world)
+    rs_ms = _max_over_ranks(rs_ms, world)
+
+    unfused_after, uo = time_unfused()
+    unfused_ms = 0.5 * (unfused_before + unfused_after)
     agree = float((uo.float() - out.float()).abs().max() / uo.float().abs().max().clamp_min(1e-30))
+    clocks = sampler.stop(t_begin, t_end) if sampler else None
 
     # ---- end to end through host buffers: H2D of this rank's activations, both ops, D2H of the result
     a_host = a.cpu().pin_memory()
@@ -273,7 +294,8 @@ def run_ours(args):
             "ag_gemm": {"ms": ag_ms, "tflops_per_gpu": ag_tflops},
             "gemm_rs": {"ms": rs_ms, "tflops_per_gpu": rs_tflops},
             "unfused": {"what": "NCCL all_gather + cuBLAS matmul, cuBLAS matmul + NCCL reduce_scatter (torch)",
-                        "ms_per_step": unfused_ms, "tflops_per_gpu": flops_gpu / (unfused_ms * 1e-3) / 1e12,
+                        "ms_per_step": unfused_ms, "ms_before_fused_region": unfused_before,
+                        "ms_after_fused_region": unfused_after, "tflops_per_gpu": flops_gpu / (unfused_ms * 1e-3) / 1e12,
                         "max_rel_diff_vs_fused": agree},
             "speedup_vs_unfused": unfused_ms / ms_per_step,
             "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,

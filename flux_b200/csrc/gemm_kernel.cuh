@@ -123,10 +123,13 @@ struct SmemLayout {
   static constexpr int kBRows = CTA2 ? BN / 2 : BN;
   static constexpr int kBBytes = kBRows * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // epilogue staging: per epilogue warp one 32 x 32 fp32 block, 128-byte rows, 128-byte swizzle
+  // epilogue staging: per epilogue warp 32 x 32 fp32 blocks, 128-byte rows, 128-byte swizzle; two
+  // blocks per warp where shared memory allows, so that two pushes per warp can be in flight
   static constexpr int kEpiPitch = 128;
-  static constexpr int kEpiWarpBytes = 32 * kEpiPitch;
+  static constexpr int kEpiBlockBytes = 32 * kEpiPitch;
   static constexpr int kEpiOffset = STAGES * kStageBytes;
+  static constexpr int kEpiBufs = (kEpiOffset + 8 * kEpiBlockBytes + (2 * STAGES + 4) * 8 + 64 + 1024 <= 232448) ? 2 : 1;
+  static constexpr int kEpiWarpBytes = kEpiBufs * kEpiBlockBytes;
   static constexpr int kBarOffset = kEpiOffset + 4 * kEpiWarpBytes;
   static constexpr int kNumBars = 2 * STAGES + 4;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
@@ -394,8 +397,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     // ------------------------------------------------------------- epilogue
     const int quad = warp & 3;
     const int row_in_tile = quad * 32 + lane;
-    const uint32_t stage_blk = smem_base + L::kEpiOffset + (warp - 2) * L::kEpiWarpBytes;
-    const uint32_t stage_row = stage_blk + lane * L::kEpiPitch;
+    const uint32_t stage_blk0 = smem_base + L::kEpiOffset + (warp - 2) * L::kEpiWarpBytes;
+    int* pending_cnt = nullptr;  // reduce-scatter: counter of the previous pushed tile, published one tile late
     int it = 0;
     for (int t = tile_first; t < total_tiles; t += tile_step, ++it) {
       const int acc = it & 1;
@@ -498,12 +501,17 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             }
           }
         }
+        if (own && lane == 0) bulk_commit();  // keeps the number of groups per tile uniform
         if (p.epi_mode == kEpiRsPush && !own) {
           // Park the warp's 32 x 32 fp32 block in shared memory (lane = row, 16-byte pieces XOR-swizzled
           // by row so that the writes spread over all banks and match the tensor map's 128-byte swizzle),
           // then push it to the owner with one tiled store: 4 KB per operation over NVLink, rows and
           // columns outside the owner's slot are clipped by the tensor map.
-          if (lane == 0) bulk_wait_read();  // the previous store out of this block has been read
+          const uint32_t stage_blk = stage_blk0 + (L::kEpiBufs == 2 ? (c & 1) * L::kEpiBlockBytes : 0);
+          const uint32_t stage_row = stage_blk + lane * L::kEpiPitch;
+          if (lane == 0) {  // the previous store out of this block has been read
+            if (L::kEpiBufs == 2) bulk_wait_read_keep1(); else bulk_wait_read();
+          }
           __syncwarp();
 #pragma unroll
           for (int q = 0; q < 8; ++q)
@@ -559,16 +567,28 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
         else mbar_arrive(bar_tempty(acc));
       }
-      if (p.epi_mode == kEpiRsPush && !own) {
-        // This warp's 32 rows of the tile are on their way: wait until the copies are complete, then
-        // publish them to the owner. Each epilogue warp adds 1, so a complete 128-row tile counts 4
-        // per source rank. (No CTA-wide barrier here: a role that gave up must never strand the others.)
-        if (lane == 0) bulk_wait_all();
-        __syncwarp();
-        if (lane == 0 && tc.rows > 0) {
-          fence_acq_rel_sys();
-          red_add_release_sys(p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx, 1);
+      if (p.epi_mode == kEpiRsPush) {
+        // Publish the PREVIOUS pushed tile of this warp: its stores were issued a whole tile ago, so
+        // waiting for all groups but this tile's BN/32 costs nothing, whereas waiting for the stores
+        // just issued would put NVLink round trips on the epilogue's critical path. Each epilogue warp
+        // adds 1, so a complete 128-row tile counts 4 per source rank. (No CTA-wide barrier here: a
+        // role that gave up must never strand the others.)
+        if (lane == 0) {
+          if (pending_cnt != nullptr) {
+            bulk_wait_all_but<BN / 32>();
+            fence_acq_rel_sys();
+            red_add_release_sys(pending_cnt, 1);
+          }
+          pending_cnt = (!own && tc.rows > 0) ? p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx : nullptr;
         }
+      }
+    }
+    if (p.epi_mode == kEpiRsPush && lane == 0) {
+      // also on the way out after a failed wait: the stores must not outlive the CTA
+      bulk_wait_all();
+      if (pending_cnt != nullptr) {
+        fence_acq_rel_sys();
+        red_add_release_sys(pending_cnt, 1);
       }
     }
   } else {
