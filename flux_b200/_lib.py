@@ -17,6 +17,8 @@ FLUXB_ERR_CUDA = -2
 FLUXB_ERR_TIMEOUT = -3
 FLUXB_ERR_UNSUPPORTED = -4
 MAX_WORLD = 8
+STATIC_MAX_ROWS = 65536
+STATIC_MAX_EXPERTS = 256
 IPC_HANDLE_BYTES = 64
 
 BF16, F16, F32, E4M3, E5M2 = 0, 1, 2, 3, 4
@@ -86,6 +88,7 @@ SIGNATURES = {
     "fluxb_moe_ag_scatter_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _pp, _pp, _vp, _pp]),
     "fluxb_moe_ag_scatter_destroy": (_i, [_vp]),
     "fluxb_moe_ag_scatter_forward": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _tun, _vp]),
+    "fluxb_moe_scatter_gemm_static": (_i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _tun, _vp]),
     "fluxb_moe_gather_rs_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "fluxb_moe_gather_rs_stage_bytes": (_sz, [_i, _i, _i, _i]),
     "fluxb_moe_gather_rs_cnt_bytes": (_sz, [_i, _i, _i]),

@@ -579,3 +579,114 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------
+// Scatter + grouped GEMM without any allocation: the routing tables live in a
+// fixed device array of this translation unit instead of a caller workspace.
+// ---------------------------------------------------------------------------
+namespace fluxb {
+
+// worst-case table bytes for FLUXB_STATIC_MAX_ROWS routed rows and FLUXB_STATIC_MAX_EXPERTS experts:
+// tiles (rows/128 + experts + 1) * 16 B, one counter, two offset arrays, rows * 4 B of gather index
+constexpr size_t kStaticTableBytes =
+    ((FLUXB_STATIC_MAX_ROWS / kBM + FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(GroupTile) + 255) / 256 * 256 + 256 +
+    2 * (((FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(int) + 255) / 256 * 256) +
+    (static_cast<size_t>(FLUXB_STATIC_MAX_ROWS) * sizeof(int) + 255) / 256 * 256;
+
+// In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
+static __device__ __align__(256) unsigned char g_static_tables[kStaticTableBytes];
+
+// Device address of the array on the current device, looked up once per device.
+static int static_tables_ptr(int device, void** out) {
+  static void* ptrs[64] = {};
+  FLUXB_REQUIRE(device >= 0 && device < 64, "device index %d not supported", device);
+  if (ptrs[device] == nullptr) {
+    void* ptr = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_tables);
+    if (e != cudaSuccess || ptr == nullptr)
+      FLUXB_FAIL(FLUXB_ERR_CUDA, "cudaGetSymbolAddress(routing tables) failed: %s", cudaGetErrorString(e));
+    ptrs[device] = ptr;
+  }
+  *out = ptrs[device];
+  return FLUXB_OK;
+}
+
+}  // namespace fluxb
+
+extern "C" int fluxb_moe_scatter_gemm_static(fluxb_comm_t comm, const void* tokens, int ntokens, int hidden,
+                                             const void* weights, int nexperts, int ffn, int topk,
+                                             const int* splits_dev, const int* scatter_index_dev,
+                                             const float* out_scale, void* out, int in_dtype, int out_dtype,
+                                             const fluxb_tuning* tuning, fluxb_stream_t stream_) {
+  FLUXB_REQUIRE(comm != nullptr && tokens != nullptr && weights != nullptr && splits_dev != nullptr &&
+                    scatter_index_dev != nullptr && out != nullptr, "moe_scatter_gemm_static: NULL argument");
+  FLUXB_REQUIRE(comm->world == 1, "moe_scatter_gemm_static: needs a world-1 communicator (got world=%d)", comm->world);
+  FLUXB_REQUIRE(is_16bit(in_dtype) || is_fp8(in_dtype), "moe_scatter_gemm_static: input dtype %d unsupported", in_dtype);
+  FLUXB_REQUIRE(out_dtype == FLUXB_BF16 || out_dtype == FLUXB_F16, "moe_scatter_gemm_static: output dtype %d unsupported", out_dtype);
+  FLUXB_REQUIRE(ntokens >= 1 && topk >= 1 && nexperts >= 1, "moe_scatter_gemm_static: ntokens=%d topk=%d nexperts=%d invalid",
+                ntokens, topk, nexperts);
+  const long long rows = static_cast<long long>(ntokens) * topk;
+  FLUXB_REQUIRE(rows <= FLUXB_STATIC_MAX_ROWS,
+                "moe_scatter_gemm_static: ntokens*topk = %lld exceeds the built-in table capacity of %d rows; "
+                "use fluxb_moe_ag_scatter_forward with a workspace", rows, FLUXB_STATIC_MAX_ROWS);
+  FLUXB_REQUIRE(nexperts <= FLUXB_STATIC_MAX_EXPERTS,
+                "moe_scatter_gemm_static: nexperts = %d exceeds the built-in table capacity of %d experts", nexperts,
+                FLUXB_STATIC_MAX_EXPERTS);
+  FLUXB_REQUIRE(ffn >= 8 && ffn % 8 == 0, "moe_scatter_gemm_static: ffn=%d must be a multiple of 8", ffn);
+  const int eb = dtype_bytes(in_dtype);
+  const long long row_bytes = static_cast<long long>(hidden) * eb;
+  FLUXB_REQUIRE(hidden >= 1 && row_bytes % 16 == 0,
+                "moe_scatter_gemm_static: hidden=%d gives a row pitch that is not a multiple of 16 bytes", hidden);
+  int dev = -1;
+  FLUXB_CUDA(cudaGetDevice(&dev));
+  FLUXB_REQUIRE(dev == comm->device, "moe_scatter_gemm_static: device %d is current, the communicator lives on %d", dev,
+                comm->device);
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_);
+  void* tables = nullptr;
+  int rc = static_tables_ptr(dev, &tables);
+  if (rc != FLUXB_OK) return rc;
+
+  // same table layout as the workspace form, sized for the built-in capacity
+  MoeTables tb = carve_tables(tables, FLUXB_STATIC_MAX_ROWS, FLUXB_STATIC_MAX_EXPERTS);
+  const int max_tiles = FLUXB_STATIC_MAX_ROWS / kBM + FLUXB_STATIC_MAX_EXPERTS + 1;
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.g_tiles = tb.tiles;
+  const int cg = resolve_cta_group(p, tuning);
+  const int tile_m = cg == 2 ? 2 * kBM : kBM;
+  // every table entry a later stage reads is written here first: tile list, tile count, offsets and
+  // the source-rank masks by the first kernel, the gather index of all `rows` rows by the second
+  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, nexperts, static_cast<int>(rows), max_tiles, tile_m, tb,
+                                                comm->status_dev);
+  FLUXB_CUDA(cudaGetLastError());
+  moe_route_rows_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, stream>>>(
+      scatter_index_dev, static_cast<int>(rows), topk, ntokens, nexperts, tile_m, tb);
+  FLUXB_CUDA(cudaGetLastError());
+
+  p.out_type = out_dtype == FLUXB_BF16 ? kOutBf16 : kOutF16;
+  p.M = static_cast<int>(rows);
+  p.N = ffn;
+  p.K = hidden;
+  p.nseg = 1;
+  p.seg_rows = ntokens;
+  p.epi_mode = kEpiStore;
+  p.out = out;
+  p.ldo = ffn;
+  p.alpha = 1.0f;
+  p.g_num_tiles = tb.num_tiles;
+  p.g_gather = tb.gather;
+  p.g_rows_per_expert_b = ffn;
+  p.g_expert_scale = out_scale;
+  p.g_rows_per_rank = ntokens;
+  p.g_ntokens = ntokens;
+  const int bn = resolve_block_n(comm, p, tuning, max_tiles);
+  rc = encode_tmap_2d(&p.tmap_a, tokens, in_dtype, ntokens, hidden, row_bytes, 1);
+  if (rc != FLUXB_OK) return rc;
+  rc = encode_tmap_2d(&p.tmap_b, weights, in_dtype, static_cast<long long>(nexperts) * ffn, hidden, row_bytes,
+                      cg == 2 ? bn / 2 : bn);
+  if (rc != FLUXB_OK) return rc;
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  t.block_n = bn;
+  t.cta_group = cg;
+  return launch_fused_gemm(comm, p, in_dtype, &t, stream);
+}

@@ -175,6 +175,33 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
                                  void* gathered_out, const fluxb_tuning* tuning,
                                  fluxb_stream_t stream);
 
+/* ------------------------------------- scatter + grouped GEMM, no allocation
+ * No counterpart in the reference. The single-GPU form of the MoE layer-0 product
+ *     out[scatter_index[t,k], :] = tokens[t, :] . W[expert(t,k)]^T * out_scale[expert]
+ * for callers that must not allocate device memory at call time: serving processes that hand all
+ * free device memory to their own pool at start-up (a later cudaMalloc fails or fragments the pool),
+ * and latency-critical loops that cannot afford the device-wide synchronisation an allocation may
+ * imply. The routing tables the grouped kernel needs (inverse permutation, per-expert tile list) live
+ * in a fixed device array inside the library instead of a caller-provided workspace, so the entry
+ * point itself calls no cudaMalloc / cudaFree and no allocating library routine.
+ * Limits: ntokens * topk <= FLUXB_STATIC_MAX_ROWS and nexperts <= FLUXB_STATIC_MAX_EXPERTS; larger
+ * problems are rejected with FLUXB_ERR_INVALID. Every GPU that loads the library holds the array
+ * (about 300 KB) until the process exits.
+ * The first call on a device looks up the array's device address and configures the kernel; make
+ * that first call outside any stream capture. All calls on a device share the one array, which keeps
+ * the previous call's contents (everything a call reads is rewritten by that call first): calls that
+ * overlap on the GPU (different streams) race and must be serialised by the caller.
+ * `comm` is a world-1 communicator whose device is current; tokens [ntokens, hidden], weights
+ * [nexperts, ffn, hidden], splits_dev int32 [nexperts], scatter_index_dev int32 [ntokens, topk],
+ * out_scale fp32 [nexperts] or NULL, out [ntokens*topk, ffn]. */
+#define FLUXB_STATIC_MAX_ROWS 65536
+#define FLUXB_STATIC_MAX_EXPERTS 256
+int fluxb_moe_scatter_gemm_static(fluxb_comm_t comm, const void* tokens, int ntokens, int hidden,
+                                  const void* weights, int nexperts, int ffn, int topk,
+                                  const int* splits_dev, const int* scatter_index_dev,
+                                  const float* out_scale, void* out, int in_dtype, int out_dtype,
+                                  const fluxb_tuning* tuning, fluxb_stream_t stream);
+
 /* ------------------------------------------------------ MoE gather + RS
  * Replaces GemmGroupedV3GatherRS
  * (src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:549-584, :595-820).
