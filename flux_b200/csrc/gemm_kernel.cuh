@@ -418,7 +418,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       // warps; wait (bounded) for that, then add the sum to the accumulator and write the final rows.
       const bool own = p.epi_mode == kEpiRsPush && tc.seg == p.rank;
       const float* sum_row = nullptr;
-      if (own) {
+      if (own && tc.rows > 0) {  // a pair's second half may lie entirely past the segment: nothing to wait for
         int okw = 1;
         if (lane == 0)
           okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 1, s_abort, kStatusTimeoutReduce,

@@ -128,3 +128,43 @@ def moe_case(rank, world, cfgs, dtype_name):
             # tolerance of the reference's own test for bf16 (test_moe_gather_rs.py:397-411): 2e-2
             err1 = golden.max_rel_err(out1, ref1)
             assert err1 <= 2e-2, f"rank {rank} cfg {ci} call {it}: layer 1 max rel err {err1}"
+
+
+def fp8_case(rank, world, shapes):
+    """FP8 e4m3 AG-GEMM with per-row input scales (all-gathered by the op) and per-channel weight scales,
+    and FP8 GEMM-RS, against the dequantised oracle (tolerance 3e-2)."""
+    import flux_b200 as flux
+    from oracle import golden
+
+    group = dist.group.WORLD
+    flux.init_flux_shm(group)
+    comm = flux.get_comm(group)
+    comm.set_timeout_ms(5000)
+    f8 = torch.float8_e4m3fn
+    for it, (m_local, n, k) in enumerate(shapes):
+        g = torch.Generator().manual_seed(555 + rank + 13 * it)
+        a = torch.randn(m_local, k, generator=g)
+        b = torch.randn(n, k, generator=g) * 0.02
+        qa, sa = golden.quantize_fp8_rows(a)
+        qb, sb = golden.quantize_fp8_rows(b)
+        ref, _ = golden.ag_gemm_dist(group, qa, qb, None, sa, sb)
+        op = flux.AGKernel(group, 1, m_local * world, n, k, f8)
+        out = op.forward(qa.cuda(), qb.cuda(), input_scale=sa.cuda(), weight_scale=sb.cuda())
+        torch.cuda.synchronize()
+        comm.check_status()
+        assert out.dtype == torch.bfloat16
+        err = golden.max_rel_err(out, ref)
+        assert err <= 3e-2, f"rank {rank} call {it}: fp8 AG-GEMM max rel err {err}"
+        # GEMM-RS: A [M, k] fp8 with per-row scale, B [n, k] fp8 with per-channel scale
+        m = m_local * world
+        a2 = torch.randn(m, k, generator=g)
+        qa2, sa2 = golden.quantize_fp8_rows(a2)
+        part = golden._rs_partial(qa2, qb, None, sa2, sb).float().contiguous()
+        dist.all_reduce(part, group=group)
+        mpr = m // world
+        rs = flux.GemmRS(group, 1, m, n, f8)
+        out2 = rs.forward(qa2.cuda(), qb.cuda(), input_scale=sa2.cuda(), weight_scale=sb.cuda())
+        torch.cuda.synchronize()
+        comm.check_status()
+        err2 = golden.max_rel_err(out2, part[rank * mpr:(rank + 1) * mpr])
+        assert err2 <= 3e-2, f"rank {rank} call {it}: fp8 GEMM-RS max rel err {err2}"

@@ -133,6 +133,48 @@ def test_argument_errors(flux):
         rs.forward(a2.cuda(), b.cuda())  # M > max_m
 
 
+@pytest.mark.parametrize("m,n,k", [(128, 256, 128), (256, 512, 1024), (200, 264, 144), (1024, 1536, 2048)])
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_fp8_gemm_with_row_and_channel_scales(flux, m, n, k, cta_group):
+    """FP8 e4m3 operands, per-row input scale and per-output-channel weight scale applied in the epilogue,
+    bf16 out; oracle = bf16 matmul of the e4m3 values times the scales (test_ag_kernel.py:119-124,143-147)."""
+    g = torch.Generator().manual_seed(m + n + k)
+    a = torch.randn(m, k, generator=g)
+    b = torch.randn(n, k, generator=g) * 0.02
+    qa, sa = golden.quantize_fp8_rows(a)
+    qb, sb = golden.quantize_fp8_rows(b)
+    op = flux.AGKernel(None, 1, m, n, k, torch.float8_e4m3fn)
+    out = op.gemm_only(qa.cuda(), qb.cuda(), input_scale=sa.cuda(), weight_scale=sb.cuda(),
+                       tuning={"cta_group": cta_group})
+    torch.cuda.synchronize()
+    op.comm.check_status()
+    ref, _ = golden.ag_gemm_single([qa], qb, input_scales=[sa], weight_scale=sb)
+    assert out.dtype == torch.bfloat16
+    assert golden.max_rel_err(out, ref) <= FP8_TOL
+    # scalar scales, the reference's own fp8 form (cpp_mod.pyi:439-440)
+    one_a, one_b = torch.tensor([0.5]), torch.tensor([2.0])
+    out2 = op.gemm_only(qa.cuda(), qb.cuda(), input_scale=one_a.cuda(), weight_scale=one_b.cuda())
+    ref2, _ = golden.ag_gemm_single([qa], qb, input_scales=[one_a], weight_scale=one_b)
+    assert golden.max_rel_err(out2, ref2) <= FP8_TOL
+
+
+def test_fp8_rejects_transpose_weight(flux):
+    op = flux.AGKernel(None, 1, 128, 128, 128, torch.float8_e4m3fn)
+    q = torch.zeros(128, 128).to(torch.float8_e4m3fn).cuda()
+    with pytest.raises(RuntimeError):
+        op.forward(q, q, transpose_weight=True)
+
+
+def test_transpose_weight(flux):
+    m, n, k = 256, 384, 512
+    a, b = _mk(m, n, k, torch.bfloat16, seed=9)
+    op = flux.AGKernel(None, 1, m, n, k, torch.bfloat16)
+    out = op.forward(a.cuda(), b.t().contiguous().cuda(), transpose_weight=True)  # weight given as [K, N]
+    torch.cuda.synchronize()
+    ref, _ = golden.ag_gemm_single([a], b)
+    assert golden.max_rel_err(out, ref) <= BF16_TOL
+
+
 def _need(n):
     if gpu_count() < n:
         pytest.skip(f"needs {n} GPUs")
@@ -154,3 +196,22 @@ def test_gemm_rs_multi_rank(with_bias):
     w = 1 << (w.bit_length() - 1)
     shapes = [(512, 512, 512), (256, 512, 256), (8 * w, 512, 512), (200 * w, 512, 1024), (512, 512, 512)]
     run_distributed(dist_cases.gemm_rs_case, w, shapes, "bfloat16", with_bias, None)
+
+
+def test_fp8_multi_rank():
+    _need(2)
+    w = min(gpu_count(), 8)
+    w = 1 << (w.bit_length() - 1)
+    run_distributed(dist_cases.fp8_case, w, [(256, 512, 512), (100, 264, 256)])
+
+
+def test_stress_random_m_multi_rank():
+    """Random local M per call on one op, as the reference's stress scripts do
+    (test/python/stress/stress_ag_gemm.py:218-310): no hang, every call checked."""
+    _need(2)
+    w = min(gpu_count(), 8)
+    w = 1 << (w.bit_length() - 1)
+    g = torch.Generator().manual_seed(42)
+    ms = [int(x) for x in torch.randint(1, 513, (10,), generator=g)]
+    run_distributed(dist_cases.ag_gemm_case, w, [(m, 512, 512) for m in ms], "bfloat16", False, None)
+    run_distributed(dist_cases.gemm_rs_case, w, [(m * w, 512, 256) for m in ms], "bfloat16", False, None)
