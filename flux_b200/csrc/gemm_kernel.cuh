@@ -418,10 +418,17 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       // warps; wait (bounded) for that, then add the sum to the accumulator and write the final rows.
       const bool own = p.epi_mode == kEpiRsPush && tc.seg == p.rank;
       const float* sum_row = nullptr;
+      if (own && lane == 0 && pending_cnt != nullptr) {
+        // Never hold back a publish while waiting on the peers: they may be waiting for exactly this one.
+        bulk_wait_all();
+        fence_acq_rel_sys();
+        red_add_release_sys(pending_cnt, 1);
+        pending_cnt = nullptr;
+      }
       if (own && tc.rows > 0) {  // a pair's second half may lie entirely past the segment: nothing to wait for
         int okw = 1;
         if (lane == 0)
-          okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 1, s_abort, kStatusTimeoutReduce,
+          okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 4, s_abort, kStatusTimeoutReduce,
                              budget) ? 1 : 0;
         okw = __shfl_sync(0xffffffffu, okw, 0);
         if (!okw) break;
@@ -644,19 +651,23 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       }
     }
       if (p.epi_mode == kEpiRsPush) {
-      // Owner side of the reduce-scatter: for every 128 x BN tile of this rank's rows wait (bounded)
-      // until every peer has published its partial (4 arrivals per peer: one per epilogue warp), sum
-      // the peers' partials in fp32 in rank order into this rank's own slot, and raise the tile's
-      // ready flag for the epilogue. The peers compute this rank's rows before their own, so this
-      // work is spread over the kernel and finished before the own tiles are.
+      // Owner side of the reduce-scatter. Work item = 32 rows of one 128 x BN tile of this rank's rows:
+      // wait (bounded) until every peer has published the tile (4 arrivals per peer: one per epilogue
+      // warp), sum the peers' partials in fp32 in rank order into this rank's own slot, and add 1 to the
+      // tile's ready count (the epilogue of the own tile waits for 4). Items are spread over all CTAs and
+      // every source's loads are in flight together. The peers compute this rank's rows before their own,
+      // so this work is spread over the kernel and finished before the own tiles are.
       const int ctid = threadIdx.x - 6 * 32;  // 0..127
       const int m_chunks = (p.seg_rows + kBM - 1) / kBM;
-      const int total_r = m_chunks * n_tiles;
-      const int vec_per_row = BN / 4;
+      const int total_items = m_chunks * n_tiles * 4;
+      constexpr int kVecPerRow = BN / 4;                 // float4 per tile row
+      constexpr int kVecPerItem = 32 * kVecPerRow;       // float4 per work item
       const long long slot = static_cast<long long>(p.seg_rows) * p.N;
       float* sum_base = p.rs_stage[p.rank];  // this rank's slot in its own staging
       volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
-      for (int rt = blockIdx.x; rt < total_r; rt += gridDim.x) {
+      for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+        const int quarter = item & 3;
+        const int rt = item >> 2;
         const int c = rt % m_chunks;
         const int nt = rt / m_chunks;
         const int tix = c * n_tiles + nt;
@@ -666,44 +677,45 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         const int okr = *s_flag;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (!okr) break;
-        const int rows = imin(kBM, p.seg_rows - c * kBM);
+        const int row_base = c * kBM + quarter * 32;
+        const int rows = imax(0, imin(32, p.seg_rows - row_base));
         const int n0 = nt * BN;
-        const int nvec = rows * vec_per_row;
-        for (int i0 = ctid; i0 < nvec; i0 += 4 * 128) {
-          float4 acc[4];
-          long long off[4];
+        for (int i0 = ctid; i0 < kVecPerItem; i0 += 2 * 128) {
+          long long off[2];
 #pragma unroll
-          for (int u = 0; u < 4; ++u) {
+          for (int u = 0; u < 2; ++u) {
             const int i = i0 + u * 128;
-            const int r = i / vec_per_row;
-            const int col = n0 + (i - r * vec_per_row) * 4;
-            off[u] = (i < nvec && col < p.N) ? static_cast<long long>(c * kBM + r) * p.N + col : -1;
-            acc[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            const int r = i / kVecPerRow;
+            const int col = n0 + (i - r * kVecPerRow) * 4;
+            off[u] = (i < kVecPerItem && r < rows && col < p.N) ? static_cast<long long>(row_base + r) * p.N + col : -1;
           }
-          for (int sr = 0; sr < p.world; ++sr) {
-            if (sr == p.rank) continue;
-            float4 v[4];
+          float4 v[kMaxWorld][2];
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (off[u] >= 0) v[u] = *reinterpret_cast<const float4*>(p.rs_local_stage + sr * slot + off[u]);
+          for (int sr = 0; sr < kMaxWorld; ++sr)
 #pragma unroll
-            for (int u = 0; u < 4; ++u)
-              if (off[u] >= 0) {
-                acc[u].x += v[u].x;
-                acc[u].y += v[u].y;
-                acc[u].z += v[u].z;
-                acc[u].w += v[u].w;
+            for (int u = 0; u < 2; ++u)
+              if (sr < p.world && sr != p.rank && off[u] >= 0)
+                v[sr][u] = *reinterpret_cast<const float4*>(p.rs_local_stage + sr * slot + off[u]);
+#pragma unroll
+          for (int u = 0; u < 2; ++u) {
+            if (off[u] < 0) continue;
+            float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+            for (int sr = 0; sr < kMaxWorld; ++sr)
+              if (sr < p.world && sr != p.rank) {
+                acc.x += v[sr][u].x;
+                acc.y += v[sr][u].y;
+                acc.z += v[sr][u].z;
+                acc.w += v[sr][u].w;
               }
+            *reinterpret_cast<float4*>(sum_base + off[u]) = acc;
           }
-#pragma unroll
-          for (int u = 0; u < 4; ++u)
-            if (off[u] >= 0) *reinterpret_cast<float4*>(sum_base + off[u]) = acc[u];
         }
         __threadfence();
         asm volatile("bar.sync 1, 128;" ::: "memory");
         if (ctid == 0) {
           __threadfence();
-          st_release_sys(p.rs_local_ready + tix, 1);
+          red_add_release_sys(p.rs_local_ready + tix, 1);
         }
       }
     }
