@@ -347,6 +347,109 @@ def run_kernel_only(args):
                       "tflops": 2.0 * m * n * k / (ms * 1e-3) / 1e12}), flush=True)
 
 
+def run_moe(args):
+    """Secondary workload: the MoE MLP of the reference's examples (8192 tokens, hidden 4096, 8 experts,
+    ffn 14336 sharded over TP, top-2): layer 0 = GemmGroupedV3AGScatter, layer 1 = GemmGroupedV3GatherRS,
+    beside the torch sequence (all_gather + index_select + per-expert matmul; per-expert matmul +
+    top-k sum + reduce_scatter) on the same GPUs. Prints one JSON line on rank 0."""
+    rank, world, local = _env()
+    torch.cuda.set_device(local)
+    group = None
+    if world > 1:
+        os.environ.pop("NCCL_DEBUG", None)
+        dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world)
+        group = dist.group.WORLD
+    import flux_b200 as flux
+
+    flux.init_flux_shm(group)
+    comm = flux.get_comm(group)
+    T, H, E, FFN, TOPK = 8192, 4096, 8, 14336, 2
+    ffn_l = FFN // world
+    g = torch.Generator(device="cuda").manual_seed(SEED)  # routing is global: same seed on every rank
+    logits = torch.randn(T, E, generator=g, device="cuda")
+    w, chosen = torch.topk(torch.softmax(logits, -1), TOPK, dim=-1)
+    chosen = chosen.to(torch.int32)
+    si, splits = flux.calc_scatter_index(chosen, torch.empty(E), return_splits=True)
+    gi, ti = flux.calc_gather_index(si)
+    vec = w.reshape(-1)[(gi.long() * TOPK + ti.long())].contiguous().float()
+    splits_cpu = splits.cpu()
+    gr = torch.Generator(device="cuda").manual_seed(SEED + 1 + rank)
+    tok = torch.randn(T // world, H, generator=gr, device="cuda").to(torch.bfloat16)
+    w0 = (torch.randn(E, ffn_l, H, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
+    w1 = (torch.randn(E, H, ffn_l, generator=gr, device="cuda") * 0.02).to(torch.bfloat16)
+    env = flux.DistEnvTPWithEP(group, 1, None)
+    l0 = flux.GemmGroupedV3AGScatter(env, flux.MoeArguments(T, H, FFN, E, TOPK, torch.bfloat16))
+    l1 = flux.GemmGroupedV3GatherRS(E, T * TOPK, H, TOPK, rank, world, world, 1)
+    act = torch.empty((T * TOPK, ffn_l), dtype=torch.bfloat16, device="cuda")
+
+    def fused():
+        l0.forward(tok, w0, splits, si, outputs_buf=act)
+        return l1.forward_gather_rs(act, w1, splits_cpu, si.view(-1), output_vec_scale=vec)
+
+    full_tok = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    offs = [0] + torch.cumsum(splits_cpu, 0).tolist()
+    rs_out = torch.empty((T // world, H), dtype=torch.bfloat16, device="cuda")
+
+    def unfused():
+        if world > 1:
+            dist.all_gather_into_tensor(full_tok, tok)
+            x = full_tok
+        else:
+            x = tok
+        scat = x.index_select(0, gi.long())
+        h = torch.empty((T * TOPK, ffn_l), dtype=torch.bfloat16, device="cuda")
+        for e in range(E):
+            if offs[e + 1] > offs[e]:
+                torch.matmul(scat[offs[e]:offs[e + 1]], w0[e].t(), out=h[offs[e]:offs[e + 1]])
+        o = torch.empty((T * TOPK, H), dtype=torch.bfloat16, device="cuda")
+        for e in range(E):
+            if offs[e + 1] > offs[e]:
+                torch.matmul(h[offs[e]:offs[e + 1]], w1[e].t(), out=o[offs[e]:offs[e + 1]])
+        o = (o.float() * vec[:, None]).to(torch.bfloat16)
+        red = o[si.view(-1).long()].view(T, TOPK, H).sum(1)
+        if world > 1:
+            dist.reduce_scatter_tensor(rs_out, red)
+            return rs_out
+        return red
+
+    def timeit(fn):
+        for _ in range(max(args.warmup, 3)):
+            r = fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            r = fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return _max_over_ranks(e0.elapsed_time(e1) / args.steps, world), r
+
+    ms_l0, _ = timeit(lambda: l0.forward(tok, w0, splits, si, outputs_buf=act))
+    ms_l1, _ = timeit(lambda: l1.forward_gather_rs(act, w1, splits_cpu, si.view(-1), output_vec_scale=vec))
+    ms_f, rf = timeit(fused)
+    ms_u, ru = timeit(unfused)
+    comm.check_status()
+    agree = float((rf.float() - ru.float()).abs().max() / ru.float().abs().max().clamp_min(1e-30))
+    flops_layer = 2.0 * T * TOPK * ffn_l * H
+    if rank == 0:
+        print(json.dumps({
+            "metric": "MoE MLP (AG+scatter grouped GEMM, grouped GEMM+gather-RS) aggregate TFLOP/s",
+            "value": 2 * flops_layer * world / (ms_f * 1e-3) / 1e12, "unit": "TFLOP/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_f, "higher_is_better": True,
+            "scaling": "strong", "dtype": "bf16", "data": "synthetic (seeded)",
+            "config": {"workload": f"MoE T={T} H={H} E={E} ffn={FFN} top{TOPK}, bf16, TP={world}"},
+            "layer0": {"ms": ms_l0, "tflops_per_gpu": flops_layer / (ms_l0 * 1e-3) / 1e12},
+            "layer1": {"ms": ms_l1, "tflops_per_gpu": flops_layer / (ms_l1 * 1e-3) / 1e12},
+            "unfused": {"what": "torch: all_gather + index_select + per-expert matmul; per-expert matmul + "
+                                "top-k sum + reduce_scatter", "ms_per_step": ms_u},
+            "speedup_vs_unfused": ms_u / ms_f, "max_rel_diff_vs_unfused": agree}), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
 def _cpu_sample_run(m_s, n_s, k_s, iters=1):
     """The oracle's AG-GEMM + GEMM-RS sequence on the host cores for a slice of the workload."""
     from oracle import golden
@@ -422,12 +525,15 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--cpu-seconds", type=float, default=15.0)
     ap.add_argument("--kernel-only", action="store_true", help="small single-GPU case for profiler captures")
+    ap.add_argument("--workload", default="dense", choices=["dense", "moe"], help="dense MLP (headline) or MoE MLP")
     ap.add_argument("--block-n", type=int, default=0, help="kernel-only: output tile width (0 = library default)")
     ap.add_argument("--group-m", type=int, default=0, help="kernel-only: rasterisation band height (0 = default)")
     ap.add_argument("--cta-group", type=int, default=0, help="kernel-only: 1 or 2 CTAs per tile (0 = default)")
     args = ap.parse_args()
     if args.kernel_only:
         run_kernel_only(args)
+    elif args.workload == "moe" and args.impl == "ours":
+        run_moe(args)
     elif args.impl == "reference":
         run_reference(args)
     else:

@@ -84,7 +84,7 @@ SIGNATURES = {
     "fluxb_gemm_rs_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _tun, _vp]),
     "fluxb_moe_scatter_index": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "fluxb_moe_gather_index": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
-    "fluxb_moe_ag_scatter_workspace_bytes": (_sz, [_i, _i, _i]),
+    "fluxb_moe_ag_scatter_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "fluxb_moe_ag_scatter_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _pp, _pp, _vp, _pp]),
     "fluxb_moe_ag_scatter_destroy": (_i, [_vp]),
     "fluxb_moe_ag_scatter_forward": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _tun, _vp]),

@@ -112,6 +112,13 @@ struct GemmParams {
   const int* g_scatter_rows;    // optional: sorted row -> output row (null = identity)
   int g_rows_per_rank;          // tokens per source rank (for need_mask -> flags)
   int g_ntokens;                // rows of the gathered A matrix
+  // grouped mode, permute form: the comm warps copy every gathered token row to its top-k places in
+  // an expert-sorted buffer (which tmap_a then describes) and count finished work items per source rank
+  uint8_t* g_sorted;              // [rows, K] sorted activations, null = gather4 form
+  int* g_perm_done;               // [world] finished permute items per source rank (local, zeroed per call)
+  const int* g_scatter_index;     // [tokens, topk]
+  const uint8_t* g_tokens;        // gathered tokens [tokens, K] (this rank's gather buffer, or the input at world 1)
+  int g_topk;
   // status / bounded waits
   int* status;
   unsigned long long timeout_ns;
@@ -275,7 +282,66 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   const int total_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + BKE - 1) / BKE;
 
-  if (warp == 0) {
+  if (warp == 0 && p.g_gather != nullptr) {
+    // ------------------------------------------------- TMA, row-gather form (MoE layer 0)
+    // All 32 lanes work: lane l keeps the four source rows of rows 4l..4l+3 of the tile in registers
+    // for the whole tile and issues its own gather4 per stage; lane 0 also arms the barrier and loads B.
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
+      TileCoord tc;
+      decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
+      if (p.ag_flags != nullptr) {
+        // wait for every chunk of every source rank the tile touches (lane 0 polls, all lanes follow)
+        int okw = 1;
+        if (lane == 0) {
+          const int chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
+          for (int r = 0; okw && r < p.world; ++r) {
+            if (!((tc.need_mask >> r) & 1)) continue;
+            for (int c = 0; okw && c < chunks; ++c)
+              okw = flag_wait_eq(p.ag_flags + r * p.ag_flag_stride + c, p.ag_expected, s_abort,
+                                 kStatusTimeoutFlag, budget) ? 1 : 0;
+          }
+        }
+        okw = __shfl_sync(0xffffffffu, okw, 0);
+        if (!okw) break;
+        fence_proxy_async();
+      }
+      // rows past the tile end re-read a valid row (their results are never stored)
+      const int* gi = p.g_gather + (tc.rows > 0 ? tc.row0 : 0);
+      const int nr = tc.rows > 0 ? tc.rows : 1;
+      const int r0 = lane * 4;
+      const int i0 = gi[r0 < nr ? r0 : 0];
+      const int i1 = gi[r0 + 1 < nr ? r0 + 1 : 0];
+      const int i2 = gi[r0 + 2 < nr ? r0 + 2 : 0];
+      const int i3 = gi[r0 + 3 < nr ? r0 + 3 : 0];
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (!mbar_wait(bar_empty(stage), phase ^ 1u, s_abort, kStatusTimeoutSmemEmpty, budget, 40)) {
+          ok = false;
+          break;
+        }
+        uint32_t fb = bar_full(stage);
+        if (CTA2) {
+          if (leader && lane == 0) mbar_arrive_expect_tx(fb, 2 * L::kStageBytes);
+          fb = mapa_u32(fb, 0);
+        } else if (lane == 0) {
+          mbar_arrive_expect_tx(fb, L::kStageBytes);
+        }
+        if (CTA2) tma_gather4_2d_2cta(smem_a(stage) + lane * 4 * kRowBytes, &p.tmap_a, fb, kb * BKE, i0, i1, i2, i3);
+        else tma_gather4_2d(smem_a(stage) + lane * 4 * kRowBytes, &p.tmap_a, fb, kb * BKE, i0, i1, i2, i3);
+        if (lane == 0) {
+          if (CTA2) tma_load_2d_2cta(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0 + half * (BN / 2));
+          else tma_load_2d(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0);
+        }
+        if (++stage == STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;
+    }
+  } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA
     if (lane == 0) {
       int stage = 0;
@@ -284,21 +350,22 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
         TileCoord tc;
         decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
-        if (p.ag_flags != nullptr) {
-          if (p.g_tiles == nullptr) {
+        if (p.ag_flags != nullptr && p.g_tiles == nullptr) {
+          {
             if (tc.rows > 0 && !(p.a_own_valid && tc.seg == p.rank))
               ok = flag_wait_eq(p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk, p.ag_expected,
                                 s_abort, kStatusTimeoutFlag, budget);
-          } else {
-            // grouped: wait for every chunk of every source rank the tile touches
-            const int chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
-            for (int r = 0; ok && r < p.world; ++r) {
-              if (!((tc.need_mask >> r) & 1)) continue;
-              for (int c = 0; ok && c < chunks; ++c)
-                ok = flag_wait_eq(p.ag_flags + r * p.ag_flag_stride + c, p.ag_expected, s_abort,
-                                  kStatusTimeoutFlag, budget);
-            }
           }
+          if (!ok) break;
+          fence_proxy_async();
+        }
+        if (p.g_perm_done != nullptr) {
+          // grouped, permute form: every source rank the tile reads must be fully permuted
+          const int expected = ((p.g_rows_per_rank + kBM - 1) / kBM) *
+                               static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+          for (int r = 0; ok && r < p.world; ++r)
+            if ((tc.need_mask >> r) & 1)
+              ok = flag_wait_eq(p.g_perm_done + r, expected, s_abort, kStatusTimeoutFlag, budget);
           if (!ok) break;
           fence_proxy_async();
         }
@@ -647,6 +714,66 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         if (ctid == 0 && !skip_data) {
           fence_acq_rel_sys();
           red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk, 1);
+        }
+      }
+    }
+    if (p.g_sorted != nullptr) {
+      // MoE layer 0, permute form. Work item = (source rank, 128-token chunk, 2 KB slice of the row):
+      // wait (bounded) for the chunk's arrival counter, then copy every token row of the chunk to its
+      // top-k rows of the expert-sorted buffer (one load, top-k stores) and count the item as done for
+      // that source rank. Source ranks are taken in arrival order, this rank's own tokens first.
+      const int ctid = threadIdx.x - 6 * 32;
+      const int chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
+      const int nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+      const int per_src = chunks * nslices;
+      const int total_items = p.world * per_src;
+      volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
+      for (int u = blockIdx.x; u < total_items; u += gridDim.x) {
+        const int d = u / per_src;
+        const int rem = u - d * per_src;
+        const int chunk = rem / nslices;
+        const int ks = rem - chunk * nslices;
+        int src_rank = p.rank + d;
+        if (src_rank >= p.world) src_rank -= p.world;
+        if (p.ag_flags != nullptr) {
+          if (ctid == 0)
+            *s_flag = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk, p.ag_expected, s_abort,
+                                   kStatusTimeoutFlag, budget) ? 1 : 0;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int okp = *s_flag;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (!okp) break;
+        }
+        const int r0 = chunk * kBM;
+        const int r1 = imin(r0 + kBM, p.g_rows_per_rank);
+        const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
+        const long long b1 = (b0 + kCommSliceBytes < p.ag_row_bytes) ? b0 + kCommSliceBytes : p.ag_row_bytes;
+        const int vec_per_row = static_cast<int>((b1 - b0) >> 4);
+        if (ctid < vec_per_row) {
+          const long long tok0 = static_cast<long long>(src_rank) * p.g_rows_per_rank;
+          const uint8_t* s0 = p.g_tokens + (tok0 + r0) * p.ag_row_bytes + b0 + ctid * 16;
+          uint8_t* d0 = p.g_sorted + b0 + ctid * 16;
+          const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
+          const int nrows = r1 - r0;
+          for (int rr = 0; rr < nrows; rr += 8) {
+            uint4 val[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (rr + j < nrows) val[j] = *reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes);
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+              if (rr + j < nrows)
+                for (int k = 0; k < p.g_topk; ++k) {
+                  const long long drow = si[(rr + j) * p.g_topk + k];
+                  *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
+                }
+          }
+        }
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (ctid == 0) {
+          __threadfence();
+          red_add_release_sys(p.g_perm_done + src_rank, 1);
         }
       }
     }

@@ -219,6 +219,13 @@ moe_rs_reduce_kernel(const T* __restrict__ stage, int* cnt, T* out, int n, int t
 
 using namespace fluxb;
 
+
+// CTA pairs work on 256-row tiles of one expert: worth it once experts are tall on average.
+static int grouped_cta_group(const fluxb_tuning* tuning, long long rows, int nexperts) {
+  if (tuning != nullptr && (tuning->cta_group == 1 || tuning->cta_group == 2)) return tuning->cta_group;
+  return rows / (nexperts > 0 ? nexperts : 1) >= 512 ? 2 : 1;
+}
+
 struct fluxb_moe_ag_scatter {
   fluxb_comm* comm;
   int max_ntokens, hidden, ffn_local, nexperts, topk, in_dtype, out_dtype;
@@ -249,8 +256,11 @@ static int flag_stride_of(int full_m, int world) {
 extern "C" {
 
 // ------------------------------------------------------------------ layer 0
-size_t fluxb_moe_ag_scatter_workspace_bytes(int max_ntokens, int topk, int nexperts) {
-  return tables_bytes(static_cast<long long>(max_ntokens) * topk, nexperts);
+// [routing tables][permute counters][expert-sorted activations: max_ntokens*topk rows of `hidden` elements]
+size_t fluxb_moe_ag_scatter_workspace_bytes(int max_ntokens, int topk, int nexperts, int hidden, int in_dtype) {
+  const long long rows = static_cast<long long>(max_ntokens) * topk;
+  return tables_bytes(rows, nexperts) + 256 +
+         align_up(static_cast<size_t>(rows + kBM) * hidden * dtype_bytes(in_dtype), 256);
 }
 
 int fluxb_moe_ag_scatter_create(fluxb_comm_t comm, int max_ntokens, int hidden, int ffn_local,
@@ -325,7 +335,7 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   GemmParams p;
   memset(&p, 0, sizeof(p));
   p.g_tiles = tb.tiles;
-  const int cg = resolve_cta_group(p, tuning);
+  const int cg = grouped_cta_group(tuning, rows, op->nexperts);
   const int tile_m = cg == 2 ? 2 * kBM : kBM;
   moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, op->nexperts, static_cast<int>(rows), max_tiles, tile_m,
                                                 tb, comm->status_dev);
@@ -358,31 +368,37 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   p.alpha = 1.0f;
   p.g_tiles = tb.tiles;
   p.g_num_tiles = tb.num_tiles;
-  p.g_gather = tb.gather;
+  p.g_gather = nullptr;  // permute form: A comes from the expert-sorted buffer with plain tiled loads
   p.g_rows_per_expert_b = op->ffn_local;
   p.g_expert_scale = out_scale;
   p.g_rows_per_rank = ntokens_local;
   p.g_ntokens = static_cast<int>(ntokens);
-  const uint8_t* a_base;
+  p.g_topk = op->topk;
+  p.g_scatter_index = scatter_index_dev;
+  p.ag_row_bytes = row_bytes;
+  uint8_t* ws = static_cast<uint8_t*>(op->workspace);
+  int* perm_done = reinterpret_cast<int*>(ws + tables_bytes(max_rows, op->nexperts));
+  p.g_perm_done = perm_done;
+  p.g_sorted = ws + tables_bytes(max_rows, op->nexperts) + 256;
+  FLUXB_CUDA(cudaMemsetAsync(perm_done, 0, 256, stream));
+  uint8_t* local_gather = op->gather[comm->rank] + parity * half_gather;
   if (world == 1 && !reuse) {
-    a_base = static_cast<const uint8_t*>(tokens_shard);  // nothing to gather: read the caller's tokens in place
+    p.g_tokens = static_cast<const uint8_t*>(tokens_shard);  // nothing to gather: permute straight from the caller's tokens
   } else {
-    a_base = op->gather[comm->rank] + parity * half_gather;
+    p.g_tokens = local_gather;
   }
   if (world > 1 && !reuse) {
     p.ag_flags = op->flags[comm->rank] + parity * half_flags;
     p.ag_flag_stride = op->flag_stride;
     p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
     p.ag_src = static_cast<const uint8_t*>(tokens_shard);
-    p.ag_row_bytes = row_bytes;
     for (int r = 0; r < world; ++r) {
       p.ag_dst[r] = op->gather[r] + parity * half_gather;
       p.ag_dst_flags[r] = op->flags[r] + parity * half_flags;
     }
   }
-  if (world == 1 && reuse) a_base = op->gather[0] + parity * half_gather;
   const int bn = resolve_block_n(comm, p, tuning, max_tiles);
-  int rc = encode_tmap_2d(&p.tmap_a, a_base, op->in_dtype, ntokens, op->hidden, row_bytes, 1);
+  int rc = encode_tmap_2d(&p.tmap_a, p.g_sorted, op->in_dtype, rows, op->hidden, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
   rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * op->ffn_local,
                       op->hidden, row_bytes, cg == 2 ? bn / 2 : bn);
@@ -486,8 +502,7 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   // and uploads it, gemm_grouped_v3_gather_rs.cc:245-416)
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  p.g_tiles = reinterpret_cast<const GroupTile*>(op->workspace);  // grouped problem (pointer set for real below)
-  const int cg = resolve_cta_group(p, tuning);
+  const int cg = grouped_cta_group(tuning, m, op->nexperts);
   const int tile_m = cg == 2 ? 2 * kBM : kBM;
   std::vector<GroupTile> tiles;
   long long off = 0;

@@ -72,7 +72,8 @@ class GemmGroupedV3AGScatter:
         in_dt = fluxb_dtype(self.input_dtype)
         self._gather = SymmBuffer(self.comm, lib.fluxb_ag_gemm_gather_bytes(moe_args.max_ntokens, moe_args.hidden, in_dt))
         self._flags = SymmBuffer(self.comm, lib.fluxb_ag_gemm_flag_bytes(moe_args.max_ntokens, w))
-        self._ws = torch.zeros(lib.fluxb_moe_ag_scatter_workspace_bytes(moe_args.max_ntokens, moe_args.topk, moe_args.nexperts),
+        self._ws = torch.zeros(lib.fluxb_moe_ag_scatter_workspace_bytes(moe_args.max_ntokens, moe_args.topk, moe_args.nexperts,
+                                                                      moe_args.hidden, in_dt),
                                dtype=torch.uint8, device=self.comm.device)
         h = C.c_void_p()
         _lib.check(lib.fluxb_moe_ag_scatter_create(

@@ -163,7 +163,7 @@ int fluxb_moe_gather_index(const int* scatter_index, int ntokens, int topk, int*
  * out[scatter_index[t,k], :] = token_t . W[expert]^T * out_scale[expert].
  * gather_bufs / flag_bufs sized with the fluxb_ag_gemm_* helpers
  * (full_m = max_ntokens, k_dim = hidden). */
-size_t fluxb_moe_ag_scatter_workspace_bytes(int max_ntokens, int topk, int nexperts);
+size_t fluxb_moe_ag_scatter_workspace_bytes(int max_ntokens, int topk, int nexperts, int hidden, int in_dtype);
 int fluxb_moe_ag_scatter_create(fluxb_comm_t comm, int max_ntokens, int hidden, int ffn_local,
                                 int nexperts, int topk, int in_dtype, int out_dtype,
                                 void* const* gather_bufs, int* const* flag_bufs, void* workspace,

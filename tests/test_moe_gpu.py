@@ -50,7 +50,7 @@ def test_routing_kernels_large(flux, ntokens, topk, nexperts):
     assert torch.equal(torch.sort(si.cpu().reshape(-1)).values, torch.arange(ntokens * topk, dtype=torch.int32))
 
 
-def _moe_world1(flux, ntokens, topk, nexperts, hidden, ffn, seed, skew=False):
+def _moe_world1(flux, ntokens, topk, nexperts, hidden, ffn, seed, skew=False, tuning=None):
     g = torch.Generator().manual_seed(seed)
     logits = torch.randn(ntokens, nexperts, generator=g)
     if skew:
@@ -67,7 +67,8 @@ def _moe_world1(flux, ntokens, topk, nexperts, hidden, ffn, seed, skew=False):
     env = flux.DistEnvTPWithEP(None, 1, None)
     l0 = flux.GemmGroupedV3AGScatter(env, flux.MoeArguments(ntokens, hidden, ffn, nexperts, topk, torch.bfloat16))
     gathered = torch.empty_like(tok, device="cuda")
-    out0 = l0.forward(tok.cuda(), w0.cuda(), splits.cuda(), si.cuda(), output_scale=oscale.cuda(), allgather_output=gathered)
+    out0 = l0.forward(tok.cuda(), w0.cuda(), splits.cuda(), si.cuda(), output_scale=oscale.cuda(), allgather_output=gathered,
+                      tuning=tuning)
     torch.cuda.synchronize()
     l0.comm.check_status()
     ref0, _ = golden.moe_ag_scatter_single([tok], w0, splits, si, oscale)
@@ -80,7 +81,8 @@ def _moe_world1(flux, ntokens, topk, nexperts, hidden, ffn, seed, skew=False):
     assert golden.max_rel_err(outs[1], ref_b) <= 1e-2
     l1 = flux.GemmGroupedV3GatherRS(nexperts, ntokens * topk, hidden, topk, 0, 1, 1, 1)
     vec = rw.reshape(-1)[(gi.long() * topk + ti.long())].contiguous()
-    out1 = l1.forward_gather_rs(ref0.cuda(), w1.cuda(), splits, si.reshape(-1).cuda(), output_vec_scale=vec.cuda())
+    out1 = l1.forward_gather_rs(ref0.cuda(), w1.cuda(), splits, si.reshape(-1).cuda(), output_vec_scale=vec.cuda(),
+                                tuning=tuning)
     torch.cuda.synchronize()
     l1.comm.check_status()
     ref1 = golden.moe_gather_rs_single([ref0], [w1], splits, si, topk, output_vec_scales=[vec])[0]
@@ -100,6 +102,13 @@ def _moe_world1(flux, ntokens, topk, nexperts, hidden, ffn, seed, skew=False):
                                                               (1024, 2, 8, 1024, 512), (96, 4, 32, 256, 128)])
 def test_moe_world1(flux, ntokens, topk, nexperts, hidden, ffn):
     _moe_world1(flux, ntokens, topk, nexperts, hidden, ffn, seed=ntokens + nexperts)
+
+
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_moe_world1_tile_shapes(flux, cta_group):
+    """Both tile shapes of the grouped kernel, with experts whose row counts are not multiples of the tile."""
+    _moe_world1(flux, 1000, 2, 4, 256, 384, seed=77 + cta_group, tuning={"cta_group": cta_group})
+    _moe_world1(flux, 4096, 2, 8, 512, 256, seed=78 + cta_group)  # default choice (pairs: 1024 rows per expert)
 
 
 def test_moe_world1_empty_and_skewed_experts(flux):
