@@ -119,6 +119,10 @@ struct GemmParams {
   const int* g_scatter_index;     // [tokens, topk]
   const uint8_t* g_tokens;        // gathered tokens [tokens, K] (this rank's gather buffer, or the input at world 1)
   int g_topk;
+  // split-K tail: the tiles of the last, partial wave are split along K over the otherwise idle
+  // workers; parts 1.. park their fp32 accumulators here, part 0 adds them before its epilogue
+  float* splitk_scratch;  // null = never split
+  int* splitk_cnt;        // [tail tile][half][epilogue warp] arrivals, self-clearing
   // status / bounded waits
   int* status;
   unsigned long long timeout_ns;
@@ -282,6 +286,39 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   const int total_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + BKE - 1) / BKE;
 
+  // Work schedule, identical in every role: worker w (a CTA, or a CTA pair) takes tiles w, w+P, ...
+  // of the full waves; if the last wave is at most half full, each of its tiles is cut along K into
+  // `split` parts and worker w takes part w % split of tail tile w / split.
+  const int full_waves = total_tiles / tile_step;
+  const int full_tiles = full_waves * tile_step;
+  const int tail_tiles = total_tiles - full_tiles;
+  int split = 1;
+  if (p.splitk_scratch != nullptr && p.g_tiles == nullptr && tail_tiles > 0 && 2 * tail_tiles <= tile_step) {
+    int sp = tile_step / tail_tiles;
+    if (sp > 8) sp = 8;
+    if (sp > num_kb / 4) sp = num_kb / 4;
+    if (sp >= 2) split = sp;
+  }
+  auto get_item = [&](int i, int& t, int& kb0, int& kb1, int& part) -> bool {
+    part = 0;
+    kb0 = 0;
+    kb1 = num_kb;
+    if (split <= 1) {
+      t = tile_first + i * tile_step;
+      return t < total_tiles;
+    }
+    if (i < full_waves) {
+      t = tile_first + i * tile_step;
+      return true;
+    }
+    if (i > full_waves || tile_first >= tail_tiles * split) return false;
+    t = full_tiles + tile_first / split;
+    part = tile_first % split;
+    kb0 = static_cast<int>(static_cast<long long>(part) * num_kb / split);
+    kb1 = static_cast<int>(static_cast<long long>(part + 1) * num_kb / split);
+    return true;
+  };
+
   if (warp == 0 && p.g_gather != nullptr) {
     // ------------------------------------------------- TMA, row-gather form (MoE layer 0)
     // All 32 lanes work: lane l keeps the four source rows of rows 4l..4l+3 of the tile in registers
@@ -347,7 +384,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
+      int t, kb0, kb1, part;
+      for (int wi = 0; ok && get_item(wi, t, kb0, kb1, part); ++wi) {
         TileCoord tc;
         decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
         if (p.ag_flags != nullptr && p.g_tiles == nullptr) {
@@ -369,7 +407,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           if (!ok) break;
           fence_proxy_async();
         }
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_empty(stage), phase ^ 1u, s_abort, kStatusTimeoutSmemEmpty, budget, 40)) {
             ok = false;
             break;
@@ -422,14 +460,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int t = tile_first; ok && t < total_tiles; t += tile_step, ++it) {
+      int t, kb0, kb1, part;
+      for (; ok && get_item(it, t, kb0, kb1, part); ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
         if (!mbar_wait(bar_tempty(acc), acc_phase ^ 1u, s_abort, kStatusTimeoutTmemEmpty, budget))
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_full(stage), phase, s_abort, kStatusTimeoutSmemFull, budget)) {
             ok = false;
             break;
@@ -440,7 +479,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
             // each UMMA consumes 32 bytes of K: advance the start address by 32 B (>>4 = 2)
-            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+            const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
             if (CTA2) {
               if (KIND == 0) umma_f16_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
               else umma_f8_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
@@ -467,13 +506,55 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     const uint32_t stage_blk0 = smem_base + L::kEpiOffset + (warp - 2) * L::kEpiWarpBytes;
     int* pending_cnt = nullptr;  // reduce-scatter: counter of the previous pushed tile, published one tile late
     int it = 0;
-    for (int t = tile_first; t < total_tiles; t += tile_step, ++it) {
+    int t, kb0, kb1, part;
+    for (; get_item(it, t, kb0, kb1, part); ++it) {
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       TileCoord tc;
       decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
       if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget, 500)) break;
       tc_fence_after();
+      // split-K tail: where this warp's 32 rows of a tail tile's partial accumulators live
+      const bool is_tail = split > 1 && it == full_waves;
+      float* sk_rows = nullptr;
+      int* sk_cnt = nullptr;
+      if (is_tail) {
+        const int tt = t - full_tiles;
+        sk_rows = p.splitk_scratch + (static_cast<long long>(tt) * (split - 1) * TILE_M + half * kBM + quad * 32 + lane) * BN;
+        sk_cnt = p.splitk_cnt + (tt * 2 + half) * 4 + quad;
+      }
+      if (is_tail && part > 0) {
+        // not the finisher: park the raw fp32 accumulators, signal, done with this item
+        float* dst = sk_rows + static_cast<long long>(part - 1) * TILE_M * BN;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          uint32_t r[32];
+          tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN + c * 32), r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(dst + c * 32 + q * 4) = make_uint4(r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
+        }
+        tc_fence_before();
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) {
+          if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
+          else mbar_arrive(bar_tempty(acc));
+          red_add_release_sys(sk_cnt, 1);
+        }
+        continue;
+      }
+      if (is_tail) {
+        // finisher: every other part of this warp's rows must have been parked
+        int okw = 1;
+        if (lane == 0) {
+          okw = flag_wait_eq(sk_cnt, split - 1, s_abort, kStatusTimeoutTmemFull, budget) ? 1 : 0;
+          if (okw) *sk_cnt = 0;  // this warp is the only reader: clear for the next launch
+        }
+        okw = __shfl_sync(0xffffffffu, okw, 0);
+        if (!okw) break;
+      }
       const bool row_ok = row_in_tile < tc.rows;
       const int grow = tc.row0 + row_in_tile;  // global / sorted row
       float row_scale = p.alpha;
@@ -538,6 +619,30 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         tmem_ld_wait();
         const int col0 = tc.n0 + c * 32;
         const bool active = row_ok && col0 < p.N;
+        if (is_tail) {
+          // add the parked partial accumulators of the other K parts, two parts' loads in flight at a time
+          for (int sp = 0; sp < split - 1; sp += 2) {
+            float4 pv[2][8];
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+              if (sp + u < split - 1) {
+                const float* src = sk_rows + static_cast<long long>(sp + u) * TILE_M * BN + c * 32;
+#pragma unroll
+                for (int q = 0; q < 8; ++q) pv[u][q] = *reinterpret_cast<const float4*>(src + q * 4);
+              }
+#pragma unroll
+            for (int u = 0; u < 2; ++u)
+              if (sp + u < split - 1) {
+#pragma unroll
+                for (int q = 0; q < 8; ++q) {
+                  r[q * 4] = __float_as_uint(__uint_as_float(r[q * 4]) + pv[u][q].x);
+                  r[q * 4 + 1] = __float_as_uint(__uint_as_float(r[q * 4 + 1]) + pv[u][q].y);
+                  r[q * 4 + 2] = __float_as_uint(__uint_as_float(r[q * 4 + 2]) + pv[u][q].z);
+                  r[q * 4 + 3] = __float_as_uint(__uint_as_float(r[q * 4 + 3]) + pv[u][q].w);
+                }
+              }
+          }
+        }
         float v[32];
 #pragma unroll
         for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_scale;

@@ -159,12 +159,27 @@ int fluxb_comm_create(int rank, int world, fluxb_comm_t* out) {
     delete c;
     FLUXB_FAIL(FLUXB_ERR_CUDA, "cudaHostGetDevicePointer failed: %s", cudaGetErrorString(e));
   }
+  // scratch of the split-K tail: one 128 x 256 fp32 tile per SM bounds every launch's need
+  const size_t sk_bytes = static_cast<size_t>(sms) * kBM * 256 * sizeof(float);
+  const size_t cnt_bytes = static_cast<size_t>(sms) * 8 * sizeof(int);
+  if (cudaMalloc(reinterpret_cast<void**>(&c->splitk_scratch), sk_bytes) != cudaSuccess ||
+      cudaMalloc(reinterpret_cast<void**>(&c->splitk_cnt), cnt_bytes) != cudaSuccess ||
+      cudaMemset(c->splitk_cnt, 0, cnt_bytes) != cudaSuccess) {
+    cudaGetLastError();
+    if (c->splitk_scratch != nullptr) cudaFree(c->splitk_scratch);
+    if (c->splitk_cnt != nullptr) cudaFree(c->splitk_cnt);
+    cudaFreeHost(c->status_host);
+    delete c;
+    FLUXB_FAIL(FLUXB_ERR_CUDA, "could not allocate the split-K scratch (%zu bytes)", sk_bytes);
+  }
   *out = c;
   return FLUXB_OK;
 }
 
 int fluxb_comm_destroy(fluxb_comm_t comm) {
   if (comm == nullptr) return FLUXB_OK;
+  if (comm->splitk_scratch != nullptr) cudaFree(comm->splitk_scratch);
+  if (comm->splitk_cnt != nullptr) cudaFree(comm->splitk_cnt);
   if (comm->status_host != nullptr) cudaFreeHost(comm->status_host);
   delete comm;
   return FLUXB_OK;
