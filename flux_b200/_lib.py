@@ -62,6 +62,7 @@ SIGNATURES = {
     "fluxb_comm_create": (_i, [_i, _i, _pp]),
     "fluxb_comm_destroy": (_i, [_vp]),
     "fluxb_comm_set_timeout_ms": (_i, [_vp, _i]),
+    "fluxb_comm_set_trace": (_i, [_vp, _vp]),
     "fluxb_status_peek": (_i, [_vp, C.POINTER(_i)]),
     "fluxb_status_clear": (_i, [_vp]),
     "fluxb_symm_alloc": (_i, [_sz, _pp, _vp]),

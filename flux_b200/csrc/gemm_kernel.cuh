@@ -123,6 +123,10 @@ struct GemmParams {
   // workers; parts 1.. park their fp32 accumulators here, part 0 adds them before its epilogue
   float* splitk_scratch;  // null = never split
   int* splitk_cnt;        // [tail tile][half][epilogue warp] arrivals, self-clearing
+  // optional timeline: 8 x u64 per CTA (globaltimer ns): 0 kernel start, 1 first operands landed,
+  // 2 last UMMA issued, 3 epilogue done, 4 comm warps done, 5 ns spent waiting on arrival flags,
+  // 6 ns the epilogue waited for "peers summed" flags, 7 work items of this CTA
+  unsigned long long* trace;
   // status / bounded waits
   int* status;
   unsigned long long timeout_ns;
@@ -246,7 +250,13 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   const int tile_first = CTA2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
   const int tile_step = CTA2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
 
+  unsigned long long* tr = p.trace != nullptr ? p.trace + static_cast<size_t>(blockIdx.x) * 8 : nullptr;
   if (threadIdx.x == 0) {
+    if (tr != nullptr) {
+      tr[0] = globaltimer_ns();
+      tr[5] = 0;
+      tr[6] = 0;
+    }
     *s_abort = 0;
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(bar_full(s), 1);
@@ -390,9 +400,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
         if (p.ag_flags != nullptr && p.g_tiles == nullptr) {
           {
-            if (tc.rows > 0 && !(p.a_own_valid && tc.seg == p.rank))
+            if (tc.rows > 0 && !(p.a_own_valid && tc.seg == p.rank)) {
+              const uint64_t w0 = tr != nullptr ? globaltimer_ns() : 0;
               ok = flag_wait_eq(p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk, p.ag_expected,
                                 s_abort, kStatusTimeoutFlag, budget);
+              if (tr != nullptr) tr[5] += globaltimer_ns() - w0;
+            }
           }
           if (!ok) break;
           fence_proxy_async();
@@ -474,6 +487,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             break;
           }
           tc_fence_after();
+          if (tr != nullptr && it == 0 && kb == kb0) tr[1] = globaltimer_ns();
           const uint64_t a_desc = make_kmajor_sw128_desc(smem_a(stage));
           const uint64_t b_desc = make_kmajor_sw128_desc(smem_b(stage));
 #pragma unroll
@@ -497,6 +511,10 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         if (ok) {
           if (CTA2) umma_commit_2cta(bar_tfull(acc), 3); else umma_commit(bar_tfull(acc));
         }
+      }
+      if (tr != nullptr) {
+        tr[2] = globaltimer_ns();
+        tr[7] = static_cast<unsigned long long>(it);
       }
     }
   } else if (warp < 6) {
@@ -575,9 +593,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       }
       if (own && tc.rows > 0) {  // a pair's second half may lie entirely past the segment: nothing to wait for
         int okw = 1;
-        if (lane == 0)
+        if (lane == 0) {
+          const uint64_t w0 = (tr != nullptr && warp == 2) ? globaltimer_ns() : 0;
           okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 4, s_abort, kStatusTimeoutReduce,
                              budget) ? 1 : 0;
+          if (tr != nullptr && warp == 2) tr[6] += globaltimer_ns() - w0;
+        }
         okw = __shfl_sync(0xffffffffu, okw, 0);
         if (!okw) break;
       }
@@ -762,6 +783,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         }
       }
     }
+    if (tr != nullptr && warp == 2 && lane == 0) tr[3] = globaltimer_ns();
     if (p.epi_mode == kEpiRsPush && lane == 0) {
       // also on the way out after a failed wait: the stores must not outlive the CTA
       bulk_wait_all();
@@ -953,6 +975,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     }
   }
 
+  if (tr != nullptr && threadIdx.x == 6 * 32) tr[4] = globaltimer_ns();
   // ------------------------------------------------------------------ teardown
   if (CTA2) cluster_sync_all(); else __syncthreads();
   const int err = *s_abort;

@@ -112,6 +112,7 @@ int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
   if (p.group_m <= 0) p.group_m = (tuning != nullptr && tuning->group_m > 0) ? tuning->group_m : 8;
   p.status = comm->status_dev;
   p.timeout_ns = comm->timeout_ns;
+  p.trace = comm->trace;
   p.splitk_scratch = comm->splitk_scratch;
   p.splitk_cnt = comm->splitk_cnt;
   p.rank = comm->rank;

@@ -62,6 +62,7 @@ struct fluxb_comm {
   int* status_dev = nullptr;   // device alias of status_host
   unsigned long long timeout_ns = 10ull * 1000 * 1000 * 1000;
   int barrier_epoch = 0;
+  unsigned long long* trace = nullptr;  // optional per-CTA timeline buffer (caller-owned device memory)
   float* splitk_scratch = nullptr;  // sm_count x 128 x 256 fp32: parked partial accumulators of split tail tiles
   int* splitk_cnt = nullptr;        // per (tail tile, half, epilogue warp) arrivals, zero between launches
 };

@@ -193,6 +193,12 @@ int fluxb_comm_set_timeout_ms(fluxb_comm_t comm, int timeout_ms) {
   return FLUXB_OK;
 }
 
+int fluxb_comm_set_trace(fluxb_comm_t comm, void* device_buffer) {
+  FLUXB_REQUIRE(comm != nullptr, "set_trace: comm is NULL");
+  comm->trace = static_cast<unsigned long long*>(device_buffer);
+  return FLUXB_OK;
+}
+
 int fluxb_status_peek(fluxb_comm_t comm, int* status) {
   FLUXB_REQUIRE(comm != nullptr && status != nullptr, "status_peek: NULL argument");
   *status = *reinterpret_cast<volatile int*>(comm->status_host);

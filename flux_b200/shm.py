@@ -144,6 +144,18 @@ class Comm:
     def set_timeout_ms(self, ms: int) -> None:
         _lib.check(_lib.load().fluxb_comm_set_timeout_ms(self.handle, int(ms)))
 
+    def enable_trace(self, on: bool = True):
+        """Per-CTA timeline of the fused kernel (see fluxb_comm_set_trace): returns the [SMs, 8] int64
+        tensor later launches fill with %globaltimer stamps, or None when switched off."""
+        if not on:
+            _lib.check(_lib.load().fluxb_comm_set_trace(self.handle, None))
+            self._trace = None
+            return None
+        sms = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self._trace = torch.zeros((sms, 8), dtype=torch.int64, device=self.device)
+        _lib.check(_lib.load().fluxb_comm_set_trace(self.handle, self._trace.data_ptr()))
+        return self._trace
+
     def status(self) -> int:
         s = C.c_int(0)
         _lib.check(_lib.load().fluxb_status_peek(self.handle, C.byref(s)))

@@ -75,6 +75,12 @@ int fluxb_device_supported(void);
 int fluxb_comm_create(int rank, int world, fluxb_comm_t* out);
 int fluxb_comm_destroy(fluxb_comm_t comm);
 int fluxb_comm_set_timeout_ms(fluxb_comm_t comm, int timeout_ms);
+/* Optional timeline of the fused kernel (the reference has only host-side profiling,
+ * python/flux/util.py:111-172): device_buffer = 8 x uint64 per CTA (64 B x SM count), filled by every
+ * later launch with %globaltimer stamps: kernel start, first operands landed, last UMMA issued, epilogue
+ * done, comm warps done, ns waited on arrival flags, ns waited on peers-summed flags, work items.
+ * NULL switches it off (default). */
+int fluxb_comm_set_trace(fluxb_comm_t comm, void* device_buffer);
 /* Device-written status word: 0 = ok, else the code of the wait that expired. */
 int fluxb_status_peek(fluxb_comm_t comm, int* status);
 int fluxb_status_clear(fluxb_comm_t comm);
