@@ -75,7 +75,7 @@ class AllGatherOption:
 
     def __repr__(self):
         return (
-            f"AllGatherOption(mode={self.mode}, fuse_sync={self.fuse_sync}, "
+            f"AllGatherOption(mode={self.mode!r}, fuse_sync={self.fuse_sync}, "
             f"use_cuda_core_local={self.use_cuda_core_local}, use_cuda_core_ag={self.use_cuda_core_ag}, "
             f"input_buffer_copied={self.input_buffer_copied}, use_read={self.use_read})"
         )
