@@ -105,6 +105,7 @@ struct GemmParams {
   int rs_out_type;
   // grouped mode
   const GroupTile* g_tiles;  // null = dense
+  const int* g_order;        // optional visiting order of the M tiles (null = table order)
   const int* g_num_tiles;    // device scalar
   const int* g_gather;       // sorted row -> source row of A (null: A rows are already sorted)
   int g_rows_per_expert_b;   // rows of B per expert (= N)
@@ -191,9 +192,10 @@ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_ti
     tc.need_mask = 0;
     tc.expert = 0;
   } else {
-    const GroupTile g = p.g_tiles[m_idx];
+    const int mi = p.g_order != nullptr ? p.g_order[m_idx] : m_idx;
+    const GroupTile g = p.g_tiles[mi];
     tc.seg = 0;
-    tc.chunk = m_idx;
+    tc.chunk = mi;
     tc.row0 = g.a_row0 + half * kBM;
     tc.rows = imax(0, imin(kBM, g.rows - half * kBM));
     tc.expert = g.expert;
@@ -530,7 +532,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       const uint32_t acc_phase = (it >> 1) & 1;
       TileCoord tc;
       decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
-      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget, 500)) break;
+      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget, 2000)) break;
       tc_fence_after();
       // split-K tail: where this warp's 32 rows of a tail tile's partial accumulators live
       const bool is_tail = split > 1 && it == full_waves;
@@ -780,6 +782,15 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             red_add_release_sys(pending_cnt, 1);
           }
           pending_cnt = (!own && tc.rows > 0) ? p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx : nullptr;
+          // Exception: rows of the previous rank are the last ones it is waiting for before it starts its
+          // own tiles (every rank computes its own rows last), so their publish is latency-critical.
+          const int prev_rank = p.rank == 0 ? p.nseg - 1 : p.rank - 1;
+          if (pending_cnt != nullptr && tc.seg == prev_rank) {
+            bulk_wait_all();
+            fence_acq_rel_sys();
+            red_add_release_sys(pending_cnt, 1);
+            pending_cnt = nullptr;
+          }
         }
       }
     }
@@ -892,7 +903,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
               if (rr + j < nrows)
                 for (int k = 0; k < p.g_topk; ++k) {
                   const long long drow = si[(rr + j) * p.g_topk + k];
-                  *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
+                  if (drow >= 0 && drow < p.M)  // a corrupt routing entry must not become a wild store
+                    *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
                 }
           }
         }

@@ -30,6 +30,7 @@ struct MoeTables {
   int* expert_off;  // [E+1]
   int* tile_base;   // [E+1]
   int* gather;      // [max_rows]
+  int* order;       // [max tiles] visiting order of the tiles
 };
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -40,6 +41,7 @@ static size_t tables_bytes(long long max_rows, int nexperts) {
   b += 256;                                                 // num_tiles
   b += align_up((nexperts + 1) * sizeof(int), 256) * 2;     // expert_off, tile_base
   b += align_up(static_cast<size_t>(max_rows) * sizeof(int), 256);  // gather
+  b += align_up((max_rows / kBM + nexperts + 1) * sizeof(int), 256);  // order
   return b;
 }
 
@@ -55,6 +57,8 @@ static MoeTables carve_tables(void* ws, long long max_rows, int nexperts) {
   t.tile_base = reinterpret_cast<int*>(p);
   p += align_up((nexperts + 1) * sizeof(int), 256);
   t.gather = reinterpret_cast<int*>(p);
+  p += align_up(static_cast<size_t>(max_rows) * sizeof(int), 256);
+  t.order = reinterpret_cast<int*>(p);
   return t;
 }
 
@@ -116,6 +120,28 @@ __global__ void moe_route_rows_kernel(const int* __restrict__ scatter_index, int
   atomicOr(&t.tiles[tile].need_mask, 1 << (token / tokens_per_rank));
 }
 
+// Visiting order of the tiles: stable counting sort by how late the tile's farthest source rank
+// arrives (this rank's own tokens first, then rank+1, ...), so that early tiles need early data.
+__global__ void moe_order_tiles_kernel(MoeTables t, int rank, int world) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const int n = *t.num_tiles;
+  int count[kMaxWorld + 1];
+  for (int i = 0; i <= kMaxWorld; ++i) count[i] = 0;
+  auto key_of = [&](int mask) {
+    int key = 0;
+    for (int r = 0; r < world; ++r)
+      if ((mask >> r) & 1) {
+        int d = r - rank;
+        if (d < 0) d += world;
+        if (d > key) key = d;
+      }
+    return key;
+  };
+  for (int i = 0; i < n; ++i) count[key_of(t.tiles[i].need_mask) + 1] += 1;
+  for (int i = 1; i <= kMaxWorld; ++i) count[i] += count[i - 1];
+  for (int i = 0; i < n; ++i) t.order[count[key_of(t.tiles[i].need_mask)]++] = i;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
@@ -134,7 +160,7 @@ struct PushTargets {
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_topk_push_kernel(const T* __restrict__ inter, const int* __restrict__ scatter_index, int topk, int n,
-                     int tokens_per_rank, int rank, int world, PushTargets tg) {
+                     int total_rows, int tokens_per_rank, int rank, int world, PushTargets tg) {
   const int blocks_per_owner = (tokens_per_rank + kTokBlock - 1) / kTokBlock;
   const int total = world * blocks_per_owner;
   const int nvec = n / 8;
@@ -151,6 +177,7 @@ moe_topk_push_kernel(const T* __restrict__ inter, const int* __restrict__ scatte
         float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
         for (int k = 0; k < topk; ++k) {
           const int row = scatter_index[token * topk + k];
+          if (row < 0 || row >= total_rows) continue;  // a corrupt routing entry must not become a wild load
           const uint4 raw = *reinterpret_cast<const uint4*>(inter + static_cast<long long>(row) * n + v * 8);
           const T* e = reinterpret_cast<const T*>(&raw);
 #pragma unroll
@@ -343,6 +370,11 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   moe_route_rows_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, stream>>>(
       scatter_index_dev, static_cast<int>(rows), op->topk, ntokens_local, op->nexperts, tile_m, tb);
   FLUXB_CUDA(cudaGetLastError());
+  if (world > 1) {
+    moe_order_tiles_kernel<<<1, 32, 0, stream>>>(tb, comm->rank, world);
+    FLUXB_CUDA(cudaGetLastError());
+    p.g_order = tb.order;
+  }
 
   const size_t half_gather = (static_cast<size_t>(op->max_ntokens) + kBM) * op->hidden * eb;
   const size_t half_flags = static_cast<size_t>(world) * op->flag_stride;
@@ -575,14 +607,14 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   int* local_cnt = op->cnt[comm->rank] + parity * op->cnt_cap;
   if (op->out_dtype == FLUXB_BF16) {
     moe_topk_push_kernel<__nv_bfloat16><<<pgrid, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(inter), routing_idx_dev, topk, n, tpr, comm->rank, world, tg);
+        static_cast<const __nv_bfloat16*>(inter), routing_idx_dev, topk, n, m, tpr, comm->rank, world, tg);
     FLUXB_CUDA(cudaGetLastError());
     moe_rs_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, stream>>>(
         static_cast<const __nv_bfloat16*>(local_stage), local_cnt, static_cast<__nv_bfloat16*>(out), n, tpr, world,
         comm->status_dev, comm->timeout_ns);
   } else {
     moe_topk_push_kernel<__half><<<pgrid, 256, 0, stream>>>(static_cast<const __half*>(inter), routing_idx_dev, topk,
-                                                           n, tpr, comm->rank, world, tg);
+                                                           n, m, tpr, comm->rank, world, tg);
     FLUXB_CUDA(cudaGetLastError());
     moe_rs_reduce_kernel<__half><<<rgrid, 256, 0, stream>>>(static_cast<const __half*>(local_stage), local_cnt,
                                                            static_cast<__half*>(out), n, tpr, world, comm->status_dev,
@@ -606,7 +638,8 @@ namespace fluxb {
 constexpr size_t kStaticTableBytes =
     ((FLUXB_STATIC_MAX_ROWS / kBM + FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(GroupTile) + 255) / 256 * 256 + 256 +
     2 * (((FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(int) + 255) / 256 * 256) +
-    (static_cast<size_t>(FLUXB_STATIC_MAX_ROWS) * sizeof(int) + 255) / 256 * 256;
+    (static_cast<size_t>(FLUXB_STATIC_MAX_ROWS) * sizeof(int) + 255) / 256 * 256 +
+    ((FLUXB_STATIC_MAX_ROWS / kBM + FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(int) + 255) / 256 * 256;
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
 static __device__ __align__(256) unsigned char g_static_tables[kStaticTableBytes];
