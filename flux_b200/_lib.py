@@ -23,6 +23,7 @@ IPC_HANDLE_BYTES = 64
 
 BF16, F16, F32, E4M3, E5M2 = 0, 1, 2, 3, 4
 BIAS_NONE, BIAS_MN, BIAS_1N = 0, 1, 2
+WEIGHT_KN = 1
 
 STATUS_NAMES = {
     0: "ok",
@@ -71,18 +72,18 @@ SIGNATURES = {
     "fluxb_symm_close": (_i, [_vp]),
     "fluxb_enable_peer_access": (_i, [_i, _i]),
     "fluxb_barrier_all": (_i, [_vp, _pp, _vp]),
-    "fluxb_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _f, _tun, _vp]),
+    "fluxb_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _f, _i, _tun, _vp]),
     "fluxb_ag_gemm_gather_bytes": (_sz, [_i, _i, _i]),
     "fluxb_ag_gemm_flag_bytes": (_sz, [_i, _i]),
     "fluxb_ag_gemm_scale_bytes": (_sz, [_i]),
     "fluxb_ag_gemm_create": (_i, [_vp, _i, _i, _i, _i, _i, _pp, _pp, _pp, _pp]),
     "fluxb_ag_gemm_destroy": (_i, [_vp]),
-    "fluxb_ag_gemm_forward": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _vp, _tun, _vp]),
+    "fluxb_ag_gemm_forward": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _i, _vp, _tun, _vp]),
     "fluxb_gemm_rs_stage_bytes": (_sz, [_i, _i, _i]),
     "fluxb_gemm_rs_cnt_bytes": (_sz, [_i, _i, _i]),
     "fluxb_gemm_rs_create": (_i, [_vp, _i, _i, _i, _i, _pp, _pp, _pp]),
     "fluxb_gemm_rs_destroy": (_i, [_vp]),
-    "fluxb_gemm_rs_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _tun, _vp]),
+    "fluxb_gemm_rs_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _i, _tun, _vp]),
     "fluxb_moe_scatter_index": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "fluxb_moe_gather_index": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "fluxb_moe_ag_scatter_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),

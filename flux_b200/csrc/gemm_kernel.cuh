@@ -64,6 +64,7 @@ struct GemmParams {
   CUtensorMap tmap_b;
   CUtensorMap tmap_a_own;  // all-gather: this rank's own shard, read in place (valid if a_own_valid)
   int a_own_valid;
+  int b_mn_major;  // 1: B is stored [K, N] (N contiguous), loaded as 64-column boxes (16-bit inputs only)
   int M, N, K;
   // M segmentation: nseg segments of seg_rows rows; tiles never straddle a
   // segment; segments are visited (seg_first + i) % nseg.
@@ -459,8 +460,20 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
                 tma_gather4_2d(smem_a(stage) + q * 4 * kRowBytes, &p.tmap_a, fb, kb * BKE, i0, i1, i2, i3);
             }
           }
-          if (CTA2) tma_load_2d_2cta(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0 + half * (BN / 2));
-          else tma_load_2d(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0);
+          if (p.b_mn_major) {
+            // B is [K, N]: one box of 64 columns x BKE rows per 64 output columns
+            constexpr int kBoxes = L::kBRows / 64;
+            const int ncol0 = tc.b_row0 + (CTA2 ? half * (BN / 2) : 0);
+#pragma unroll
+            for (int j = 0; j < kBoxes; ++j) {
+              if (CTA2) tma_load_2d_2cta(smem_b(stage) + j * (BKE * kRowBytes), &p.tmap_b, fb, ncol0 + j * 64, kb * BKE);
+              else tma_load_2d(smem_b(stage) + j * (BKE * kRowBytes), &p.tmap_b, fb, ncol0 + j * 64, kb * BKE);
+            }
+          } else if (CTA2) {
+            tma_load_2d_2cta(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0 + half * (BN / 2));
+          } else {
+            tma_load_2d(smem_b(stage), &p.tmap_b, fb, kb * BKE, tc.b_row0);
+          }
           if (++stage == STAGES) {
             stage = 0;
             phase ^= 1u;
@@ -491,17 +504,20 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           tc_fence_after();
           if (tr != nullptr && it == 0 && kb == kb0) tr[1] = globaltimer_ns();
           const uint64_t a_desc = make_kmajor_sw128_desc(smem_a(stage));
-          const uint64_t b_desc = make_kmajor_sw128_desc(smem_b(stage));
+          const uint64_t b_desc = p.b_mn_major ? make_mnmajor_sw128_desc(smem_b(stage), BKE * kRowBytes)
+                                               : make_kmajor_sw128_desc(smem_b(stage));
+          // each UMMA consumes 32 bytes of K of a K-major operand: advance the start address by 32 B
+          // (>>4 = 2); of an MN-major operand it consumes 16 K rows of 128 B: 2048 B (>>4 = 128)
+          const uint32_t b_step = p.b_mn_major ? 128u : 2u;
 #pragma unroll
           for (int k = 0; k < 4; ++k) {
-            // each UMMA consumes 32 bytes of K: advance the start address by 32 B (>>4 = 2)
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
             if (CTA2) {
-              if (KIND == 0) umma_f16_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
-              else umma_f8_2cta(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+              if (KIND == 0) umma_f16_2cta(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
+              else umma_f8_2cta(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
             } else {
-              if (KIND == 0) umma_f16(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
-              else umma_f8(d_tmem, a_desc + 2u * k, b_desc + 2u * k, idesc, accum);
+              if (KIND == 0) umma_f16(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
+              else umma_f8(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
             }
           }
           if (CTA2) umma_commit_2cta(bar_empty(stage), 3); else umma_commit(bar_empty(stage));
@@ -532,7 +548,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       const uint32_t acc_phase = (it >> 1) & 1;
       TileCoord tc;
       decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
-      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget, 2000)) break;
+      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget, 300)) break;
       tc_fence_after();
       // split-K tail: where this warp's 32 rows of a tail tile's partial accumulators live
       const bool is_tail = split > 1 && it == full_waves;

@@ -52,7 +52,7 @@ static int launch_inst(const fluxb_comm* comm, const GemmParams& p, uint32_t ide
   return FLUXB_OK;
 }
 
-static int pick_block_n(long long m_tiles, int n, int ctas) {
+static int pick_block_n(long long m_tiles, int n, int ctas, int per_cta_div, bool need_box64) {
   // cost = waves * tile width, with a small penalty for narrow tiles (more
   // operand traffic per flop); the candidate with the lowest cost wins.
   const int cand[4] = {256, 192, 128, 64};
@@ -62,6 +62,8 @@ static int pick_block_n(long long m_tiles, int n, int ctas) {
   for (int i = 0; i < 4; ++i) {
     const int bn = cand[i];
     if (bn > 64 && n <= bn / 2) continue;
+    // a [K,N] weight is loaded in 64-column boxes: each CTA's share of the tile must be whole boxes
+    if (need_box64 && ((bn / per_cta_div) % 64 != 0)) continue;
     const long long tiles = m_tiles * ((n + bn - 1) / bn);
     const long long waves = (tiles + ctas - 1) / ctas;
     const double cost = static_cast<double>(waves) * bn * pen[i];
@@ -89,7 +91,7 @@ int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tun
     long long m_tiles = m_tiles_hint;
     if (m_tiles <= 0) m_tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + tile_m - 1) / tile_m);
     int ctas = (tuning != nullptr && tuning->num_ctas > 0) ? tuning->num_ctas : comm->sm_count;
-    bn = pick_block_n(m_tiles, p.N, cg == 2 ? ctas / 2 : ctas);
+    bn = pick_block_n(m_tiles, p.N, cg == 2 ? ctas / 2 : ctas, cg == 2 ? 2 : 1, p.b_mn_major != 0);
   }
   return bn;
 }
@@ -99,6 +101,8 @@ int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
   const int cg = resolve_cta_group(p, tuning);
   const int bn = resolve_block_n(comm, p, tuning, p.g_tiles != nullptr ? 1024 : 0);
   FLUXB_REQUIRE(bn == 64 || bn == 128 || bn == 192 || bn == 256, "block_n=%d not in {64,128,192,256}", bn);
+  FLUXB_REQUIRE(!p.b_mn_major || (bn / (cg == 2 ? 2 : 1)) % 64 == 0,
+                "a [K,N] weight needs a tile width whose per-CTA share is a multiple of 64 (block_n=%d, cta_group=%d)", bn, cg);
   int grid = comm->sm_count;
   if (tuning != nullptr && tuning->num_ctas > 0) grid = tuning->num_ctas < grid ? tuning->num_ctas : grid;
   if (p.g_tiles == nullptr) {
@@ -126,7 +130,7 @@ int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
     case FLUXB_E5M2: fmt = 1; break;
     default: FLUXB_FAIL(FLUXB_ERR_INVALID, "input dtype %d is not bf16/f16/e4m3/e5m2", in_dtype);
   }
-  const uint32_t idesc = make_idesc(fmt, cg == 2 ? 2 * kBM : kBM, static_cast<uint32_t>(bn));
+  const uint32_t idesc = make_idesc(fmt, cg == 2 ? 2 * kBM : kBM, static_cast<uint32_t>(bn), p.b_mn_major ? 1u : 0u);
 #define FLUXB_LAUNCH(BN_, ST1_, ST2_)                                                              \
   (cg == 2 ? (kind == 0 ? launch_inst<BN_, ST2_, 0, true>(comm, p, idesc, grid, stream)            \
                         : launch_inst<BN_, ST2_, 1, true>(comm, p, idesc, grid, stream))           \
@@ -164,6 +168,18 @@ static int check_gemm_shapes(const char* who, int m, int n, int k, int in_dtype,
 
 static void zero_params(GemmParams& p) { memset(&p, 0, sizeof(p)); }
 
+// B operand: [n, k] (k contiguous) as one box of `box_rows` rows, or, with the FLUXB_WEIGHT_KN flag,
+// [k, n] (n contiguous) as 64-column boxes feeding an MN-major UMMA operand.
+static int encode_b(GemmParams& p, const void* b, int in_dtype, int n, int k, int box_rows, int flags) {
+  const long long eb = dtype_bytes(in_dtype);
+  if (flags & FLUXB_WEIGHT_KN) {
+    FLUXB_REQUIRE(is_16bit(in_dtype), "a [K,N] weight needs 16-bit inputs (fp8 forbids transpose_weight)");
+    p.b_mn_major = 1;
+    return encode_tmap_kn(&p.tmap_b, b, in_dtype, k, n, static_cast<long long>(n) * eb, kRowBytes / static_cast<int>(eb));
+  }
+  return encode_tmap_2d(&p.tmap_b, b, in_dtype, n, k, static_cast<long long>(k) * eb, box_rows);
+}
+
 }  // namespace fluxb
 
 using namespace fluxb;
@@ -197,7 +213,7 @@ extern "C" {
 
 int fluxb_gemm(fluxb_comm_t comm, const void* a, const void* b, void* c, int m, int n, int k,
                int in_dtype, int out_dtype, const void* bias, int bias_mode, const float* scale_a,
-               const float* scale_b, float alpha, const fluxb_tuning* tuning, fluxb_stream_t stream) {
+               const float* scale_b, float alpha, int flags, const fluxb_tuning* tuning, fluxb_stream_t stream) {
   FLUXB_REQUIRE(comm != nullptr && a != nullptr && b != nullptr && c != nullptr, "gemm: NULL argument");
   int rc = check_gemm_shapes("gemm", m, n, k, in_dtype, out_dtype);
   if (rc != FLUXB_OK) return rc;
@@ -222,11 +238,11 @@ int fluxb_gemm(fluxb_comm_t comm, const void* a, const void* b, void* c, int m, 
   p.scale_a = scale_a;
   p.scale_b = scale_b;
   p.alpha = alpha;
+  p.b_mn_major = (flags & FLUXB_WEIGHT_KN) ? 1 : 0;
   const int bn = resolve_block_n(comm, p, tuning, 0);
   rc = encode_tmap_2d(&p.tmap_a, a, in_dtype, m, k, static_cast<long long>(k) * eb, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, b, in_dtype, n, k, static_cast<long long>(k) * eb,
-                      resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn);
+  rc = encode_b(p, b, in_dtype, n, k, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn, flags);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;
@@ -285,7 +301,7 @@ int fluxb_ag_gemm_destroy(fluxb_ag_gemm_t op) {
 
 int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, const void* b,
                           int n, int k, void* c, const void* bias, int bias_mode,
-                          const float* scale_a_shard, const float* scale_b, float alpha,
+                          const float* scale_a_shard, const float* scale_b, float alpha, int flags,
                           void* gathered_out, const fluxb_tuning* tuning, fluxb_stream_t stream_) {
   FLUXB_REQUIRE(op != nullptr && a_shard != nullptr && b != nullptr && c != nullptr,
                 "ag_gemm_forward: NULL argument");
@@ -307,7 +323,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
 
   if (world == 1) {
     rc = fluxb_gemm(comm, a_shard, b, c, m_local, n, k, op->in_dtype, op->out_dtype, bias, bias_mode,
-                    scale_a_shard, scale_b, alpha, tuning, stream_);
+                    scale_a_shard, scale_b, alpha, flags, tuning, stream_);
     if (rc != FLUXB_OK) return rc;
     if (gathered_out != nullptr)
       FLUXB_CUDA(cudaMemcpyAsync(gathered_out, a_shard, m_local * row_bytes, cudaMemcpyDeviceToDevice, stream));
@@ -352,6 +368,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
     p.ag_dst_scale[r] = op->has_scales ? op->scales[r] + parity * op->full_m : nullptr;
   }
   if (scale_a_shard != nullptr) p.scale_a = op->scales[comm->rank] + parity * op->full_m;
+  p.b_mn_major = (flags & FLUXB_WEIGHT_KN) ? 1 : 0;
   if (tuning == nullptr || tuning->group_m <= 0) {
     // one shard per rasterisation band, so that tiles are visited in arrival order
     const int tile_m = resolve_cta_group(p, tuning) == 2 ? 2 * kBM : kBM;
@@ -367,7 +384,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   // per-row scales travel through the scale buffer under the same flags as the data: keep the
   // flagged path for the own shard too in that case
   p.a_own_valid = scale_a_shard == nullptr ? 1 : 0;
-  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k, row_bytes, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn);
+  rc = encode_b(p, b, op->in_dtype, n, k, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn, flags);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;
@@ -434,7 +451,7 @@ int fluxb_gemm_rs_destroy(fluxb_gemm_rs_t op) {
 
 int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int m, int n,
                           int k_local, void* out, const void* bias, int bias_mode,
-                          const float* scale_a, const float* scale_b, float alpha,
+                          const float* scale_a, const float* scale_b, float alpha, int flags,
                           const fluxb_tuning* tuning, fluxb_stream_t stream_) {
   FLUXB_REQUIRE(op != nullptr && a != nullptr && b != nullptr && out != nullptr,
                 "gemm_rs_forward: NULL argument");
@@ -450,7 +467,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   FLUXB_REQUIRE(bias_mode != FLUXB_BIAS_1N, "gemm_rs_forward: only [M,N] bias is supported");
   if (world == 1)
     return fluxb_gemm(comm, a, b, out, m, n, k_local, op->in_dtype, op->out_dtype, bias, bias_mode,
-                      scale_a, scale_b, alpha, tuning, stream_);
+                      scale_a, scale_b, alpha, flags, tuning, stream_);
   FLUXB_REQUIRE(bias_mode == FLUXB_BIAS_NONE || op->out_dtype == FLUXB_BF16,
                 "gemm_rs_forward: bias needs a bf16 output");
 
@@ -480,6 +497,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   p.scale_a = scale_a;
   p.scale_b = scale_b;
   p.alpha = alpha;
+  p.b_mn_major = (flags & FLUXB_WEIGHT_KN) ? 1 : 0;
   const size_t half_stage = static_cast<size_t>(op->max_m) * op->n_dim;
   for (int r = 0; r < world; ++r) {
     p.rs_stage[r] = op->stage[r] + parity * half_stage + static_cast<size_t>(comm->rank) * mpr * n;
@@ -497,7 +515,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   const long long row_bytes = static_cast<long long>(k_local) * eb;
   rc = encode_tmap_2d(&p.tmap_a, a, op->in_dtype, m, k_local, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, b, op->in_dtype, n, k_local, row_bytes, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn);
+  rc = encode_b(p, b, op->in_dtype, n, k_local, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn, flags);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
   t.block_n = bn;

@@ -74,6 +74,10 @@ namespace fluxb {
 int encode_tmap_2d(CUtensorMap* out, const void* base, int elt_dtype, long long rows, long long k,
                    long long ld_bytes, int box_rows);
 
+// 16-bit [k, n] row-major matrix (n contiguous) read as 64-column x `box_k`-row boxes, 128-byte swizzle
+int encode_tmap_kn(CUtensorMap* out, const void* base, int elt_dtype, long long k, long long n, long long ld_bytes,
+                   int box_k);
+
 // fp32 [rows, n] row-major matrix, 32 x 32 element boxes, 128-byte swizzle (reduce-scatter pushes)
 int encode_tmap_f32_store(CUtensorMap* out, const void* base, long long rows, long long n);
 

@@ -385,13 +385,29 @@ __device__ __forceinline__ uint64_t make_kmajor_sw128_desc(uint32_t smem_addr) {
   return d;
 }
 
+// Shared-memory operand descriptor for an MN-major tile (the operand is stored [K][MN] with MN
+// contiguous): TMA wrote it as boxes of 64 elements of MN (128 B) x `k` rows with 128-byte swizzle, one
+// box after the other. Inside a box the K rows are 128 B apart and groups of 8 rows 1024 B (stride byte
+// offset); the next 64 elements of MN start one box later (leading byte offset = box_bytes).
+__device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, uint32_t box_bytes) {
+  uint64_t d = 0;
+  d |= static_cast<uint64_t>((smem_addr & 0x3FFFFu) >> 4);
+  d |= static_cast<uint64_t>((box_bytes >> 4) & 0x3FFFu) << 16;
+  d |= static_cast<uint64_t>(1024 >> 4) << 32;
+  d |= static_cast<uint64_t>(1) << 46;
+  d |= static_cast<uint64_t>(2) << 61;
+  return d;
+}
+
 // Instruction descriptor (dense, fp32 accumulate, both operands K-major).
 //   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format
 //   [15] A major (0 = K)       [16] B major (0 = K)
 //   [17,23) N >> 3             [24,29) M >> 4
 // A/B format: kind::f16 -> 0 = f16, 1 = bf16; kind::f8f6f4 -> 0 = e4m3, 1 = e5m2
-__host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t m, uint32_t n) {
-  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+__host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t m, uint32_t n,
+                                                  uint32_t b_mn_major = 0) {
+  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (b_mn_major << 16) | ((n >> 3) << 17) |
+         ((m >> 4) << 24);
 }
 
 }  // namespace fluxb

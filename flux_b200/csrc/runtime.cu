@@ -62,6 +62,25 @@ int encode_tmap_2d(CUtensorMap* out, const void* base, int elt_dtype, long long 
   return FLUXB_OK;
 }
 
+int encode_tmap_kn(CUtensorMap* out, const void* base, int elt_dtype, long long k, long long n, long long ld_bytes,
+                   int box_k) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) FLUXB_FAIL(FLUXB_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  FLUXB_REQUIRE(dtype_bytes(elt_dtype) == 2, "[K,N] weights need a 16-bit element type");
+  FLUXB_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0 && (ld_bytes & 15) == 0 && k > 0 && n > 0,
+                "[K,N] tensor map: base and row pitch must be 16-byte aligned");
+  CUtensorMapDataType dt = elt_dtype == FLUXB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(k)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld_bytes)};
+  cuuint32_t box[2] = {64, static_cast<cuuint32_t>(box_k)};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    FLUXB_FAIL(FLUXB_ERR_CUDA, "cuTensorMapEncodeTiled ([K,N] map) failed with CUresult %d", static_cast<int>(r));
+  return FLUXB_OK;
+}
+
 int encode_tmap_f32_store(CUtensorMap* out, const void* base, long long rows, long long n) {
   EncodeTiledFn fn = get_encode_fn();
   if (fn == nullptr) FLUXB_FAIL(FLUXB_ERR_CUDA, "cuTensorMapEncodeTiled is not available");

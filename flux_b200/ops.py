@@ -213,16 +213,19 @@ class AGKernel:
         _check(input.dim() == 2 and weight.dim() == 2, "AGKernel: input and weight must be 2-D")
         _check(input.dtype == self.input_dtype and weight.dtype == self.input_dtype, "AGKernel: dtype mismatch")
         _check(output_scale is None, "AGKernel: output_scale is not supported")
+        flags = 0
         if transpose_weight:
-            # fp8 forbids transpose_weight (src/ag_gemm/ths_op/gemm_with_barrier.cc:188)
+            # weight arrives as [K, N] ("RRR"); fp8 forbids it (src/ag_gemm/ths_op/gemm_with_barrier.cc:188,196-197).
+            # The kernel reads it in place as an MN-major operand: no transposing copy.
             _check(not is_fp8_dtype(self.input_dtype), "AGKernel: fp8 does not support transpose_weight")
-            weight = weight.t()
+            flags |= _lib.WEIGHT_KN
         _check(input.is_contiguous(), "AGKernel: input must be contiguous")
         if not weight.is_contiguous():
             weight = weight.contiguous()
         m_local, k = input.shape
-        n = weight.shape[0]
-        _check(weight.shape[1] == k, f"AGKernel: weight K {weight.shape[1]} != input K {k}")
+        n = weight.shape[1] if transpose_weight else weight.shape[0]
+        wk = weight.shape[0] if transpose_weight else weight.shape[1]
+        _check(wk == k, f"AGKernel: weight K {wk} != input K {k}")
         _check(k == self.k_dim, f"AGKernel: k={k} differs from k_dim={self.k_dim}")
         m = m_local * world
         _check(m <= self.full_m, f"AGKernel: M={m} exceeds full_m={self.full_m}")
@@ -240,13 +243,13 @@ class AGKernel:
                 bias_mode = _lib.BIAS_1N
             else:
                 raise RuntimeError(f"AGKernel: bias shape {tuple(bias.shape)} is neither [M,N] nor [1,N]")
-        return input, weight, output, bias_mode, m_local, n, k
+        return input, weight, output, bias_mode, m_local, n, k, flags
 
     def forward(self, input, weight, bias=None, output=None, input_scale=None, weight_scale=None,
                 output_scale=None, fast_accum=False, transpose_weight=False, all_gather_option=None,
                 gathered_input=None, tuning=None):
         w = self.comm.world
-        input, weight, output, bias_mode, m_local, n, k = self._prep(
+        input, weight, output, bias_mode, m_local, n, k, flags = self._prep(
             input, weight, bias, output, input_scale, weight_scale, output_scale, transpose_weight, w)
         sa = _expand_scale(input_scale, m_local, "input_scale")
         sb = _expand_scale(weight_scale, n, "weight_scale")
@@ -257,7 +260,7 @@ class AGKernel:
         _lib.check(
             lib.fluxb_ag_gemm_forward(
                 self._h, input.data_ptr(), m_local, weight.data_ptr(), n, k, output.data_ptr(), _ptr(bias),
-                bias_mode, _ptr(sa), _ptr(sb), 1.0, _ptr(gathered_input), _tuning(tuning), _cur_stream(),
+                bias_mode, _ptr(sa), _ptr(sb), 1.0, flags, _ptr(gathered_input), _tuning(tuning), _cur_stream(),
             )
         )
         return output
@@ -266,7 +269,7 @@ class AGKernel:
                   output_scale=None, fast_accum=False, transpose_weight=False, tuning=None):
         """Same kernel without communication: `input` is the full [M,K] matrix
         (src/ag_gemm/ths_op/all_gather_gemm_op.cc:166-194)."""
-        input, weight, output, bias_mode, m, n, k = self._prep(
+        input, weight, output, bias_mode, m, n, k, flags = self._prep(
             input, weight, bias, output, input_scale, weight_scale, output_scale, transpose_weight, 1)
         sa = _expand_scale(input_scale, m, "input_scale")
         sb = _expand_scale(weight_scale, n, "weight_scale")
@@ -275,7 +278,7 @@ class AGKernel:
             lib.fluxb_gemm(
                 self.comm.handle, input.data_ptr(), weight.data_ptr(), output.data_ptr(), m, n, k,
                 fluxb_dtype(self.input_dtype), fluxb_dtype(self.output_dtype), _ptr(bias), bias_mode,
-                _ptr(sa), _ptr(sb), 1.0, _tuning(tuning), _cur_stream(),
+                _ptr(sa), _ptr(sb), 1.0, flags, _tuning(tuning), _cur_stream(),
             )
         )
         return output
@@ -327,16 +330,18 @@ class GemmRS:
         _check(input.dim() == 2 and weight.dim() == 2, "GemmRS: input and weight must be 2-D")
         _check(input.dtype == self.input_dtype and weight.dtype == self.input_dtype, "GemmRS: dtype mismatch")
         _check(output_scale is None, "GemmRS: output_scale is not supported")
+        flags = 0
         if self.transpose_weight:
             _check(not is_fp8_dtype(self.input_dtype), "GemmRS: fp8 does not support transpose_weight")
-            weight = weight.t()
+            flags |= _lib.WEIGHT_KN  # [K, N] weight read in place as an MN-major operand
         if not weight.is_contiguous():
             weight = weight.contiguous()
         _check(input.is_contiguous(), "GemmRS: input must be contiguous")
         m, k = input.shape
-        n = weight.shape[0]
+        n = weight.shape[1] if self.transpose_weight else weight.shape[0]
+        wk = weight.shape[0] if self.transpose_weight else weight.shape[1]
         w = self.comm.world
-        _check(weight.shape[1] == k, f"GemmRS: weight K {weight.shape[1]} != input K {k}")
+        _check(wk == k, f"GemmRS: weight K {wk} != input K {k}")
         # shape rules of src/gemm_rs/ths_op/gemm_reduce_scatter.cc:499-504
         _check(m <= self.max_m, f"GemmRS: M={m} exceeds max_m={self.max_m}")
         _check(n == self.n_dim, f"GemmRS: N={n} differs from n_dim={self.n_dim}")
@@ -355,7 +360,7 @@ class GemmRS:
         _lib.check(
             lib.fluxb_gemm_rs_forward(
                 self._h, input.data_ptr(), weight.data_ptr(), m, n, k, out.data_ptr(), _ptr(bias), bias_mode,
-                _ptr(sa), _ptr(sb), 1.0, _tuning(tuning), _cur_stream(),
+                _ptr(sa), _ptr(sb), 1.0, flags, _tuning(tuning), _cur_stream(),
             )
         )
         return out

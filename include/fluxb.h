@@ -46,6 +46,10 @@ extern "C" {
 #define FLUXB_BIAS_MN 1 /* [M,N], added elementwise        */
 #define FLUXB_BIAS_1N 2 /* [1,N], broadcast over rows      */
 
+/* `flags` of the GEMM entry points */
+#define FLUXB_WEIGHT_KN 1 /* the weight is [K,N] with N contiguous ("RRR", transpose_weight=True in the
+                             reference, src/ag_gemm/ths_op/gemm_with_barrier.cc:55,196-197); 16-bit inputs only */
+
 typedef struct fluxb_comm* fluxb_comm_t;
 typedef struct fluxb_ag_gemm* fluxb_ag_gemm_t;
 typedef struct fluxb_gemm_rs* fluxb_gemm_rs_t;
@@ -104,7 +108,7 @@ int fluxb_barrier_all(fluxb_comm_t comm, int* const* sync_bufs, fluxb_stream_t s
  * with K contiguous. scale_a / scale_b may be NULL. */
 int fluxb_gemm(fluxb_comm_t comm, const void* a, const void* b, void* c, int m, int n, int k,
                int in_dtype, int out_dtype, const void* bias, int bias_mode, const float* scale_a,
-               const float* scale_b, float alpha, const fluxb_tuning* tuning, fluxb_stream_t stream);
+               const float* scale_b, float alpha, int flags, const fluxb_tuning* tuning, fluxb_stream_t stream);
 
 /* ----------------------------------------------------------------- AG-GEMM
  * Replaces AllGatherGemmOp (src/ag_gemm/ths_op/all_gather_gemm_op.cc:97-123
@@ -131,7 +135,7 @@ int fluxb_ag_gemm_destroy(fluxb_ag_gemm_t op);
  * m_local, n, k. Asynchronous on `stream`. */
 int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, const void* b,
                           int n, int k, void* c, const void* bias, int bias_mode,
-                          const float* scale_a_shard, const float* scale_b, float alpha,
+                          const float* scale_a_shard, const float* scale_b, float alpha, int flags,
                           void* gathered_out, const fluxb_tuning* tuning, fluxb_stream_t stream);
 
 /* ----------------------------------------------------------------- GEMM-RS
@@ -148,7 +152,7 @@ int fluxb_gemm_rs_destroy(fluxb_gemm_rs_t op);
  * Partials travel and are summed in fp32; the result is rounded once. */
 int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int m, int n,
                           int k_local, void* out, const void* bias, int bias_mode,
-                          const float* scale_a, const float* scale_b, float alpha,
+                          const float* scale_a, const float* scale_b, float alpha, int flags,
                           const fluxb_tuning* tuning, fluxb_stream_t stream);
 
 /* ---------------------------------------------------------- MoE index work

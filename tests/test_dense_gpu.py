@@ -100,8 +100,7 @@ def test_gemm_linearity_at_full_size(flux):
     a1 = torch.randn(m, k, generator=g, device="cuda").to(torch.bfloat16)
     a2 = torch.randn(m, k, generator=g, device="cuda").to(torch.bfloat16)
     b = (torch.randn(n, k, generator=g, device="cuda") * 0.02).to(torch.bfloat16)
-    op = flux.AGKernel(None, 1, m, n, k, torch.bfloat16, output_dtype=torch.float32) \
-        if False else flux.AGKernel(None, 1, m, n, k, torch.bfloat16)
+    op = flux.AGKernel(None, 1, m, n, k, torch.bfloat16)
     o1 = op.gemm_only(a1, b).float()
     o2 = op.gemm_only(a2, b).float()
     # a1 + a2 rounded to bf16 is not exactly the sum; use the exactly representable 2*a1
@@ -165,14 +164,22 @@ def test_fp8_rejects_transpose_weight(flux):
         op.forward(q, q, transpose_weight=True)
 
 
-def test_transpose_weight(flux):
-    m, n, k = 256, 384, 512
-    a, b = _mk(m, n, k, torch.bfloat16, seed=9)
+@pytest.mark.parametrize("m,n,k", [(256, 384, 512), (300, 264, 200), (1024, 2048, 1024), (128, 64, 64)])
+@pytest.mark.parametrize("cta_group", [1, 2])
+def test_transpose_weight(flux, m, n, k, cta_group):
+    """transpose_weight=True: the weight arrives as [K, N] and is read in place (MN-major operand)."""
+    a, b = _mk(m, n, k, torch.bfloat16, seed=9 + m)
     op = flux.AGKernel(None, 1, m, n, k, torch.bfloat16)
-    out = op.forward(a.cuda(), b.t().contiguous().cuda(), transpose_weight=True)  # weight given as [K, N]
+    w_kn = b.t().contiguous().cuda()
+    out = op.forward(a.cuda(), w_kn, transpose_weight=True, tuning={"cta_group": cta_group})
     torch.cuda.synchronize()
+    op.comm.check_status()
     ref, _ = golden.ag_gemm_single([a], b)
     assert golden.max_rel_err(out, ref) <= BF16_TOL
+    rs = flux.GemmRS(None, 1, m, n, torch.bfloat16, transpose_weight=True)
+    out2 = rs.forward(a.cuda(), w_kn)
+    torch.cuda.synchronize()
+    assert golden.max_rel_err(out2, ref) <= BF16_TOL
 
 
 def _need(n):
