@@ -24,6 +24,7 @@ IPC_HANDLE_BYTES = 64
 BF16, F16, F32, E4M3, E5M2 = 0, 1, 2, 3, 4
 BIAS_NONE, BIAS_MN, BIAS_1N = 0, 1, 2
 WEIGHT_KN = 1
+RS_FP32_WIRE = 2
 
 STATUS_NAMES = {
     0: "ok",

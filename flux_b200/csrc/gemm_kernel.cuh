@@ -43,6 +43,7 @@ constexpr int kRowBytes = 128;    // bytes of K per smem row (one swizzle span)
 constexpr int kThreads = 320;
 constexpr int kMaxWorld = 8;
 constexpr int kCommSliceBytes = 2048;  // bytes of one row handled by one comm unit
+constexpr int kAgSubRows = 32;         // rows of one all-gather push unit; kBM / kAgSubRows units signal one chunk flag
 
 enum EpiMode : int {
   kEpiStore = 0,    // write D (out dtype) to p.out
@@ -69,7 +70,10 @@ struct GemmParams {
   // M segmentation: nseg segments of seg_rows rows; tiles never straddle a
   // segment; segments are visited (seg_first + i) % nseg.
   int nseg, seg_rows, seg_first;
-  int group_m;  // rasterisation band height in M tiles
+  int group_m;  // rasterisation band height in M tiles (uniform bands, used when n_bands == 0)
+  int rs_wire16;  // reduce-scatter partials cross NVLink in the 16-bit output format instead of fp32
+  int n_bands;  // > 0: explicit bands, band b covers M tiles [band_end[b-1], band_end[b])
+  int band_end[8];
   // epilogue
   int epi_mode, out_type, bias_mode;
   void* out;
@@ -171,12 +175,25 @@ __device__ __forceinline__ int imax(int a, int b) { return a > b ? a : b; }
 template <int BN, int TILE_M>
 __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_tiles, int n_tiles,
                                             int tps, int half, TileCoord& tc) {
-  const int gmn = p.group_m * n_tiles;
-  const int band = t / gmn;
-  const int r = t - band * gmn;
-  const int gm_eff = imin(p.group_m, m_tiles - band * p.group_m);
-  const int m_idx = band * p.group_m + r % gm_eff;
-  const int n_idx = r / gm_eff;
+  // Rasterisation: M tiles are grouped into bands; inside a band consecutive work items walk down the
+  // band's M tiles first, then move to the next column block (A band stays in L2, B streams once per band).
+  int m_idx, n_idx;
+  if (p.n_bands > 0) {
+    int b = 0;
+    while (b + 1 < p.n_bands && t >= p.band_end[b] * n_tiles) ++b;
+    const int m_lo = b > 0 ? p.band_end[b - 1] : 0;
+    const int h = p.band_end[b] - m_lo;
+    const int r = t - m_lo * n_tiles;
+    m_idx = m_lo + r % h;
+    n_idx = r / h;
+  } else {
+    const int gmn = p.group_m * n_tiles;
+    const int band = t / gmn;
+    const int r = t - band * gmn;
+    const int gm_eff = imin(p.group_m, m_tiles - band * p.group_m);
+    m_idx = band * p.group_m + r % gm_eff;
+    n_idx = r / gm_eff;
+  }
   tc.n_idx = n_idx;
   tc.n0 = n_idx * BN;
   if (p.g_tiles == nullptr) {
@@ -719,9 +736,44 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             }
           }
         }
-        if (own && lane == 0) bulk_commit();  // keeps the number of groups per tile uniform
-        if (p.epi_mode == kEpiRsPush && !own) {
-          // Park the warp's 32 x 32 fp32 block in shared memory (lane = row, 16-byte pieces XOR-swizzled
+        // keeps the number of store groups per tile uniform (one per staged box)
+        if (own && lane == 0 && (!p.rs_wire16 || (c & 1))) bulk_commit();
+        if (p.epi_mode == kEpiRsPush && !own && p.rs_wire16) {
+          // 16-bit wire format: two 32-column steps fill one 32 x 64 box (128-byte rows, 16-byte pieces
+          // XOR-swizzled by row like the tensor map's 128-byte swizzle); the box is pushed to the owner
+          // with one tiled store after the second step. Rows and columns outside the owner's slot are
+          // clipped by the tensor map.
+          const int box = c >> 1, h = c & 1;
+          const uint32_t stage_blk = stage_blk0 + (L::kEpiBufs == 2 ? (box & 1) * L::kEpiBlockBytes : 0);
+          const uint32_t stage_row = stage_blk + lane * L::kEpiPitch;
+          if (h == 0) {
+            if (lane == 0) {  // the previous store out of this block has been read
+              if (L::kEpiBufs == 2) bulk_wait_read_keep1(); else bulk_wait_read();
+            }
+            __syncwarp();
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              w[j] = (p.rs_out_type == kOutBf16) ? pack_bf16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1])
+                                                  : pack_f16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((h * 4 + q) ^ (lane & 7)) << 4)),
+                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                         : "memory");
+          }
+          if (h == 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (tc.rows > quad * 32 && col0 - 32 < p.N)
+                tma_store_2d(&p.tmap_rs[tc.seg], stage_blk, col0 - 32, tc.chunk * kBM + quad * 32);
+              bulk_commit();
+            }
+          }
+        } else if (p.epi_mode == kEpiRsPush && !own) {
+          // fp32 wire format. Park the warp's 32 x 32 fp32 block in shared memory (lane = row, 16-byte pieces XOR-swizzled
           // by row so that the writes spread over all banks and match the tensor map's 128-byte swizzle),
           // then push it to the owner with one tiled store: 4 KB per operation over NVLink, rows and
           // columns outside the owner's slot are clipped by the tensor map.
@@ -788,12 +840,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       if (p.epi_mode == kEpiRsPush) {
         // Publish the PREVIOUS pushed tile of this warp: its stores were issued a whole tile ago, so
         // waiting for all groups but this tile's BN/32 costs nothing, whereas waiting for the stores
-        // just issued would put NVLink round trips on the epilogue's critical path. Each epilogue warp
+        // just issued (one group per staged box) would put NVLink round trips on the epilogue's critical path. Each epilogue warp
         // adds 1, so a complete 128-row tile counts 4 per source rank. (No CTA-wide barrier here: a
         // role that gave up must never strand the others.)
         if (lane == 0) {
           if (pending_cnt != nullptr) {
-            bulk_wait_all_but<BN / 32>();
+            if (p.rs_wire16) bulk_wait_all_but<BN / 64>(); else bulk_wait_all_but<BN / 32>();
             fence_acq_rel_sys();
             red_add_release_sys(pending_cnt, 1);
           }
@@ -825,17 +877,25 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       const int ctid = threadIdx.x - 6 * 32;  // 0..127
       const int chunks = (p.seg_rows + kBM - 1) / kBM;
       const int nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
-      const int per_dest = chunks * nslices;
-      const int total_units = p.world * per_dest;
+      // Unit = 32 rows x 2 KB of the shard for one destination. Units are ordered destination by
+      // destination (the rank that needs this shard soonest first: rank-1, rank-2, ...), and one
+      // destination's units are spread over all CTAs, so that at any moment every rank sends to one peer
+      // and receives from one peer at full link rate and the shards land in the order they are consumed.
+      constexpr int kSubs = kBM / kAgSubRows;
+      const int per_dest = chunks * kSubs * nslices;
+      const int d_first = p.a_own_valid ? 1 : 0;  // own tiles read the caller's tensor: nothing to copy
+      const int total_units = (p.world - d_first) * per_dest;
       for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
-        const int d = u / per_dest;
-        const int rem = u - d * per_dest;
-        const int chunk = rem / nslices;
-        const int ks = rem - chunk * nslices;
-        int dest = p.rank - d;  // self first, then the rank that needs this shard soonest
+        const int d = d_first + u / per_dest;
+        const int rem = u - (d - d_first) * per_dest;
+        const int chunk = rem / (kSubs * nslices);
+        const int rem2 = rem - chunk * (kSubs * nslices);
+        const int sub = rem2 / nslices;
+        const int ks = rem2 - sub * nslices;
+        int dest = p.rank - d;
         if (dest < 0) dest += p.world;
-        const int r0 = chunk * kBM;
-        const int r1 = imin(r0 + kBM, p.seg_rows);
+        const int r0 = imin(chunk * kBM + sub * kAgSubRows, p.seg_rows);
+        const int r1 = imin(r0 + kAgSubRows, p.seg_rows);
         const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
         const long long b1 = (b0 + kCommSliceBytes < p.ag_row_bytes) ? b0 + kCommSliceBytes : p.ag_row_bytes;
         const int vec_per_row = static_cast<int>((b1 - b0) >> 4);
@@ -843,9 +903,8 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         uint8_t* dst = p.ag_dst[dest] +
                        (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0;
         // one 16-byte column of the slice per thread, 8 rows in flight
-        const int nrows = r1 - r0;
-        const bool skip_data = p.a_own_valid && dest == p.rank;  // own tiles read the caller's tensor
-        if (ctid < vec_per_row && !skip_data) {
+        const int nrows = r1 - r0;  // 0 for a unit past the shard's last row: it still signals
+        if (ctid < vec_per_row) {
           const uint8_t* s0 = src + ctid * 16;
           uint8_t* d0 = dst + ctid * 16;
           for (int rr = 0; rr < nrows; rr += 8) {
@@ -865,7 +924,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           for (int rr = r0 + ctid; rr < r1; rr += 128) sd[rr] = p.ag_src_scale[rr];
         }
         asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ctid == 0 && !skip_data) {
+        if (ctid == 0) {
           fence_acq_rel_sys();
           red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk, 1);
         }
@@ -962,6 +1021,54 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         const int row_base = c * kBM + quarter * 32;
         const int rows = imax(0, imin(32, p.seg_rows - row_base));
         const int n0 = nt * BN;
+        if (p.rs_wire16) {
+          // peers' partials are 16-bit (8 values per 16-byte load); the sum stays fp32
+          constexpr int kVec16PerRow = BN / 8;
+          constexpr int kVec16PerItem = 32 * kVec16PerRow;
+          for (int i0 = ctid; i0 < kVec16PerItem; i0 += 2 * 128) {
+            long long off[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int i = i0 + u * 128;
+              const int r = i / kVec16PerRow;
+              const int col = n0 + (i - r * kVec16PerRow) * 8;
+              off[u] = (i < kVec16PerItem && r < rows && col < p.N) ? static_cast<long long>(row_base + r) * p.N + col : -1;
+            }
+            uint4 v[kMaxWorld][2];
+#pragma unroll
+            for (int sr = 0; sr < kMaxWorld; ++sr)
+#pragma unroll
+              for (int u = 0; u < 2; ++u)
+                if (sr < p.world && sr != p.rank && off[u] >= 0)
+                  v[sr][u] = *reinterpret_cast<const uint4*>(
+                      reinterpret_cast<const uint16_t*>(p.rs_local_stage + sr * slot) + off[u]);
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              if (off[u] < 0) continue;
+              float acc[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+#pragma unroll
+              for (int sr = 0; sr < kMaxWorld; ++sr)
+                if (sr < p.world && sr != p.rank) {
+                  const uint32_t w[4] = {v[sr][u].x, v[sr][u].y, v[sr][u].z, v[sr][u].w};
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    if (p.rs_out_type == kOutBf16) {
+                      acc[2 * j] += __uint_as_float(w[j] << 16);
+                      acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+                    } else {
+                      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                      acc[2 * j] += f.x;
+                      acc[2 * j + 1] += f.y;
+                    }
+                  }
+                }
+              *reinterpret_cast<float4*>(sum_base + off[u]) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+              *reinterpret_cast<float4*>(sum_base + off[u] + 4) = make_float4(acc[4], acc[5], acc[6], acc[7]);
+            }
+          }
+        } else
         for (int i0 = ctid; i0 < kVecPerItem; i0 += 2 * 128) {
           long long off[2];
 #pragma unroll

@@ -168,6 +168,28 @@ static int check_gemm_shapes(const char* who, int m, int n, int k, int in_dtype,
 
 static void zero_params(GemmParams& p) { memset(&p, 0, sizeof(p)); }
 
+// Rasterisation bands for the segmented ops, in units of segments (= shards / owners) of `tps` M tiles.
+// Bands are at most 8 M tiles tall (taller bands re-stream B less often and draw less power).
+// first_single: the first band is exactly one segment (all-gather: this rank's own shard, available at
+// once) and the following bands double in size, so that early tiles only need early arrivals.
+// last_single: the last band is exactly one segment (reduce-scatter: this rank's own rows, finished last).
+static void make_bands(GemmParams& p, int nseg, int tps, bool first_single, bool last_single) {
+  int max_seg = tps > 0 ? 8 / tps : 1;
+  if (max_seg < 1) max_seg = 1;
+  int done = 0, nb = 0, next = 1;
+  const int body_end = last_single ? nseg - 1 : nseg;
+  while (done < body_end && nb < 7) {
+    int take = first_single ? next : max_seg;
+    if (take > max_seg) take = max_seg;
+    if (take > body_end - done) take = body_end - done;
+    done += take;
+    p.band_end[nb++] = done * tps;
+    next *= 2;
+  }
+  if (done < nseg) p.band_end[nb++] = nseg * tps;
+  p.n_bands = nb;
+}
+
 // B operand: [n, k] (k contiguous) as one box of `box_rows` rows, or, with the FLUXB_WEIGHT_KN flag,
 // [k, n] (n contiguous) as 64-column boxes feeding an MN-major UMMA operand.
 static int encode_b(GemmParams& p, const void* b, int in_dtype, int n, int k, int box_rows, int flags) {
@@ -358,7 +380,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   p.alpha = alpha;
   p.ag_flags = op->flags[comm->rank] + parity * half_flags;
   p.ag_flag_stride = op->flag_stride;
-  p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+  p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes) * (kBM / kAgSubRows);
   p.ag_src = static_cast<const uint8_t*>(a_shard);
   p.ag_row_bytes = row_bytes;
   p.ag_src_scale = scale_a_shard;
@@ -370,10 +392,11 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   if (scale_a_shard != nullptr) p.scale_a = op->scales[comm->rank] + parity * op->full_m;
   p.b_mn_major = (flags & FLUXB_WEIGHT_KN) ? 1 : 0;
   if (tuning == nullptr || tuning->group_m <= 0) {
-    // one shard per rasterisation band, so that tiles are visited in arrival order
+    // own shard first, then bands that double (1, 2, 4 shards ...) so that tiles follow the arrival order
     const int tile_m = resolve_cta_group(p, tuning) == 2 ? 2 * kBM : kBM;
     const int tps = (m_local + tile_m - 1) / tile_m;
     p.group_m = tps < 8 ? tps : 8;
+    make_bands(p, world, tps, /*first_single=*/true, /*last_single=*/false);
   }
   const int bn = resolve_block_n(comm, p, tuning, 0);
   uint8_t* local_gather = op->gather[comm->rank] + parity * half_gather;
@@ -498,18 +521,24 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   p.scale_b = scale_b;
   p.alpha = alpha;
   p.b_mn_major = (flags & FLUXB_WEIGHT_KN) ? 1 : 0;
+  // Partials cross NVLink in the output's 16-bit format (half the bytes of fp32; the owner still sums in
+  // fp32 and rounds once more at the end). Slots keep their fp32-sized stride; 16-bit data fills the
+  // first half of a peer's slot, the owner's own slot holds the fp32 sum of the peers' partials.
+  p.rs_wire16 = (ot == kOutBf16 || ot == kOutF16) && !(flags & FLUXB_RS_FP32_WIRE) ? 1 : 0;
   const size_t half_stage = static_cast<size_t>(op->max_m) * op->n_dim;
   for (int r = 0; r < world; ++r) {
     p.rs_stage[r] = op->stage[r] + parity * half_stage + static_cast<size_t>(comm->rank) * mpr * n;
     p.rs_cnt[r] = op->cnt[r] + parity * 2 * op->cnt_cap;
-    rc = encode_tmap_f32_store(&p.tmap_rs[r], p.rs_stage[r], mpr, n);
+    rc = p.rs_wire16 ? encode_tmap_b16_store(&p.tmap_rs[r], p.rs_stage[r], mpr, n)
+                     : encode_tmap_f32_store(&p.tmap_rs[r], p.rs_stage[r], mpr, n);
     if (rc != FLUXB_OK) return rc;
   }
   if (tuning == nullptr || tuning->group_m <= 0) {
-    // one owner per rasterisation band: rows owned by peers first, this rank's rows last
+    // rows owned by peers first, in bands of up to 8 M tiles; this rank's own rows as the last band
     const int tile_m = resolve_cta_group(p, tuning) == 2 ? 2 * kBM : kBM;
     const int tps = (mpr + tile_m - 1) / tile_m;
     p.group_m = tps < 8 ? tps : 8;
+    make_bands(p, world, tps, /*first_single=*/false, /*last_single=*/true);
   }
   const int bn = resolve_block_n(comm, p, tuning, 0);
   const long long row_bytes = static_cast<long long>(k_local) * eb;

@@ -80,6 +80,7 @@ int encode_tmap_kn(CUtensorMap* out, const void* base, int elt_dtype, long long 
 
 // fp32 [rows, n] row-major matrix, 32 x 32 element boxes, 128-byte swizzle (reduce-scatter pushes)
 int encode_tmap_f32_store(CUtensorMap* out, const void* base, long long rows, long long n);
+int encode_tmap_b16_store(CUtensorMap* out, const void* base, long long rows, long long n);
 
 // Output tile width for a problem: the caller's choice, else a wave-quantisation heuristic.
 // `m_tiles_hint` > 0 overrides the M-tile count derived from the segments (grouped problems).

@@ -98,6 +98,24 @@ int encode_tmap_f32_store(CUtensorMap* out, const void* base, long long rows, lo
   return FLUXB_OK;
 }
 
+// Store map over a [rows, n] matrix of 16-bit elements: 32-row x 64-column boxes (128-byte rows, 128-byte swizzle).
+int encode_tmap_b16_store(CUtensorMap* out, const void* base, long long rows, long long n) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (fn == nullptr) FLUXB_FAIL(FLUXB_ERR_CUDA, "cuTensorMapEncodeTiled is not available");
+  FLUXB_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0 && (n * 2) % 16 == 0 && rows > 0 && n > 0,
+                "store tensor map: base and row pitch must be 16-byte aligned (rows=%lld n=%lld)", rows, n);
+  cuuint64_t dims[2] = {static_cast<cuuint64_t>(n), static_cast<cuuint64_t>(rows)};
+  cuuint64_t strides[1] = {static_cast<cuuint64_t>(n) * 2};
+  cuuint32_t box[2] = {64, 32};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    FLUXB_FAIL(FLUXB_ERR_CUDA, "cuTensorMapEncodeTiled (16-bit store map) failed with CUresult %d", static_cast<int>(r));
+  return FLUXB_OK;
+}
+
 // One block, one thread per peer. Epoch-valued handshake: rank r stores the
 // epoch into slot r of every peer's array, then waits until every slot of its
 // own array has reached the epoch. Values only grow, so nothing is reset.

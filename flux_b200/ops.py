@@ -304,6 +304,9 @@ class GemmRS:
         self.input_dtype = input_dtype
         self.output_dtype = _out_dtype(input_dtype, output_dtype)
         self.transpose_weight = bool(transpose_weight)
+        # Partial sums travel to their owner in the 16-bit output format (as in the reference, which reduces
+        # in the output dtype); set to True to send them as fp32 at twice the NVLink bytes.
+        self.fp32_wire = False
         lib = _lib.load()
         w = self.comm.world
         self._stage = SymmBuffer(self.comm, lib.fluxb_gemm_rs_stage_bytes(self.max_m, self.n_dim, w))
@@ -334,6 +337,8 @@ class GemmRS:
         if self.transpose_weight:
             _check(not is_fp8_dtype(self.input_dtype), "GemmRS: fp8 does not support transpose_weight")
             flags |= _lib.WEIGHT_KN  # [K, N] weight read in place as an MN-major operand
+        if self.fp32_wire:
+            flags |= _lib.RS_FP32_WIRE
         if not weight.is_contiguous():
             weight = weight.contiguous()
         _check(input.is_contiguous(), "GemmRS: input must be contiguous")

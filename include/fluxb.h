@@ -49,6 +49,9 @@ extern "C" {
 /* `flags` of the GEMM entry points */
 #define FLUXB_WEIGHT_KN 1 /* the weight is [K,N] with N contiguous ("RRR", transpose_weight=True in the
                              reference, src/ag_gemm/ths_op/gemm_with_barrier.cc:55,196-197); 16-bit inputs only */
+#define FLUXB_RS_FP32_WIRE 2 /* fluxb_gemm_rs_forward: send the partial sums to their owner as fp32 instead of
+                                the 16-bit output format (the reference reduces in the output format,
+                                src/gemm_rs/ths_op/gemm_reduce_scatter.cc:335-899); twice the NVLink bytes */
 
 typedef struct fluxb_comm* fluxb_comm_t;
 typedef struct fluxb_ag_gemm* fluxb_ag_gemm_t;

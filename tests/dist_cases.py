@@ -45,7 +45,7 @@ def ag_gemm_case(rank, world, shapes, dtype_name, with_bias, tuning):
             f"rank {rank} call {it}: gathered input differs from all_gather"
 
 
-def gemm_rs_case(rank, world, shapes, dtype_name, with_bias, tuning):
+def gemm_rs_case(rank, world, shapes, dtype_name, with_bias, tuning, fp32_wire=False):
     """GemmRS.forward vs the gloo golden path, several calls on one op."""
     import flux_b200 as flux
     from oracle import golden
@@ -58,6 +58,7 @@ def gemm_rs_case(rank, world, shapes, dtype_name, with_bias, tuning):
     max_m = max(s[0] for s in shapes)
     n = shapes[0][1]
     op = flux.GemmRS(group, 1, max_m, n, dtype)
+    op.fp32_wire = fp32_wire
     for it, (m, nn, k_local) in enumerate(shapes):
         assert nn == n
         a, b = _inputs(rank, m, n, k_local, dtype, seed=4321 + 17 * it)
@@ -65,7 +66,8 @@ def gemm_rs_case(rank, world, shapes, dtype_name, with_bias, tuning):
         if with_bias:
             g = torch.Generator().manual_seed(77 + rank + it)
             bias = (torch.randn(m, n, generator=g) * 0.1).to(dtype)
-        # golden: fp32 partials over gloo (the reference reduces the rounded partials; the product keeps fp32)
+        # golden: fp32 partials over gloo (the reference and the product's default reduce partials that were
+        # rounded to the output format; fp32_wire keeps them fp32)
         part = golden._rs_partial(a, b, bias, None, None).float().contiguous()
         dist.all_reduce(part, group=group)
         mpr = m // world

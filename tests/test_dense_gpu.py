@@ -205,6 +205,16 @@ def test_gemm_rs_multi_rank(with_bias):
     run_distributed(dist_cases.gemm_rs_case, w, shapes, "bfloat16", with_bias, None)
 
 
+def test_gemm_rs_fp32_wire_multi_rank():
+    """Partials sent as fp32 (FLUXB_RS_FP32_WIRE) instead of the 16-bit output format, and fp16 outputs."""
+    _need(2)
+    w = min(gpu_count(), 8)
+    w = 1 << (w.bit_length() - 1)
+    shapes = [(512, 512, 512), (200 * w, 512, 1024), (8 * w, 512, 512)]
+    run_distributed(dist_cases.gemm_rs_case, w, shapes, "bfloat16", False, None, True)
+    run_distributed(dist_cases.gemm_rs_case, w, shapes, "float16", False, None, False)
+
+
 def test_fp8_multi_rank():
     _need(2)
     w = min(gpu_count(), 8)
