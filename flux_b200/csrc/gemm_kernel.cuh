@@ -43,8 +43,6 @@ constexpr int kRowBytes = 128;    // bytes of K per smem row (one swizzle span)
 constexpr int kThreads = 320;
 constexpr int kMaxWorld = 8;
 constexpr int kCommSliceBytes = 2048;  // bytes of one row handled by one comm unit
-constexpr int kAgBulkDefault = 0;    // default of GemmParams::ag_bulk
-constexpr int kRsDirectDefault = 0;  // default of GemmParams::rs_direct
 constexpr int kAgSubRows = 32;         // rows of one all-gather push unit; kBM / kAgSubRows units signal one chunk flag
 
 enum EpiMode : int {
@@ -73,8 +71,6 @@ struct GemmParams {
   // segment; segments are visited (seg_first + i) % nseg.
   int nseg, seg_rows, seg_first;
   int group_m;  // rasterisation band height in M tiles (uniform bands, used when n_bands == 0)
-  int ag_bulk;    // all-gather push with bulk copies through shared memory instead of register copies
-  int rs_direct;  // reduce-scatter: the epilogue of an own tile reads the peers' 16-bit partials itself
   int rs_wire16;  // reduce-scatter partials cross NVLink in the 16-bit output format instead of fp32
   int n_bands;  // > 0: explicit bands, band b covers M tiles [band_end[b-1], band_end[b])
   int band_end[8];
@@ -153,14 +149,12 @@ struct SmemLayout {
   static constexpr int kEpiPitch = 128;
   static constexpr int kEpiBlockBytes = 32 * kEpiPitch;
   static constexpr int kEpiOffset = STAGES * kStageBytes;
-  static constexpr int kEpiBufs = (kEpiOffset + 8 * kEpiBlockBytes + (2 * STAGES + 4) * 8 + 128 + 1024 <= 232448) ? 2 : 1;
+  static constexpr int kEpiBufs = (kEpiOffset + 8 * kEpiBlockBytes + (2 * STAGES + 4) * 8 + 64 + 1024 <= 232448) ? 2 : 1;
   static constexpr int kEpiWarpBytes = kEpiBufs * kEpiBlockBytes;
   static constexpr int kBarOffset = kEpiOffset + 4 * kEpiWarpBytes;
   static constexpr int kNumBars = 2 * STAGES + 4;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
-  // misc: tensor-memory address, abort word, a flag word, then 8 mbarriers of the comm warps' bulk copies
-  static constexpr int kCommBarOffset = kMiscOffset + 64;
-  static constexpr int kTotal = kMiscOffset + 128 + 1024;  // + slack for 1024-byte alignment
+  static constexpr int kTotal = kMiscOffset + 64 + 1024;  // + slack for 1024-byte alignment
 };
 
 struct TileCoord {
@@ -292,7 +286,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       mbar_init(bar_tfull(a), 1);
       mbar_init(bar_tempty(a), CTA2 ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
     }
-    for (int b = 0; b < 8; ++b) mbar_init(smem_base + L::kCommBarOffset + 8u * b, 1);
     mbar_init_fence();
     tma_prefetch_desc(&p.tmap_a);
     tma_prefetch_desc(&p.tmap_b);
@@ -637,10 +630,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         int okw = 1;
         if (lane == 0) {
           const uint64_t w0 = (tr != nullptr && warp == 2) ? globaltimer_ns() : 0;
-          if (p.rs_direct)  // every peer has published this tile (4 arrivals each)
-            okw = flag_wait_eq(p.rs_local_cnt + tc.chunk * n_tiles + tc.n_idx, 4 * (p.world - 1), s_abort,
-                               kStatusTimeoutReduce, budget) ? 1 : 0;
-          else
           okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 4, s_abort, kStatusTimeoutReduce,
                              budget) ? 1 : 0;
           if (tr != nullptr && warp == 2) tr[6] += globaltimer_ns() - w0;
@@ -735,39 +724,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
             }
           }
         }
-        if (own && active && p.rs_direct) {
-          // add the peers' 16-bit partials of this lane's row in rank order: one 8-column piece at a time,
-          // all peers' loads of the piece in flight together
-          const long long slot16 = 2ll * p.seg_rows * p.N;  // slots keep their fp32-sized stride
-          const uint16_t* prow = reinterpret_cast<const uint16_t*>(p.rs_local_stage) +
-                                 (static_cast<long long>(tc.chunk) * kBM + row_in_tile) * p.N + col0;
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            if (col0 + q * 8 < p.N) {  // N % 8 == 0: a piece is inside the matrix or outside it
-              uint4 pv[kMaxWorld];
-#pragma unroll
-              for (int sr = 0; sr < kMaxWorld; ++sr)
-                if (sr < p.world && sr != p.rank)
-                  pv[sr] = *reinterpret_cast<const uint4*>(prow + sr * slot16 + q * 8);
-#pragma unroll
-              for (int sr = 0; sr < kMaxWorld; ++sr)
-                if (sr < p.world && sr != p.rank) {
-                  const uint32_t w[4] = {pv[sr].x, pv[sr].y, pv[sr].z, pv[sr].w};
-#pragma unroll
-                  for (int j = 0; j < 4; ++j) {
-                    if (p.rs_out_type == kOutBf16) {
-                      v[q * 8 + 2 * j] += __uint_as_float(w[j] << 16);
-                      v[q * 8 + 2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
-                    } else {
-                      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
-                      v[q * 8 + 2 * j] += f.x;
-                      v[q * 8 + 2 * j + 1] += f.y;
-                    }
-                  }
-                }
-            }
-          }
-        } else if (own && active) {
+        if (own && active) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             if (col0 + q * 4 + 4 <= p.N) {
@@ -916,82 +873,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     }
   } else {
     // ----------------------------------------------------------------- comm
-    if (p.ag_src != nullptr && p.ag_bulk) {
-      // Push with the copy engine. A shard is one contiguous block of seg_rows x row_bytes on both sides, so
-      // each comm warp moves 4 KB pieces: bulk load into one of its staging blocks (the epilogue's push
-      // staging, unused in this mode), bulk store to the peer, publish on the destination's chunk counter
-      // two pieces late (so that waiting for a store's completion does not stall the next copies).
-      // Pieces are ordered destination by destination (rank-1 first: it needs this shard soonest) and
-      // interleaved over all comm warps of the grid. Every piece index of a 128-row chunk signals 1, also
-      // the empty ones of a ragged last chunk, so the receiver always waits for pieces-per-chunk arrivals.
-      constexpr int kPiece = L::kEpiBlockBytes;  // 4096
-      constexpr int NB = L::kEpiBufs;
-      const int cw = warp - 6;
-      const uint32_t buf0 = smem_base + L::kEpiOffset + cw * L::kEpiWarpBytes;
-      const uint32_t cbar0 = smem_base + L::kCommBarOffset + 16u * cw;
-      const int chunks = (p.seg_rows + kBM - 1) / kBM;
-      const long long chunk_bytes = static_cast<long long>(kBM) * p.ag_row_bytes;
-      const int ppc = static_cast<int>((chunk_bytes + kPiece - 1) / kPiece);
-      const int per_dest = chunks * ppc;
-      const int d_first = p.a_own_valid ? 1 : 0;
-      const long long total = static_cast<long long>(p.world - d_first) * per_dest;
-      const long long nwarps = static_cast<long long>(gridDim.x) * 4;
-      int* pend[2] = {nullptr, nullptr};
-      int used = 0;  // non-empty pieces so far (lane 0): selects the staging block and the barrier phase
-      bool ok = true;
-      for (long long i = static_cast<long long>(blockIdx.x) * 4 + cw; i < total && ok; i += nwarps) {
-        const int d = d_first + static_cast<int>(i / per_dest);
-        const int rem = static_cast<int>(i - static_cast<long long>(d - d_first) * per_dest);
-        const int chunk = rem / ppc;
-        const int j = rem - chunk * ppc;
-        int dest = p.rank - d;
-        if (dest < 0) dest += p.world;
-        const int rows_c = imin(kBM, p.seg_rows - chunk * kBM);
-        const long long cb = static_cast<long long>(rows_c) * p.ag_row_bytes;
-        const long long o0 = static_cast<long long>(j) * kPiece;
-        const uint32_t bytes = o0 < cb ? static_cast<uint32_t>(cb - o0 < kPiece ? cb - o0 : kPiece) : 0u;
-        const long long src_off = static_cast<long long>(chunk) * chunk_bytes + o0;
-        const int b = used % NB;
-        const uint32_t buf = buf0 + b * kPiece;
-        const uint32_t cbar = cbar0 + 8u * b;
-        if (j == 0 && p.ag_src_scale != nullptr) {
-          float* sd = p.ag_dst_scale[dest] + static_cast<long long>(p.rank) * p.seg_rows;
-          for (int rr = chunk * kBM + lane; rr < chunk * kBM + rows_c; rr += 32) sd[rr] = p.ag_src_scale[rr];
-        }
-        __syncwarp();
-        if (lane == 0) {
-          if (bytes > 0) {
-            // the store that last used this block has read it (it is at least NB groups back)
-            if (NB == 2) bulk_wait_read_keep1(); else bulk_wait_read();
-            mbar_arrive_expect_tx(cbar, bytes);
-            bulk_load(buf, p.ag_src + src_off, bytes, cbar);
-            ok = mbar_wait(cbar, static_cast<uint32_t>((used / NB) & 1), s_abort, kStatusTimeoutFlag, budget);
-            ++used;
-            if (ok)
-              bulk_store(p.ag_dst[dest] + static_cast<long long>(p.rank) * p.seg_rows * p.ag_row_bytes + src_off,
-                         buf, bytes);
-          }
-          bulk_commit();
-          if (pend[0] != nullptr) {
-            bulk_wait_all_but<2>();
-            fence_acq_rel_sys();
-            red_add_release_sys(pend[0], 1);
-          }
-          pend[0] = pend[1];
-          pend[1] = p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk;
-        }
-        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      }
-      if (lane == 0) {
-        bulk_wait_all();  // also after a failed wait: no copy may outlive the CTA
-        if (ok) {
-          fence_acq_rel_sys();
-          if (pend[0] != nullptr) red_add_release_sys(pend[0], 1);
-          if (pend[1] != nullptr) red_add_release_sys(pend[1], 1);
-        }
-      }
-      __syncwarp();
-    } else if (p.ag_src != nullptr) {
+    if (p.ag_src != nullptr) {
       const int ctid = threadIdx.x - 6 * 32;  // 0..127
       const int chunks = (p.seg_rows + kBM - 1) / kBM;
       const int nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
@@ -1109,7 +991,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         }
       }
     }
-      if (p.epi_mode == kEpiRsPush && !p.rs_direct) {
+      if (p.epi_mode == kEpiRsPush) {
       // Owner side of the reduce-scatter. Work item = 32 rows of one 128 x BN tile of this rank's rows:
       // wait (bounded) until every peer has published the tile (4 arrivals per peer: one per epilogue
       // warp), sum the peers' partials in fp32 in rank order into this rank's own slot, and add 1 to the

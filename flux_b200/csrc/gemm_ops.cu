@@ -380,8 +380,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   p.alpha = alpha;
   p.ag_flags = op->flags[comm->rank] + parity * half_flags;
   p.ag_flag_stride = op->flag_stride;
-  p.ag_bulk = kAgBulkDefault ^ (variant_bits() & 1);
-  p.ag_expected = ag_expected_count(row_bytes, p.ag_bulk != 0);
+  p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes) * (kBM / kAgSubRows);
   p.ag_src = static_cast<const uint8_t*>(a_shard);
   p.ag_row_bytes = row_bytes;
   p.ag_src_scale = scale_a_shard;
@@ -526,7 +525,6 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   // fp32 and rounds once more at the end). Slots keep their fp32-sized stride; 16-bit data fills the
   // first half of a peer's slot, the owner's own slot holds the fp32 sum of the peers' partials.
   p.rs_wire16 = (ot == kOutBf16 || ot == kOutF16) && !(flags & FLUXB_RS_FP32_WIRE) ? 1 : 0;
-  p.rs_direct = p.rs_wire16 ? (kRsDirectDefault ^ ((variant_bits() >> 1) & 1)) : 0;
   const size_t half_stage = static_cast<size_t>(op->max_m) * op->n_dim;
   for (int r = 0; r < world; ++r) {
     p.rs_stage[r] = op->stage[r] + parity * half_stage + static_cast<size_t>(comm->rank) * mpr * n;

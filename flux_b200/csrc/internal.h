@@ -80,11 +80,6 @@ int encode_tmap_kn(CUtensorMap* out, const void* base, int elt_dtype, long long 
 
 // fp32 [rows, n] row-major matrix, 32 x 32 element boxes, 128-byte swizzle (reduce-scatter pushes)
 int encode_tmap_f32_store(CUtensorMap* out, const void* base, long long rows, long long n);
-// Developer switch, read at every call: environment variable FLUXB_VARIANT, a bit mask that flips the
-// default of a protocol variant (bit 0: all-gather push, bit 1: reduce-scatter owner-side sum).
-int variant_bits();
-// pieces-per-chunk arrivals a receiver of the all-gather push waits for
-int ag_expected_count(long long row_bytes, bool bulk);
 int encode_tmap_b16_store(CUtensorMap* out, const void* base, long long rows, long long n);
 
 // Output tile width for a problem: the caller's choice, else a wave-quantisation heuristic.

@@ -422,8 +422,7 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   if (world > 1 && !reuse) {
     p.ag_flags = op->flags[comm->rank] + parity * half_flags;
     p.ag_flag_stride = op->flag_stride;
-    p.ag_bulk = kAgBulkDefault ^ (variant_bits() & 1);
-    p.ag_expected = ag_expected_count(row_bytes, p.ag_bulk != 0);
+    p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes) * (kBM / kAgSubRows);
     p.ag_src = static_cast<const uint8_t*>(tokens_shard);
     for (int r = 0; r < world; ++r) {
       p.ag_dst[r] = op->gather[r] + parity * half_gather;

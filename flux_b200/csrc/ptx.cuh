@@ -337,14 +337,6 @@ __device__ __forceinline__ void tma_gather4_2d_2cta(uint32_t smem_dst, const voi
 // bulk copies shared -> global (used to push row segments to peer memory in
 // full 128-byte pieces instead of per-lane 16-byte stores)
 // ----------------------------------------------------------------------------
-// 1-D bulk load global -> shared (no multicast); completion is counted in bytes on the mbarrier.
-// Both addresses 16-byte aligned, size a multiple of 16 bytes.
-__device__ __forceinline__ void bulk_load(uint32_t smem_dst, const void* gsrc, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(smem_dst),
-      "l"(gsrc), "r"(bytes), "r"(bar)
-      : "memory");
-}
 __device__ __forceinline__ void bulk_store(void* gdst, uint32_t smem_src, uint32_t bytes) {
   asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_src),
                "r"(bytes)

@@ -2,7 +2,6 @@
 // CUDA IPC handles, the bounded all-rank barrier, tensor-map encoding.
 // Stands in for src/ths_op/flux_shm.cc and src/cuda/cudaipc_barrier_all.cu of
 // the reference (no NVSHMEM, no NCCL).
-#include <cstdlib>
 #include <string.h>
 
 #include "internal.h"
@@ -97,16 +96,6 @@ int encode_tmap_f32_store(CUtensorMap* out, const void* base, long long rows, lo
   if (r != CUDA_SUCCESS)
     FLUXB_FAIL(FLUXB_ERR_CUDA, "cuTensorMapEncodeTiled (store map) failed with CUresult %d", static_cast<int>(r));
   return FLUXB_OK;
-}
-
-int variant_bits() {
-  const char* e = getenv("FLUXB_VARIANT");
-  return e != nullptr ? atoi(e) : 0;
-}
-
-int ag_expected_count(long long row_bytes, bool bulk) {
-  if (bulk) return static_cast<int>((static_cast<long long>(kBM) * row_bytes + 4095) / 4096);  // 4 KB pieces
-  return static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes) * (kBM / kAgSubRows);
 }
 
 // Store map over a [rows, n] matrix of 16-bit elements: 32-row x 64-column boxes (128-byte rows, 128-byte swizzle).
