@@ -304,7 +304,12 @@ def run_ours(args):
             "roofline": {"bound": "tensor", "achieved": ag_tflops, "peak": sustained, "unit": "TFLOP/s",
                          "frac": ag_tflops / sustained, "frac_of_burst_peak": ag_tflops / burst,
                          "peak_source": f"{peak_src} cuBLAS bf16, sustained (kernel timed inside a long step)",
-                         "kernel": "fused_gemm_kernel (AG-GEMM launch)", "traffic": None},
+                         "kernel": "fused_gemm_kernel (AG-GEMM launch)",
+                         # ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the M=4096, N=6144, K=12288 launch:
+                         # 709.2 MB; DRAM traffic grows with the number of 6144-column blocks a launch covers
+                         "traffic": 709.2e6 * (N0 // world) / 6144.0,
+                         "traffic_source": "ncu capture of the N=6144 launch (profiles/), scaled by N/6144",
+                         "algorithmic_bytes": 2.0 * (M * K0 + (N0 // world) * K0 + M * (N0 // world))},
             "clocks": clocks,
             "sampled_max_rel_err": sampled_err,
             "wall_ms_timed_region": wall_ms,
