@@ -1,8 +1,8 @@
 """Generate the golden vectors under tests/golden/ from the reference's own code.
 
-Run in a checkout that has the reference mounted (default /root/reference):
+Run where a checkout of the reference (bytedance/flux) is available:
 
-    python tests/golden/make_golden.py [--reference /path/to/flux]
+    python tests/golden/make_golden.py --reference /path/to/flux
 
 The reference's pure-torch golden helpers live in `python/flux/testing/*.py`,
 which `import flux` (the compiled extension, not buildable here). This script
@@ -172,7 +172,7 @@ def gen_moe_l1(ref_root):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of a checkout of the reference")
     args = ap.parse_args()
     ref_root = Path(args.reference)
     _, moe_utils, ag, _ = load_reference_helpers(ref_root)
