@@ -6,7 +6,7 @@ is the intended drop-in spelling (names follow python/flux/cpp_mod.py:96-196).
 The compute lives in `libfluxb.so` (hand-written CUDA behind the C ABI of
 `include/fluxb.h`); there is no CPU or library fallback.
 """
-from . import util
+from . import layers, util
 from ._lib import FluxbError, Tuning
 from .ops import (
     AGKernel,
@@ -23,6 +23,7 @@ from .ops import (
     is_fp8_dtype,
     uniform_initialize,
 )
+from .layers import ColumnParallelLinear, MoEMLP, RowParallelLinear, TensorParallelMLP
 from .moe import GemmGroupedV3AGScatter, GemmGroupedV3GatherRS, calc_gather_index, calc_scatter_index
 from .shm import GroupBarrier, default_comm, flux_create_tensor_list, get_comm, init_flux_shm
 from .util import bench_func, get_arch, group_profile, torch_allclose, with_torch_deterministic
@@ -35,4 +36,5 @@ __all__ = [
     "GroupBarrier", "flux_create_tensor_list", "create_tensor_list", "get_comm", "init_flux_shm", "bench_func",
     "get_arch", "group_profile", "GemmGroupedV3AGScatter", "GemmGroupedV3GatherRS", "calc_scatter_index",
     "calc_gather_index", "default_comm", "torch_allclose", "with_torch_deterministic", "FluxbError", "Tuning", "util",
+    "layers", "ColumnParallelLinear", "RowParallelLinear", "TensorParallelMLP", "MoEMLP",
 ]

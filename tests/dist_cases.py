@@ -170,3 +170,44 @@ def fp8_case(rank, world, shapes):
         comm.check_status()
         err2 = golden.max_rel_err(out2, part[rank * mpr:(rank + 1) * mpr])
         assert err2 <= 3e-2, f"rank {rank} call {it}: fp8 GEMM-RS max rel err {err2}"
+
+
+def tp_mlp_case(rank, world):
+    """TensorParallelMLP forward + backward on `world` GPUs against the unsharded fp32 model (gloo gathers)."""
+    import flux_b200 as flux
+
+    group = dist.group.WORLD
+    flux.init_flux_shm(group)
+    comm = flux.get_comm(group)
+    comm.set_timeout_ms(5000)
+    hidden, ffn, tokens = 512, 256 * world, 128 * world
+    torch.manual_seed(21 + rank)
+    mlp = flux.TensorParallelMLP(hidden, ffn, tokens, group)
+    x_shard = torch.randn(tokens // world, hidden, device="cuda").bfloat16().requires_grad_(True)
+    g_shard = torch.randn(tokens // world, hidden, device="cuda").bfloat16()
+    y_shard = mlp(x_shard)
+    (y_shard.float() * g_shard.float()).sum().backward()
+    torch.cuda.synchronize()
+    comm.check_status()
+
+    def gather(t, dim):
+        parts = [torch.empty_like(t.cpu()) for _ in range(world)]
+        dist.all_gather(parts, t.detach().cpu().contiguous(), group=group)
+        return torch.cat(parts, dim=dim).float()
+
+    w1 = gather(mlp.fc1.weight, 0).requires_grad_(True)
+    w2 = gather(mlp.fc2.weight, 1).requires_grad_(True)
+    x = gather(x_shard, 0).requires_grad_(True)
+    g = gather(g_shard, 0)
+    y = torch.nn.functional.gelu((x @ w1.t()).bfloat16().float()) @ w2.t()
+    (y * g).sum().backward()
+    mpr, fl = tokens // world, ffn // world
+    rows, cols = slice(rank * mpr, (rank + 1) * mpr), slice(rank * fl, (rank + 1) * fl)
+
+    def rel(a, b):
+        return float((a.float().cpu() - b).abs().max() / b.abs().max())
+
+    assert rel(y_shard, y.detach()[rows]) <= 2e-2
+    assert rel(x_shard.grad, x.grad[rows]) <= 2e-2
+    assert rel(mlp.fc1.weight.grad, w1.grad[cols]) <= 2e-2
+    assert rel(mlp.fc2.weight.grad, w2.grad[:, cols]) <= 2e-2

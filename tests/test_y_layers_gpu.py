@@ -1,0 +1,84 @@
+"""Tensor-parallel layers (flux_b200/layers.py) on the GPU: forward and backward of the sequence-parallel MLP
+and the forward of the MoE block against unsharded fp32 torch models built from the same bf16 parameters
+(tolerance 1e-2 of the largest reference value for single GEMMs, 2e-2 for chained ones, as the reference's
+own bf16 tests use: test/python/moe_gather_rs/test_moe_gather_rs.py:397-411)."""
+import pytest
+import torch
+
+import dist_cases
+from _dist import run_distributed
+from conftest import gpu_count
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(x, ref):
+    return float((x.float() - ref.float()).abs().max() / ref.float().abs().max().clamp_min(1e-12))
+
+
+@pytest.mark.parametrize("with_bias", [False, True])
+def test_tp_mlp_world1(with_bias):
+    import flux_b200 as flux
+
+    flux.init_flux_shm(None)
+    hidden, ffn, tokens = 512, 1024, 384
+    torch.manual_seed(3)
+    mlp = flux.TensorParallelMLP(hidden, ffn, tokens, None, bias=with_bias)
+    if with_bias:
+        with torch.no_grad():
+            mlp.fc1.bias.normal_(std=0.1)
+            mlp.fc2.bias.normal_(std=0.1)
+    x = torch.randn(tokens, hidden, device="cuda").bfloat16().requires_grad_(True)
+    g = torch.randn(tokens, hidden, device="cuda").bfloat16()
+    y = mlp(x)
+    (y.float() * g.float()).sum().backward()
+    torch.cuda.synchronize()
+    flux.get_comm(None).check_status()
+
+    w1 = mlp.fc1.weight.detach().float().requires_grad_(True)
+    w2 = mlp.fc2.weight.detach().float().requires_grad_(True)
+    xr = x.detach().float().requires_grad_(True)
+    h = xr @ w1.t()
+    if with_bias:
+        h = h + mlp.fc1.bias.detach().float()
+    yr = torch.nn.functional.gelu(h.bfloat16().float()) @ w2.t()
+    if with_bias:
+        yr = yr + mlp.fc2.bias.detach().float()
+    (yr * g.float()).sum().backward()
+    assert y.shape == (tokens, hidden) and y.dtype == torch.bfloat16
+    assert _rel(y, yr) <= 2e-2
+    assert _rel(x.grad, xr.grad) <= 2e-2
+    assert _rel(mlp.fc1.weight.grad, w1.grad) <= 2e-2
+    assert _rel(mlp.fc2.weight.grad, w2.grad) <= 2e-2
+
+
+def test_moe_block_world1():
+    import flux_b200 as flux
+
+    flux.init_flux_shm(None)
+    hidden, ffn, nexperts, topk, tokens = 512, 1024, 4, 2, 256
+    torch.manual_seed(4)
+    blk = flux.MoEMLP(hidden, ffn, nexperts, topk, tokens, None)
+    x = torch.randn(tokens, hidden, device="cuda").bfloat16()
+    y = blk(x)
+    torch.cuda.synchronize()
+    flux.get_comm(None).check_status()
+    chosen, wts = blk.route(x)
+    ref = torch.zeros(tokens, hidden, device="cuda")
+    for e in range(nexperts):
+        for k in range(topk):
+            rows = (chosen[:, k] == e).nonzero().flatten()
+            if rows.numel() == 0:
+                continue
+            h = torch.nn.functional.gelu((x[rows].float() @ blk.w_up[e].detach().float().t()).bfloat16()).float()
+            ref[rows] += wts[rows, k:k + 1] * (h @ blk.w_down[e].detach().float().t())
+    assert y.shape == (tokens, hidden)
+    assert _rel(y, ref) <= 2e-2
+
+
+def test_tp_mlp_multi_rank():
+    if gpu_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    w = min(gpu_count(), 8)
+    w = 1 << (w.bit_length() - 1)
+    run_distributed(dist_cases.tp_mlp_case, w)
