@@ -6,7 +6,7 @@ is the intended drop-in spelling (names follow python/flux/cpp_mod.py:96-196).
 The compute lives in `libfluxb.so` (hand-written CUDA behind the C ABI of
 `include/fluxb.h`); there is no CPU or library fallback.
 """
-from . import layers, util
+from . import layers, tune, util
 from ._lib import FluxbError, Tuning
 from .ops import (
     AGKernel,
@@ -36,5 +36,5 @@ __all__ = [
     "GroupBarrier", "flux_create_tensor_list", "create_tensor_list", "get_comm", "init_flux_shm", "bench_func",
     "get_arch", "group_profile", "GemmGroupedV3AGScatter", "GemmGroupedV3GatherRS", "calc_scatter_index",
     "calc_gather_index", "default_comm", "torch_allclose", "with_torch_deterministic", "FluxbError", "Tuning", "util",
-    "layers", "ColumnParallelLinear", "RowParallelLinear", "TensorParallelMLP", "MoEMLP",
+    "layers", "tune", "ColumnParallelLinear", "RowParallelLinear", "TensorParallelMLP", "MoEMLP",
 ]

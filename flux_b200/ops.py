@@ -16,6 +16,7 @@ from typing import List, Optional
 import torch
 
 from . import _lib
+from . import tune as _tune
 from .shm import Comm, SymmBuffer, fluxb_dtype, get_comm
 
 
@@ -256,6 +257,8 @@ class AGKernel:
         if gathered_input is not None:
             _check(tuple(gathered_input.shape) == (m_local * w, k) and gathered_input.dtype == self.input_dtype
                    and gathered_input.is_contiguous(), "AGKernel: gathered_input has the wrong shape, dtype or layout")
+        if tuning is None and _tune.TABLE.records:
+            tuning = _tune.TABLE.get(_tune.record_key("ag_gemm", m_local * w, n, k, self.input_dtype, w))
         lib = _lib.load()
         _lib.check(
             lib.fluxb_ag_gemm_forward(
@@ -286,8 +289,22 @@ class AGKernel:
     def profiling(self, input, weight, bias=None, output=None, input_scale=None, weight_scale=None,
                   output_scale=None, fast_accum=False, transpose_weight=False, all_gather_option=None,
                   gathered_input=None, prof_ctx=None):
-        return self.forward(input, weight, bias, output, input_scale, weight_scale, output_scale, fast_accum,
-                            transpose_weight, all_gather_option, gathered_input)
+        """Sweep the tile shapes for this problem (every rank times every candidate, the slowest rank
+        decides), remember the winner for later `forward` calls of the same shape, add it to `prof_ctx`
+        and return the output computed with it (src/ag_gemm/ths_op/all_gather_gemm_op.cc:361-474)."""
+        w = self.comm.world
+        n = weight.shape[1] if transpose_weight else weight.shape[0]
+        key = _tune.record_key("ag_gemm", input.shape[0] * w, n, input.shape[1], self.input_dtype, w)
+
+        def run(t):
+            return self.forward(input, weight, bias, output, input_scale, weight_scale, output_scale, fast_accum,
+                                transpose_weight, all_gather_option, gathered_input, tuning=t if t else {})
+
+        best, table = _tune.sweep(run, self.comm.group)
+        rec = _tune.TABLE.put(key, best, min(ms for _, ms in table))
+        if prof_ctx is not None:
+            prof_ctx.records.append(_tune.record_line(key, rec))
+        return run(best)
 
 
 class GemmRS:
@@ -361,6 +378,8 @@ class GemmRS:
         sa = _expand_scale(input_scale, m, "input_scale")
         sb = _expand_scale(weight_scale, n, "weight_scale")
         out = torch.empty((m // w, n), dtype=self.output_dtype, device=input.device)
+        if tuning is None and _tune.TABLE.records:
+            tuning = _tune.TABLE.get(_tune.record_key("gemm_rs", m, n, k, self.input_dtype, w))
         lib = _lib.load()
         _lib.check(
             lib.fluxb_gemm_rs_forward(
@@ -383,8 +402,21 @@ class GemmRS:
 
     def profiling(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
                   fast_accum=False, prof_ctx=None, reduce_scatter_option=None):
-        return self.forward(input, weight, bias, input_scale, weight_scale, output_scale, fast_accum,
-                            reduce_scatter_option)
+        """Sweep the tile shapes for this problem; see `AGKernel.profiling`
+        (src/gemm_rs/ths_op/gemm_reduce_scatter.cc:902-960)."""
+        m, k = input.shape
+        n = weight.shape[1] if self.transpose_weight else weight.shape[0]
+        key = _tune.record_key("gemm_rs", m, n, k, self.input_dtype, self.comm.world)
+
+        def run(t):
+            return self.forward(input, weight, bias, input_scale, weight_scale, output_scale, fast_accum,
+                                reduce_scatter_option, tuning=t if t else {})
+
+        best, table = _tune.sweep(run, self.comm.group)
+        rec = _tune.TABLE.put(key, best, min(ms for _, ms in table))
+        if prof_ctx is not None:
+            prof_ctx.records.append(_tune.record_line(key, rec))
+        return run(best)
 
 
 def bitwise_check(a: torch.Tensor, b: torch.Tensor) -> bool:

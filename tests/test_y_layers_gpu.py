@@ -82,3 +82,35 @@ def test_tp_mlp_multi_rank():
     w = min(gpu_count(), 8)
     w = 1 << (w.bit_length() - 1)
     run_distributed(dist_cases.tp_mlp_case, w)
+
+
+def test_profiling_records_a_tuning():
+    """`profiling()` sweeps the tile shapes, returns a correct output and leaves a record that later
+    `forward` calls of the same shape pick up (src/ag_gemm/ths_op/all_gather_gemm_op.cc:361-474)."""
+    import flux_b200 as flux
+    from flux_b200 import tune
+    from oracle import golden
+
+    flux.init_flux_shm(None)
+    m, n, k = 512, 768, 1024
+    g = torch.Generator().manual_seed(8)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+    ref, _ = golden.ag_gemm_single([a], b)
+    ctx = flux.ProfilingContext("ag_gemm")
+    try:
+        ag = flux.AGKernel(None, 1, m, n, k, torch.bfloat16)
+        out = ag.profiling(a.cuda(), b.cuda(), prof_ctx=ctx)
+        torch.cuda.synchronize()
+        assert golden.max_rel_err(out, ref) <= 1e-2
+        key = tune.record_key("ag_gemm", m, n, k, torch.bfloat16, 1)
+        assert key in tune.TABLE.records and ctx.get_latest_record().startswith(f"fluxb_tuning[{key}]")
+        out2 = ag.forward(a.cuda(), b.cuda())
+        torch.cuda.synchronize()
+        assert golden.max_rel_err(out2, ref) <= 1e-2
+        rs = flux.GemmRS(None, 1, m, n, torch.bfloat16)
+        out3 = rs.profiling(a.cuda(), b.cuda(), prof_ctx=ctx)
+        torch.cuda.synchronize()
+        assert golden.max_rel_err(out3, ref) <= 1e-2 and len(ctx.get_all_record_codes()) == 2
+    finally:
+        tune.TABLE.records.clear()
