@@ -14,6 +14,7 @@ from .ops import (
     AllGatherOption,
     DistEnvTP,
     DistEnvTPWithEP,
+    GemmOnly,
     GemmRS,
     MoeArguments,
     ProfilingContext,
@@ -31,7 +32,7 @@ from .util import bench_func, get_arch, group_profile, torch_allclose, with_torc
 create_tensor_list = flux_create_tensor_list
 
 __all__ = [
-    "AGKernel", "AGRingMode", "AllGatherOption", "DistEnvTP", "DistEnvTPWithEP", "GemmRS", "MoeArguments",
+    "AGKernel", "AGRingMode", "AllGatherOption", "DistEnvTP", "DistEnvTPWithEP", "GemmOnly", "GemmRS", "MoeArguments",
     "ProfilingContext", "ReduceScatterOption", "RingMode", "bitwise_check", "is_fp8_dtype", "uniform_initialize",
     "GroupBarrier", "flux_create_tensor_list", "create_tensor_list", "get_comm", "init_flux_shm", "bench_func",
     "get_arch", "group_profile", "GemmGroupedV3AGScatter", "GemmGroupedV3GatherRS", "calc_scatter_index",

@@ -17,7 +17,7 @@ import torch
 
 from . import _lib
 from . import tune as _tune
-from .shm import Comm, SymmBuffer, fluxb_dtype, get_comm
+from .shm import Comm, SymmBuffer, default_comm, fluxb_dtype, get_comm
 
 
 def _check(cond: bool, msg: str) -> None:
@@ -417,6 +417,69 @@ class GemmRS:
         if prof_ctx is not None:
             prof_ctx.records.append(_tune.record_line(key, rec))
         return run(best)
+
+
+class GemmOnly:
+    """`flux.GemmOnly(input_dtype, output_dtype=None, transpose_weight=False, use_fp8_gemm=False)`: the plain
+    GEMM the reference uses as its unfused building block (src/pybind/gemm_only.cc; shapes and formulas in
+    python/flux/cpp_mod.pyi:215-253): output = input[M,K] @ weight[N,K].T (weight [K,N] if transpose_weight),
+    fp8 with scalar or per-row / per-channel scales, bias [M,N] (16-bit) or [1,N]. Same kernel as the fused
+    ops, without communication. The int8 modes are not supported."""
+
+    def __init__(self, input_dtype, output_dtype=None, transpose_weight=False, use_fp8_gemm=False):
+        _check(input_dtype in (torch.bfloat16, torch.float16) or is_fp8_dtype(input_dtype),
+               f"GemmOnly: input dtype {input_dtype} is not supported (bf16, fp16, fp8 only)")
+        _check(not (transpose_weight and is_fp8_dtype(input_dtype)), "GemmOnly: fp8 does not support transpose_weight")
+        self.input_dtype = input_dtype
+        self.output_dtype = _out_dtype(input_dtype, output_dtype)
+        self.transpose_weight = bool(transpose_weight)
+        try:
+            self.comm: Comm = default_comm()
+        except RuntimeError:
+            self.comm = get_comm(None)
+
+    def forward(self, input, weight, bias=None, output_buf=None, input_scale=None, weight_scale=None,
+                output_scale=None, fast_accum=False, tuning=None):
+        _check(input.is_cuda and weight.is_cuda, "GemmOnly: tensors must be CUDA tensors")
+        _check(input.dim() == 2 and weight.dim() == 2, "GemmOnly: input and weight must be 2-D")
+        _check(input.dtype == self.input_dtype and weight.dtype == self.input_dtype, "GemmOnly: dtype mismatch")
+        _check(output_scale is None, "GemmOnly: output_scale is not supported")
+        _check(input.is_contiguous(), "GemmOnly: input must be contiguous")
+        if not weight.is_contiguous():
+            weight = weight.contiguous()
+        m, k = input.shape
+        n = weight.shape[1] if self.transpose_weight else weight.shape[0]
+        wk = weight.shape[0] if self.transpose_weight else weight.shape[1]
+        _check(wk == k, f"GemmOnly: weight K {wk} != input K {k}")
+        if output_buf is None:
+            output_buf = torch.empty((m, n), dtype=self.output_dtype, device=input.device)
+        else:
+            _check(tuple(output_buf.shape) == (m, n) and output_buf.dtype == self.output_dtype
+                   and output_buf.is_contiguous(), "GemmOnly: output_buf has the wrong shape, dtype or layout")
+        bias_mode = _lib.BIAS_NONE
+        if bias is not None:
+            _check(bias.dtype == self.output_dtype and bias.is_contiguous(), "GemmOnly: bias dtype/layout")
+            if tuple(bias.shape) == (m, n):
+                bias_mode = _lib.BIAS_MN
+            elif tuple(bias.shape) in ((1, n), (n,)):
+                bias_mode = _lib.BIAS_1N
+            else:
+                raise RuntimeError(f"GemmOnly: bias shape {tuple(bias.shape)} is neither [M,N] nor [1,N]")
+        sa = _expand_scale(input_scale, m, "input_scale")
+        sb = _expand_scale(weight_scale, n, "weight_scale")
+        _lib.check(
+            _lib.load().fluxb_gemm(
+                self.comm.handle, input.data_ptr(), weight.data_ptr(), output_buf.data_ptr(), m, n, k,
+                fluxb_dtype(self.input_dtype), fluxb_dtype(self.output_dtype), _ptr(bias), bias_mode,
+                _ptr(sa), _ptr(sb), 1.0, _lib.WEIGHT_KN if self.transpose_weight else 0, _tuning(tuning),
+                _cur_stream(),
+            )
+        )
+        return output_buf
+
+    def profiling(self, input, weight, bias=None, output_buf=None, input_scale=None, weight_scale=None,
+                  output_scale=None, fast_accum=False, prof_ctx=None):
+        return self.forward(input, weight, bias, output_buf, input_scale, weight_scale, output_scale, fast_accum)
 
 
 def bitwise_check(a: torch.Tensor, b: torch.Tensor) -> bool:

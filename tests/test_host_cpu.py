@@ -84,3 +84,17 @@ def test_build_recipe_lists_every_source():
     names = {p.name for p in build.sources()}
     assert {"gemm_ops.cu", "moe_ops.cu", "moe_index.cu", "runtime.cu"} <= names
     assert "arch=compute_100a,code=sm_100a" in build.NVCC_FLAGS
+
+
+def test_gemm_only_rejects_unsupported_modes():
+    """GemmOnly's int8 modes and fp8 with transposed weights are refused at construction
+    (python/flux/cpp_mod.pyi:215-253 lists the modes; src/ag_gemm/ths_op/gemm_with_barrier.cc:188 the fp8 rule)."""
+    import pytest
+    import torch
+
+    import flux_b200 as flux
+
+    with pytest.raises(RuntimeError):
+        flux.GemmOnly(torch.int8)
+    with pytest.raises(RuntimeError):
+        flux.GemmOnly(torch.float8_e4m3fn, transpose_weight=True)

@@ -114,3 +114,25 @@ def test_profiling_records_a_tuning():
         assert golden.max_rel_err(out3, ref) <= 1e-2 and len(ctx.get_all_record_codes()) == 2
     finally:
         tune.TABLE.records.clear()
+
+
+@pytest.mark.parametrize("transpose_weight", [False, True])
+def test_gemm_only_op(transpose_weight):
+    """`flux.GemmOnly` (python/flux/cpp_mod.pyi:215-253): plain GEMM with [N,K] or [K,N] weights and a [1,N] bias."""
+    import flux_b200 as flux
+    from oracle import golden
+
+    flux.init_flux_shm(None)
+    m, n, k = 384, 640, 512
+    g = torch.Generator().manual_seed(12)
+    a = torch.randn(m, k, generator=g).bfloat16()
+    b = (torch.randn(n, k, generator=g) * 0.02).bfloat16()
+    bias = (torch.randn(1, n, generator=g) * 0.1).bfloat16()
+    ref, _ = golden.ag_gemm_single([a], b, bias=bias)
+    op = flux.GemmOnly(torch.bfloat16, transpose_weight=transpose_weight)
+    w = b.t().contiguous().cuda() if transpose_weight else b.cuda()
+    out = op.forward(a.cuda(), w, bias=bias.cuda())
+    torch.cuda.synchronize()
+    op.comm.check_status()
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16
+    assert golden.max_rel_err(out, ref) <= 1e-2
