@@ -232,13 +232,15 @@ class MoEMLP(torch.nn.Module):
          and weights of all ranks are all-gathered (T x topk numbers) because the routing is global;
       2. `calc_scatter_index` / `calc_gather_index` give each (token, k) pair its row in expert order;
       3. layer 0: all-gather of the tokens + scatter + grouped GEMM in one kernel (`GemmGroupedV3AGScatter`);
-      4. activation;
+      4. activation; with `gated=True` (SwiGLU-style) a second up projection `w_gate` runs over the same gathered
+         tokens (`forward_multiple_weights`: the all-gather happens once) and the activation is
+         `act(gate) * up`;
       5. layer 1: grouped GEMM + weighted top-k sum + reduce-scatter (`GemmGroupedV3GatherRS`), the routing
          weight of every row applied in fp32 through `output_vec_scale`.
     """
 
     def __init__(self, hidden: int, ffn_hidden: int, nexperts: int, topk: int, max_tokens: int, group=None,
-                 activation: Optional[Callable[[torch.Tensor], torch.Tensor]] = None,
+                 activation: Optional[Callable[[torch.Tensor], torch.Tensor]] = None, gated: bool = False,
                  dtype: torch.dtype = torch.bfloat16, device="cuda"):
         super().__init__()
         self.group = group
@@ -253,9 +255,16 @@ class MoEMLP(torch.nn.Module):
         self.router = torch.nn.Parameter(torch.empty((self.nexperts, self.hidden), dtype=torch.float32, device=device))
         self.w_up = torch.nn.Parameter(torch.empty((self.nexperts, ffn_local, self.hidden), dtype=dtype, device=device))
         self.w_down = torch.nn.Parameter(torch.empty((self.nexperts, self.hidden, ffn_local), dtype=dtype, device=device))
-        for w in (self.router, self.w_up, self.w_down):
-            torch.nn.init.normal_(w, std=0.02)
-        self.activation = activation if activation is not None else torch.nn.functional.gelu
+        self.w_gate = None
+        if gated:
+            self.w_gate = torch.nn.Parameter(torch.empty((self.nexperts, ffn_local, self.hidden), dtype=dtype,
+                                                         device=device))
+        for w in (self.router, self.w_up, self.w_down, self.w_gate):
+            if w is not None:
+                torch.nn.init.normal_(w, std=0.02)
+        if activation is None:
+            activation = torch.nn.functional.silu if gated else torch.nn.functional.gelu
+        self.activation = activation
         self._l0 = None
         self._l1 = None
 
@@ -286,7 +295,11 @@ class MoEMLP(torch.nn.Module):
         gather_index, topk_index = _gather_index(scatter_index)
         # routing weight of every expert-sorted row
         row_scale = weights.reshape(-1)[gather_index.long() * self.topk + topk_index.long()].contiguous()
-        act = self._l0.forward(x_shard.contiguous(), self.w_up, splits, scatter_index)
-        act = self.activation(act)
+        if self.w_gate is None:
+            act = self.activation(self._l0.forward(x_shard.contiguous(), self.w_up, splits, scatter_index))
+        else:
+            gate, up = self._l0.forward_multiple_weights(x_shard.contiguous(), [self.w_gate, self.w_up], splits,
+                                                         scatter_index)
+            act = self.activation(gate) * up
         return self._l1.forward_gather_rs(act, self.w_down, splits.cpu(), scatter_index.reshape(-1),
                                           output_vec_scale=row_scale)

@@ -170,6 +170,9 @@ class FakeL0:
         out, _ = golden.moe_ag_scatter_single(shards, weights.detach(), splits_gpu, scatter_index)
         return out
 
+    def forward_multiple_weights(self, inputs_shard, weights, splits_gpu, scatter_index):
+        return [self.forward(inputs_shard, w, splits_gpu, scatter_index) for w in weights]
+
 
 class FakeL1:
     """Interface of GemmGroupedV3GatherRS.forward_gather_rs, computed by the oracle."""
@@ -188,7 +191,7 @@ class FakeL1:
                                          output_vec_scale=output_vec_scale)
 
 
-def _moe_case(rank, world):
+def _moe_case(rank, world, gated=False):
     from flux_b200 import layers
     from oracle import golden
 
@@ -199,7 +202,7 @@ def _moe_case(rank, world):
     layers._make_moe_l1 = lambda group, max_tokens, hidden, nexperts, topk, dtype: FakeL1(group, topk)
     hidden, ffn, nexperts, topk, tokens = 16, 24, 4, 2, 6 * world
     torch.manual_seed(5 + rank)
-    blk = layers.MoEMLP(hidden, ffn, nexperts, topk, tokens, group, dtype=torch.float32, device="cpu")
+    blk = layers.MoEMLP(hidden, ffn, nexperts, topk, tokens, group, gated=gated, dtype=torch.float32, device="cpu")
     with torch.no_grad():
         g = torch.Generator().manual_seed(99)  # the router is replicated
         blk.router.copy_(torch.randn(nexperts, hidden, generator=g))
@@ -210,8 +213,10 @@ def _moe_case(rank, world):
         x = torch.cat(_gather_rows(x_shard, group, world), dim=0)
         w_up = torch.cat(_gather_rows(blk.w_up.detach(), group, world), dim=1)      # [E, ffn, hidden]
         w_down = torch.cat(_gather_rows(blk.w_down.detach(), group, world), dim=2)  # [E, hidden, ffn]
+        w_gate = torch.cat(_gather_rows(blk.w_gate.detach(), group, world), dim=1) if gated else None
     else:
         x, w_up, w_down = x_shard, blk.w_up.detach(), blk.w_down.detach()
+        w_gate = blk.w_gate.detach() if gated else None
     logits = x @ blk.router.detach().t()
     top, chosen = torch.topk(logits, topk, dim=1)
     wts = torch.softmax(top, dim=1)
@@ -219,7 +224,11 @@ def _moe_case(rank, world):
     for t in range(tokens):
         for k in range(topk):
             e = int(chosen[t, k])
-            ref[t] += wts[t, k] * (torch.nn.functional.gelu(x[t] @ w_up[e].t()) @ w_down[e].t())
+            if gated:
+                h = torch.nn.functional.silu(x[t] @ w_gate[e].t()) * (x[t] @ w_up[e].t())
+            else:
+                h = torch.nn.functional.gelu(x[t] @ w_up[e].t())
+            ref[t] += wts[t, k] * (h @ w_down[e].t())
     mpr = tokens // world
     torch.testing.assert_close(y_shard, ref[rank * mpr:(rank + 1) * mpr], rtol=1e-4, atol=1e-5)
 
@@ -230,3 +239,7 @@ def test_moe_block_world2():
 
 def test_moe_block_world1():
     run_distributed(_moe_case, 1, use_cuda=False)
+
+
+def test_moe_block_gated_world2():
+    run_distributed(_moe_case, 2, True, use_cuda=False)

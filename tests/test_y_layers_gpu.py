@@ -52,13 +52,14 @@ def test_tp_mlp_world1(with_bias):
     assert _rel(mlp.fc2.weight.grad, w2.grad) <= 2e-2
 
 
-def test_moe_block_world1():
+@pytest.mark.parametrize("gated", [False, True])
+def test_moe_block_world1(gated):
     import flux_b200 as flux
 
     flux.init_flux_shm(None)
     hidden, ffn, nexperts, topk, tokens = 512, 1024, 4, 2, 256
     torch.manual_seed(4)
-    blk = flux.MoEMLP(hidden, ffn, nexperts, topk, tokens, None)
+    blk = flux.MoEMLP(hidden, ffn, nexperts, topk, tokens, None, gated=gated)
     x = torch.randn(tokens, hidden, device="cuda").bfloat16()
     y = blk(x)
     torch.cuda.synchronize()
@@ -70,7 +71,12 @@ def test_moe_block_world1():
             rows = (chosen[:, k] == e).nonzero().flatten()
             if rows.numel() == 0:
                 continue
-            h = torch.nn.functional.gelu((x[rows].float() @ blk.w_up[e].detach().float().t()).bfloat16()).float()
+            up = (x[rows].float() @ blk.w_up[e].detach().float().t()).bfloat16()
+            if gated:
+                gate = (x[rows].float() @ blk.w_gate[e].detach().float().t()).bfloat16()
+                h = (torch.nn.functional.silu(gate) * up).float()
+            else:
+                h = torch.nn.functional.gelu(up).float()
             ref[rows] += wts[rows, k:k + 1] * (h @ blk.w_down[e].detach().float().t())
     assert y.shape == (tokens, hidden)
     assert _rel(y, ref) <= 2e-2
