@@ -144,7 +144,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
 /* ----------------------------------------------------------------- GEMM-RS
  * Replaces GemmRS (src/gemm_rs/ths_op/gemm_reduce_scatter.cc:335-408 ctor,
  * :552-660 forward_gemm_impl, :690-788 forward_reduce_scatter_impl).
- *   stage_bufs[r]: fluxb_gemm_rs_stage_bytes(...)   (fp32 partial tiles)
+ *   stage_bufs[r]: fluxb_gemm_rs_stage_bytes(...)   (partial tiles, slots of fp32 size)
  *   cnt_bufs[r]  : fluxb_gemm_rs_cnt_bytes(...)     (per-tile arrival counters) */
 size_t fluxb_gemm_rs_stage_bytes(int max_m, int n_dim, int world);
 size_t fluxb_gemm_rs_cnt_bytes(int max_m, int n_dim, int world);
@@ -152,7 +152,9 @@ int fluxb_gemm_rs_create(fluxb_comm_t comm, int max_m, int n_dim, int in_dtype, 
                          float* const* stage_bufs, int* const* cnt_bufs, fluxb_gemm_rs_t* out);
 int fluxb_gemm_rs_destroy(fluxb_gemm_rs_t op);
 /* out[m/world, n] = reduce_scatter_rows( a[m, k_local] . b[n, k_local]^T (+ bias) ).
- * Partials travel and are summed in fp32; the result is rounded once. */
+ * With a 16-bit output the partials travel to the owner of their rows in that
+ * format, as in the reference, are summed there in fp32 and rounded once more;
+ * FLUXB_RS_FP32_WIRE in `flags` (or an fp32 output) sends them as fp32. */
 int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int m, int n,
                           int k_local, void* out, const void* bias, int bias_mode,
                           const float* scale_a, const float* scale_b, float alpha, int flags,
