@@ -11,8 +11,10 @@ imported as they are (they import the compiled `flux` extension), so each
 function below restates one of them and cites it by the file's path inside
 bytedance/flux. Pinning: `tests/golden/` holds vectors produced by running the
 reference's own pure-torch helpers (loaded from its source files with a stub
-for the compiled module; `tests/golden/make_golden.py`) and the hand-computable
-`--debug` cases of its tests; `tests/test_oracle.py` checks this file against
+for the compiled module; `tests/golden/make_golden.py`), by running the dense
+golden functions of its test scripts (`perf_torch`, compiled unmodified from
+their source and run on 2 gloo ranks) and the hand-computable `--debug` cases
+of its tests; `tests/test_oracle.py` checks this file against
 both. The arithmetic itself is PyTorch's matmul and gloo/NCCL reductions on
 either side, so float parity is by tolerance (as in the reference's tests) and
 only routing/indexing is bit-exact.

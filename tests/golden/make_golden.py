@@ -14,6 +14,8 @@ then check `oracle/golden.py` against them without needing the reference.
 Nothing from the reference is copied: only its outputs are stored.
 """
 import argparse
+import ast
+import contextlib
 import importlib.util
 import os
 import socket
@@ -170,6 +172,102 @@ def gen_moe_l1(ref_root):
     print("moe_l1.pt:", len(outs), "cases")
 
 
+# ----------------------------------------------------------------------------- dense AG-GEMM / GEMM-RS (2 gloo ranks)
+class _NoCudaEvent:
+    """Timing events of the reference's golden functions; the timings are not used."""
+
+    def __init__(self, *a, **k):
+        pass
+
+    def record(self, *a, **k):
+        pass
+
+    def synchronize(self):
+        pass
+
+    def elapsed_time(self, other):
+        return 0.0
+
+
+class _TorchOnCpu:
+    """`torch` as the extracted functions see it: everything is the real module except `torch.cuda`, whose
+    events do nothing and whose current device is the CPU (the functions allocate on `current_device()`)."""
+
+    cuda = types.SimpleNamespace(Event=_NoCudaEvent, current_device=lambda: "cpu")
+
+    def __getattr__(self, name):
+        return getattr(torch, name)
+
+
+def _extract(ref_root: Path, rel: str, names):
+    """Compile the named top-level functions / classes of a reference script, unmodified, without running
+    the script (it parses arguments and needs the compiled extension at import)."""
+    path = ref_root / rel
+    tree = ast.parse(path.read_text(), filename=str(path))
+    keep = [n for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef)) and n.name in names]
+    assert len(keep) == len(names), f"{rel}: expected {names}"
+    return compile(ast.Module(body=keep, type_ignores=[]), str(path), "exec")
+
+
+def dense_inputs(case, rank, world):
+    """Seeded inputs of one rank for a dense case (m, n, k, dtype, with_bias); shared with tests/test_oracle.py."""
+    m, n, k, dtype, with_bias = case
+    g = torch.Generator().manual_seed(400 + rank)
+    out = {"ag_input": torch.randn(m // world, k, generator=g).to(dtype),
+           "ag_weight": (torch.randn(n // world, k, generator=g) * 0.05).to(dtype),
+           "ag_bias": (torch.randn(m, n // world, generator=g) * 0.1).to(dtype) if with_bias else None,
+           "rs_input": torch.randn(m, k // world, generator=g).to(dtype),
+           "rs_weight": (torch.randn(n, k // world, generator=g) * 0.05).to(dtype),
+           "rs_bias": (torch.randn(m, n, generator=g) * 0.1).to(dtype) if with_bias else None}
+    return out
+
+
+def _dense_worker(rank, world, port, ref_root, case, out_path):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    flux_stub, _ = _install_stub()
+    flux_stub.util.with_torch_deterministic = lambda mode, warn_only=True: contextlib.nullcontext()
+    from typing import Optional
+
+    base = {"torch": _TorchOnCpu(), "flux": flux_stub, "TP_GROUP": dist.group.WORLD, "WORLD_SIZE": world,
+            "RANK": rank, "Optional": Optional,
+            "zeros_with_fp8": lambda *a, **kw: torch.zeros(*a, **kw)}
+    d = dense_inputs(case, rank, world)
+    # AG-GEMM: test/python/ag_gemm/test_ag_kernel.py `perf_torch`
+    ns_ag = dict(base)
+    exec(_extract(Path(ref_root), "test/python/ag_gemm/test_ag_kernel.py", ["PerfResult", "perf_torch"]), ns_ag)
+    r_ag = ns_ag["perf_torch"](d["ag_input"], d["ag_weight"], d["ag_bias"], None, None, False, False, 0, 1)
+    # GEMM-RS: test/python/gemm_rs/test_gemm_rs.py `perf_torch`
+    ns_rs = dict(base)
+    exec(_extract(Path(ref_root), "test/python/gemm_rs/test_gemm_rs.py", ["PerfResult", "perf_torch"]), ns_rs)
+    r_rs = ns_rs["perf_torch"](d["rs_input"], d["rs_weight"], d["rs_bias"], 0, 1)
+    # only the outputs are stored; the test regenerates the seeded inputs with `dense_inputs`
+    mine = {"ag_out": r_ag.output.clone(), "ag_gathered_sum": r_ag.gathered_output.double().sum().item(),
+            "rs_out": r_rs.output.clone()}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
+    if rank == 0:
+        torch.save({"case": case, "ranks": gathered}, out_path)
+    dist.destroy_process_group()
+
+
+def gen_dense(ref_root):
+    outs = []
+    cases = [(256, 512, 512, torch.float32, False),   # the reference's CPU-runnable smoke shape
+             (64, 96, 128, torch.bfloat16, True), (48, 64, 64, torch.float16, True)]
+    for i, case in enumerate(cases):
+        with socket.socket() as s:
+            s.bind(("127.0.0.1", 0))
+            port = s.getsockname()[1]
+        tmp = HERE / f"_dense_{i}.pt"
+        mp.spawn(_dense_worker, args=(2, port, str(ref_root), case, str(tmp)), nprocs=2, join=True)
+        outs.append(torch.load(tmp, weights_only=False))
+        tmp.unlink()
+    torch.save(outs, HERE / "dense.pt")
+    print("dense.pt:", len(outs), "cases")
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference")
@@ -179,6 +277,7 @@ def main():
     gen_routing(moe_utils)
     gen_moe_l0(ag, moe_utils)
     gen_moe_l1(ref_root)
+    gen_dense(ref_root)
 
 
 if __name__ == "__main__":

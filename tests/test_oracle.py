@@ -163,3 +163,34 @@ def test_moe_identity_weights_roundtrip():
     vec = rw.reshape(-1)[(gi.long() * topk + ti.long())]
     out1 = golden.moe_gather_rs_single([out0], [eye], splits, si, topk, output_vec_scales=[vec])[0]
     assert torch.allclose(out1, tokens * rw.sum(1, keepdim=True), rtol=1e-5, atol=1e-6)
+
+
+def test_dense_matches_reference_vectors():
+    """Dense AG-GEMM and GEMM-RS: the oracle against outputs of the reference's own golden functions
+    (`perf_torch` of test/python/ag_gemm/test_ag_kernel.py:88-176 and test/python/gemm_rs/test_gemm_rs.py:57-157,
+    executed unmodified on 2 gloo ranks by tests/golden/make_golden.py). fp32 agrees to rounding of a
+    different summation order; 16-bit outputs to one rounding of the output format."""
+    import importlib.util
+
+    spec = importlib.util.spec_from_file_location("make_golden", os.path.join(GOLD, "make_golden.py"))
+    mg = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mg)
+    cases = _load("dense.pt")
+    assert len(cases) == 3
+    for c in cases:
+        case, ranks = c["case"], c["ranks"]
+        world = len(ranks)
+        dtype = case[3]
+        ins = [mg.dense_inputs(case, r, world) for r in range(world)]
+        tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else \
+            dict(rtol=1.6e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=2e-3, atol=2e-3)
+        rs_outs = golden.gemm_rs_single([i["rs_input"] for i in ins], [i["rs_weight"] for i in ins],
+                                        biases=[i["rs_bias"] for i in ins] if case[4] else None)
+        for r in range(world):
+            out, gathered = golden.ag_gemm_single([i["ag_input"] for i in ins], ins[r]["ag_weight"],
+                                                  bias=ins[r]["ag_bias"])
+            assert out.dtype == ranks[r]["ag_out"].dtype and out.shape == ranks[r]["ag_out"].shape
+            torch.testing.assert_close(out.float(), ranks[r]["ag_out"].float(), **tol)
+            assert abs(gathered.double().sum().item() - ranks[r]["ag_gathered_sum"]) <= 1e-6 * gathered.numel()
+            assert rs_outs[r].dtype == ranks[r]["rs_out"].dtype and rs_outs[r].shape == ranks[r]["rs_out"].shape
+            torch.testing.assert_close(rs_outs[r].float(), ranks[r]["rs_out"].float(), **tol)
