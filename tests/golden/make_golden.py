@@ -218,7 +218,13 @@ def dense_inputs(case, rank, world):
            "ag_bias": (torch.randn(m, n // world, generator=g) * 0.1).to(dtype) if with_bias else None,
            "rs_input": torch.randn(m, k // world, generator=g).to(dtype),
            "rs_weight": (torch.randn(n, k // world, generator=g) * 0.05).to(dtype),
-           "rs_bias": (torch.randn(m, n, generator=g) * 0.1).to(dtype) if with_bias else None}
+           "rs_bias": (torch.randn(m, n, generator=g) * 0.1).to(dtype) if with_bias else None,
+           "input_scale": None, "weight_scale": None}
+    if dtype in (torch.float8_e4m3fn, torch.float8_e5m2):
+        # the reference's fp8 golden takes one scalar scale per operand, the same on every rank
+        gs = torch.Generator().manual_seed(499)
+        out["input_scale"] = torch.rand(1, generator=gs) + 0.5
+        out["weight_scale"] = torch.rand(1, generator=gs) + 0.5
     return out
 
 
@@ -237,14 +243,17 @@ def _dense_worker(rank, world, port, ref_root, case, out_path):
     # AG-GEMM: test/python/ag_gemm/test_ag_kernel.py `perf_torch`
     ns_ag = dict(base)
     exec(_extract(Path(ref_root), "test/python/ag_gemm/test_ag_kernel.py", ["PerfResult", "perf_torch"]), ns_ag)
-    r_ag = ns_ag["perf_torch"](d["ag_input"], d["ag_weight"], d["ag_bias"], None, None, False, False, 0, 1)
+    is_fp8 = d["input_scale"] is not None
+    r_ag = ns_ag["perf_torch"](d["ag_input"], d["ag_weight"], d["ag_bias"], d["input_scale"], d["weight_scale"],
+                               is_fp8, False, 0, 1)
     # GEMM-RS: test/python/gemm_rs/test_gemm_rs.py `perf_torch`
     ns_rs = dict(base)
     exec(_extract(Path(ref_root), "test/python/gemm_rs/test_gemm_rs.py", ["PerfResult", "perf_torch"]), ns_rs)
-    r_rs = ns_rs["perf_torch"](d["rs_input"], d["rs_weight"], d["rs_bias"], 0, 1)
+    # (its fp8 branch calls the compiled GemmOnly op, so fp8 cases stop at the AG-GEMM)
+    r_rs = None if is_fp8 else ns_rs["perf_torch"](d["rs_input"], d["rs_weight"], d["rs_bias"], 0, 1)
     # only the outputs are stored; the test regenerates the seeded inputs with `dense_inputs`
     mine = {"ag_out": r_ag.output.clone(), "ag_gathered_sum": r_ag.gathered_output.double().sum().item(),
-            "rs_out": r_rs.output.clone()}
+            "rs_out": None if r_rs is None else r_rs.output.clone()}
     gathered = [None] * world
     dist.all_gather_object(gathered, mine)
     if rank == 0:
@@ -255,7 +264,8 @@ def _dense_worker(rank, world, port, ref_root, case, out_path):
 def gen_dense(ref_root):
     outs = []
     cases = [(256, 512, 512, torch.float32, False),   # the reference's CPU-runnable smoke shape
-             (64, 96, 128, torch.bfloat16, True), (48, 64, 64, torch.float16, True)]
+             (64, 96, 128, torch.bfloat16, True), (48, 64, 64, torch.float16, True),
+             (64, 96, 128, torch.float8_e4m3fn, False)]
     for i, case in enumerate(cases):
         with socket.socket() as s:
             s.bind(("127.0.0.1", 0))

@@ -176,21 +176,27 @@ def test_dense_matches_reference_vectors():
     mg = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mg)
     cases = _load("dense.pt")
-    assert len(cases) == 3
+    assert len(cases) == 4
     for c in cases:
         case, ranks = c["case"], c["ranks"]
         world = len(ranks)
         dtype = case[3]
         ins = [mg.dense_inputs(case, r, world) for r in range(world)]
+        fp8 = golden.is_fp8(dtype)
         tol = dict(rtol=1e-4, atol=1e-5) if dtype == torch.float32 else \
-            dict(rtol=1.6e-2, atol=1e-2) if dtype == torch.bfloat16 else dict(rtol=2e-3, atol=2e-3)
-        rs_outs = golden.gemm_rs_single([i["rs_input"] for i in ins], [i["rs_weight"] for i in ins],
-                                        biases=[i["rs_bias"] for i in ins] if case[4] else None)
+            dict(rtol=2e-3, atol=2e-3) if dtype == torch.float16 else dict(rtol=1.6e-2, atol=1e-2)
+        rs_outs = None if fp8 else golden.gemm_rs_single(
+            [i["rs_input"] for i in ins], [i["rs_weight"] for i in ins],
+            biases=[i["rs_bias"] for i in ins] if case[4] else None)
         for r in range(world):
-            out, gathered = golden.ag_gemm_single([i["ag_input"] for i in ins], ins[r]["ag_weight"],
-                                                  bias=ins[r]["ag_bias"])
+            out, gathered = golden.ag_gemm_single(
+                [i["ag_input"] for i in ins], ins[r]["ag_weight"], bias=ins[r]["ag_bias"],
+                input_scales=[i["input_scale"] for i in ins] if fp8 else None, weight_scale=ins[r]["weight_scale"])
             assert out.dtype == ranks[r]["ag_out"].dtype and out.shape == ranks[r]["ag_out"].shape
             torch.testing.assert_close(out.float(), ranks[r]["ag_out"].float(), **tol)
             assert abs(gathered.double().sum().item() - ranks[r]["ag_gathered_sum"]) <= 1e-6 * gathered.numel()
+            if fp8:
+                assert out.dtype == torch.bfloat16 and ranks[r]["rs_out"] is None
+                continue
             assert rs_outs[r].dtype == ranks[r]["rs_out"].dtype and rs_outs[r].shape == ranks[r]["rs_out"].shape
             torch.testing.assert_close(rs_outs[r].float(), ranks[r]["rs_out"].float(), **tol)
