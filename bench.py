@@ -241,26 +241,87 @@ def run_ours(args):
     agree = float((uo.float() - out.float()).abs().max() / uo.float().abs().max().clamp_min(1e-30))
     clocks = sampler.stop(t_begin, t_end) if sampler else None
 
-    # ---- end to end through host buffers: H2D of this rank's activations, both ops, D2H of the result
+    # ---- end to end through host buffers: H2D of this rank's activations, both ops, D2H of the result.
+    # Every step copies its own input from pinned host memory and its own result back; the copies run on two
+    # copy streams with double-buffered device inputs / host outputs, so that step i's copies overlap the
+    # kernels of steps i-1 / i+1 (what a serving loop does). If the pipelined form cannot be set up the plain
+    # one-stream form is timed instead; `e2e.mode` says which.
     a_host = a.cpu().pin_memory()
-    out_host = torch.empty((M // world, N1), dtype=torch.bfloat16).pin_memory()
-    a_dev = torch.empty_like(a)
 
-    def e2e_step():
-        a_dev.copy_(a_host, non_blocking=True)
-        ag.forward(a_dev, b0, output=c0)
-        o = rs.forward(c0, b1)
-        out_host.copy_(o, non_blocking=True)
+    def e2e_serial():
+        out_host = torch.empty((M // world, N1), dtype=torch.bfloat16).pin_memory()
+        a_dev = torch.empty_like(a)
 
-    for _ in range(3):
-        e2e_step()
-    barrier()
-    s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for _ in range(args.steps):
-        e2e_step()
-    s1.record()
-    barrier()
+        def step(i):
+            a_dev.copy_(a_host, non_blocking=True)
+            ag.forward(a_dev, b0, output=c0)
+            o = rs.forward(c0, b1)
+            out_host.copy_(o, non_blocking=True)
+
+        return step, (lambda: None), (lambda: None)
+
+    def e2e_pipelined():
+        main = torch.cuda.current_stream()
+        s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+        a_dev = [torch.empty_like(a) for _ in range(2)]
+        out_host = [torch.empty((M // world, N1), dtype=torch.bfloat16).pin_memory() for _ in range(2)]
+        in_ready = [torch.cuda.Event() for _ in range(2)]
+        in_free = [torch.cuda.Event() for _ in range(2)]
+        out_done = [torch.cuda.Event() for _ in range(2)]
+
+        def step(i):
+            j = i & 1
+            with torch.cuda.stream(s_in):
+                s_in.wait_event(in_free[j])  # the all-gather GEMM that read this buffer two steps ago is done
+                a_dev[j].copy_(a_host, non_blocking=True)
+                in_ready[j].record(s_in)
+            main.wait_event(in_ready[j])
+            ag.forward(a_dev[j], b0, output=c0)
+            in_free[j].record(main)
+            o = rs.forward(c0, b1)
+            done = torch.cuda.Event()
+            done.record(main)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                s_out.wait_event(out_done[j])  # the previous copy into this host buffer
+                out_host[j].copy_(o, non_blocking=True)
+                out_done[j].record(s_out)
+            o.record_stream(s_out)
+
+        def begin():  # copies of the timed region start after its first event
+            s_in.wait_stream(main)
+            s_out.wait_stream(main)
+
+        def end():  # ... and its last event waits for the last copies
+            main.wait_stream(s_in)
+            main.wait_stream(s_out)
+
+        for ev in in_free + out_done:
+            ev.record(main)
+        return step, begin, end
+
+    def time_e2e(make):
+        step, begin, end = make()
+        for i in range(4):
+            step(i)
+        end()
+        barrier()
+        s0, s1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s0.record()
+        begin()
+        for i in range(args.steps):
+            step(i)
+        end()
+        s1.record()
+        barrier()
+        return s0, s1
+
+    e2e_mode = "pipelined (copy streams, double-buffered)"
+    try:
+        s0, s1 = time_e2e(e2e_pipelined)
+    except (RuntimeError, AttributeError, TypeError) as exc:  # harness fallback, never a compute fallback
+        e2e_mode = f"serial (pipelined set-up failed: {type(exc).__name__})"
+        s0, s1 = time_e2e(e2e_serial)
     e2e_ms = _max_over_ranks(s0.elapsed_time(s1) / args.steps, world)
     comm.check_status()
 
@@ -298,7 +359,7 @@ def run_ours(args):
                         "ms_after_fused_region": unfused_after, "tflops_per_gpu": flops_gpu / (unfused_ms * 1e-3) / 1e12,
                         "max_rel_diff_vs_fused": agree},
             "speedup_vs_unfused": unfused_ms / ms_per_step,
-            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms,
+            "e2e": {"value": total_flops / (e2e_ms * 1e-3) / 1e12, "unit": "TFLOP/s", "ms_per_step": e2e_ms, "mode": e2e_mode,
                     "h2d_bytes_per_step": a.numel() * 2 * world, "d2h_bytes_per_step": out_host.numel() * 2 * world},
             "gpu_launches": args.steps * 2,
             "roofline": {"bound": "tensor", "achieved": ag_tflops, "peak": sustained, "unit": "TFLOP/s",
