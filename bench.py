@@ -541,7 +541,7 @@ def cpu_baseline(budget_s=15.0):
     while 2.0 * m_s * n_s * k_s * 2 / rate > budget_s and n_s > 384:
         n_s //= 2
     dt1, fl = _cpu_sample_run(m_s, n_s, k_s)
-    iters = max(1, min(200, int(budget_s / max(dt1, 1e-3))))
+    iters = max(1, min(2000, int(budget_s / max(dt1, 1e-3))))
     dt, fl = _cpu_sample_run(m_s, n_s, k_s, iters=iters)
     return {"value": fl / dt / 1e12, "unit": "TFLOP/s", "cores": cores, "kind": "port",
             "sample": f"oracle AG-GEMM + GEMM-RS on a slice M={m_s} N={n_s} K={k_s} (bf16, torch CPU), "
