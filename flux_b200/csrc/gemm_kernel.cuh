@@ -168,12 +168,35 @@ struct TileCoord {
   int expert;
 };
 
-__device__ __forceinline__ int imin(int a, int b) { return a < b ? a : b; }
-__device__ __forceinline__ int imax(int a, int b) { return a > b ? a : b; }
+__host__ __device__ __forceinline__ int imin(int a, int b) { return a < b ? a : b; }
+__host__ __device__ __forceinline__ int imax(int a, int b) { return a > b ? a : b; }
 
-// TILE_M = 128 (one CTA) or 256 (CTA pair, `half` = rank of this CTA inside the pair)
+// Rasterisation bands for the segmented ops, in units of segments (= shards / owners) of `tps` M tiles.
+// Bands are at most 8 M tiles tall (taller bands re-stream B less often and draw less power).
+// first_single: the first band is exactly one segment (all-gather: this rank's own shard, available at
+// once) and the following bands double in size, so that early tiles only need early arrivals.
+// last_single: the last band is exactly one segment (reduce-scatter: this rank's own rows, finished last).
+inline void make_bands(GemmParams& p, int nseg, int tps, bool first_single, bool last_single) {
+  int max_seg = tps > 0 ? 8 / tps : 1;
+  if (max_seg < 1) max_seg = 1;
+  int done = 0, nb = 0, next = 1;
+  const int body_end = last_single ? nseg - 1 : nseg;
+  while (done < body_end && nb < 7) {
+    int take = first_single ? next : max_seg;
+    if (take > max_seg) take = max_seg;
+    if (take > body_end - done) take = body_end - done;
+    done += take;
+    p.band_end[nb++] = done * tps;
+    next *= 2;
+  }
+  if (done < nseg) p.band_end[nb++] = nseg * tps;
+  p.n_bands = nb;
+}
+
+// TILE_M = 128 (one CTA) or 256 (CTA pair, `half` = rank of this CTA inside the pair).
+// Also compiled for the host: the CPU tests walk the schedule to check that every tile is visited once.
 template <int BN, int TILE_M>
-__device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_tiles, int n_tiles,
+__host__ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t, int m_tiles, int n_tiles,
                                             int tps, int half, TileCoord& tc) {
   // Rasterisation: M tiles are grouped into bands; inside a band consecutive work items walk down the
   // band's M tiles first, then move to the next column block (A band stays in L2, B streams once per band).

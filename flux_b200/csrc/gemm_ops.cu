@@ -168,28 +168,6 @@ static int check_gemm_shapes(const char* who, int m, int n, int k, int in_dtype,
 
 static void zero_params(GemmParams& p) { memset(&p, 0, sizeof(p)); }
 
-// Rasterisation bands for the segmented ops, in units of segments (= shards / owners) of `tps` M tiles.
-// Bands are at most 8 M tiles tall (taller bands re-stream B less often and draw less power).
-// first_single: the first band is exactly one segment (all-gather: this rank's own shard, available at
-// once) and the following bands double in size, so that early tiles only need early arrivals.
-// last_single: the last band is exactly one segment (reduce-scatter: this rank's own rows, finished last).
-static void make_bands(GemmParams& p, int nseg, int tps, bool first_single, bool last_single) {
-  int max_seg = tps > 0 ? 8 / tps : 1;
-  if (max_seg < 1) max_seg = 1;
-  int done = 0, nb = 0, next = 1;
-  const int body_end = last_single ? nseg - 1 : nseg;
-  while (done < body_end && nb < 7) {
-    int take = first_single ? next : max_seg;
-    if (take > max_seg) take = max_seg;
-    if (take > body_end - done) take = body_end - done;
-    done += take;
-    p.band_end[nb++] = done * tps;
-    next *= 2;
-  }
-  if (done < nseg) p.band_end[nb++] = nseg * tps;
-  p.n_bands = nb;
-}
-
 // B operand: [n, k] (k contiguous) as one box of `box_rows` rows, or, with the FLUXB_WEIGHT_KN flag,
 // [k, n] (n contiguous) as 64-column boxes feeding an MN-major UMMA operand.
 static int encode_b(GemmParams& p, const void* b, int in_dtype, int n, int k, int box_rows, int flags) {

@@ -1,0 +1,113 @@
+"""Invariants of the kernel's tile schedule, checked on the host.
+
+`tests/csrc/schedule_probe.cu` compiles the product's own `decode_tile` / `make_bands`
+(flux_b200/csrc/gemm_kernel.cuh) for the host with nvcc and walks every work item of a segmented launch.
+As the reference does for its MoE problem schedule (src/moe_ag_scatter/test/test_sort_utils.cc:20-46,210-227:
+fixed cases plus random ones, every tile covered exactly once), the tests check that each (segment, 128-row
+chunk, column tile) is visited exactly once for every tile width, both tile shapes, ragged segments, uniform
+and variable bands, and that the bands keep the visiting order the protocols rely on: all-gather starts with
+this rank's own shard and walks the segments in arrival order, reduce-scatter ends with this rank's own rows.
+"""
+import ctypes as C
+import os
+import random
+import shutil
+import subprocess
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(HERE)
+KBM = 128
+
+
+@pytest.fixture(scope="module")
+def probe():
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not os.path.exists(nvcc):
+        pytest.skip("nvcc is needed to compile the host-side schedule probe")
+    out_dir = os.path.join(HERE, "_build")
+    os.makedirs(out_dir, exist_ok=True)
+    so = os.path.join(out_dir, "libschedule_probe.so")
+    src = os.path.join(HERE, "csrc", "schedule_probe.cu")
+    deps = [src, os.path.join(ROOT, "flux_b200", "csrc", "gemm_kernel.cuh"), os.path.join(ROOT, "flux_b200", "csrc", "ptx.cuh")]
+    if not os.path.exists(so) or any(os.path.getmtime(d) > os.path.getmtime(so) for d in deps):
+        subprocess.run([nvcc, "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler",
+                        "-fPIC", "-I" + os.path.join(ROOT, "include"), "-o", so, src], check=True)
+    lib = C.CDLL(so)
+    lib.probe_dense_schedule.restype = C.c_int
+    lib.probe_dense_schedule.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int)] * 3 + [C.c_int]
+    return lib
+
+
+def walk(lib, nseg, seg_rows, n, block_n, cta_group, seg_first, group_m, bands):
+    chunks = (seg_rows + KBM - 1) // KBM
+    n_tiles = (n + block_n - 1) // block_n
+    tile_m = 256 if cta_group == 2 else 128
+    total = nseg * ((seg_rows + tile_m - 1) // tile_m) * n_tiles
+    visits = (C.c_int * (nseg * chunks * n_tiles))()
+    item_seg = (C.c_int * total)()
+    item_m = (C.c_int * total)()
+    rc = lib.probe_dense_schedule(nseg, seg_rows, n, block_n, cta_group, seg_first, group_m, bands, visits, item_seg,
+                                  item_m, total)
+    assert rc == total, f"probe returned {rc} for {(nseg, seg_rows, n, block_n, cta_group, seg_first, group_m, bands)}"
+    assert all(v == 1 for v in visits), "a tile is visited twice or never"
+    return list(item_seg)
+
+
+def check_order(segs, nseg, seg_first, bands):
+    """Segments appear band by band; the order of first appearance is seg_first, seg_first+1, ... (mod nseg)."""
+    first_seen = []
+    for s in segs:
+        if s not in first_seen:
+            first_seen.append(s)
+    assert first_seen == [(seg_first + i) % nseg for i in range(nseg)]
+    if nseg == 1:
+        return
+    if bands == 1:  # all-gather: the own shard (= seg_first) is a band of its own at the start
+        k = next(i for i, s in enumerate(segs) if s != seg_first)
+        assert all(s != seg_first for s in segs[k:])
+    if bands == 2:  # reduce-scatter: the own rows (= the last segment of the rotation) are a band of their own at the end
+        own = (seg_first + nseg - 1) % nseg
+        k = next(i for i, s in enumerate(segs) if s == own)
+        assert all(s == own for s in segs[k:])
+
+
+FIXED = [
+    # nseg, seg_rows, n, block_n, cta_group
+    (8, 512, 6144, 256, 2),    # D0 per-rank shape at TP=8
+    (8, 512, 12288, 256, 2),   # D1 at TP=8
+    (4, 1024, 12288, 256, 2),  # TP=4
+    (2, 2048, 24576, 256, 2),  # TP=2
+    (1, 4096, 49152, 256, 2),  # TP=1
+    (8, 200, 520, 64, 1),      # ragged rows and columns
+    (8, 1, 8, 64, 1),          # one row per rank
+    (3, 300, 1000, 192, 2),    # pair tiles with a ragged second half
+]
+
+
+@pytest.mark.parametrize("case", FIXED)
+@pytest.mark.parametrize("bands", [0, 1, 2])
+def test_fixed_cases(probe, case, bands):
+    nseg, seg_rows, n, bn, cg = case
+    for seg_first in {0, nseg - 1, nseg // 2}:
+        for gm in ([1, 3, 8, 16] if bands == 0 else [0]):
+            segs = walk(probe, nseg, seg_rows, n, bn, cg, seg_first, gm, bands)
+            if bands:
+                check_order(segs, nseg, seg_first, bands)
+
+
+def test_random_cases(probe):
+    rng = random.Random(1234)
+    for _ in range(3000):
+        nseg = rng.choice([1, 2, 3, 4, 8])
+        seg_rows = rng.choice([rng.randint(1, 2200), 128 * rng.randint(1, 16)])
+        n = 8 * rng.randint(1, 400)
+        bn = rng.choice([64, 128, 192, 256])
+        cg = rng.choice([1, 2])
+        bands = rng.choice([0, 1, 2])
+        gm = rng.randint(1, 20) if bands == 0 else 0
+        seg_first = rng.randrange(nseg)
+        segs = walk(probe, nseg, seg_rows, n, bn, cg, seg_first, gm, bands)
+        if bands:
+            check_order(segs, nseg, seg_first, bands)
