@@ -319,7 +319,7 @@ def run_ours(args):
     e2e_mode = "pipelined (copy streams, double-buffered)"
     try:
         s0, s1 = time_e2e(e2e_pipelined)
-    except (RuntimeError, AttributeError, TypeError) as exc:  # harness fallback, never a compute fallback
+    except Exception as exc:  # fallback of the timing harness only: both forms run the same kernels
         e2e_mode = f"serial (pipelined set-up failed: {type(exc).__name__})"
         s0, s1 = time_e2e(e2e_serial)
     e2e_ms = _max_over_ranks(s0.elapsed_time(s1) / args.steps, world)
