@@ -11,13 +11,16 @@
 //     Replaces the reference's copy-engine all-gather + per-rank flags
 //     (src/coll/ths_op/all_gather_op.cc:529-574) and the flag waits inside its
 //     sm90 kernel (src/ag_gemm/sm90_all_gather_gemm_tma_warpspecialized_cooperative.hpp:512-586).
-//   * reduce-scatter epilogue - the epilogue warps store fp32 partial tiles
-//     straight into the staging slot of the rank that owns those rows and bump
-//     that rank's per-tile counter; rows owned by peers are computed first.
+//   * reduce-scatter epilogue - the epilogue warps store partial tiles (in the
+//     16-bit output format, or fp32 on request) straight into the staging slot
+//     of the rank that owns those rows and bump that rank's per-tile counter;
+//     rows owned by peers are computed first, the owner's comm warps sum the
+//     peers' partials in fp32 and its own tiles add that sum in their epilogue.
 //     Replaces the reference's store-then-pull design
 //     (src/gemm_rs/sm90_epilogue_evt.hpp:231-242, sm90_reduce_scatter_utils.hpp:212-262).
-//   * grouped (MoE) mode - M tiles come from a device-side table, A rows are
-//     fetched by index with TMA gather4, B is the expert's weight slab.
+//   * grouped (MoE) mode - M tiles come from a device-side table, A rows come
+//     from an expert-sorted buffer the comm warps fill as tokens arrive (or are
+//     fetched by index with TMA gather4), B is the expert's weight slab.
 //
 // Warp roles (320 threads): warp 0 TMA producer, warp 1 UMMA issuer + TMEM
 // owner, warps 2-5 epilogue (one TMEM lane quadrant each), warps 6-9 comm.
@@ -47,7 +50,7 @@ constexpr int kAgSubRows = 32;         // rows of one all-gather push unit; kBM 
 
 enum EpiMode : int {
   kEpiStore = 0,    // write D (out dtype) to p.out
-  kEpiRsPush = 1,   // write fp32 partials into the owner's staging slot + counter
+  kEpiRsPush = 1,   // write partials (16-bit or fp32) into the owner's staging slot + counter
 };
 enum OutType : int { kOutBf16 = 0, kOutF16 = 1, kOutF32 = 2 };
 enum BiasMode : int { kBiasNone = 0, kBiasFull = 1, kBiasRow = 2 };
@@ -97,13 +100,13 @@ struct GemmParams {
   long long ag_row_bytes;
   int rank, world;
   // reduce-scatter push
-  CUtensorMap tmap_rs[kMaxWorld];  // fp32 [rows_per_owner, N] view of this rank's slot at owner o, 32x32 boxes
+  CUtensorMap tmap_rs[kMaxWorld];  // [rows_per_owner, N] view of this rank's slot at owner o: 16-bit 32x64 boxes, or fp32 32x32
   float* rs_stage[kMaxWorld];  // rs_stage[o] = slot of this rank inside owner o's staging
   int* rs_cnt[kMaxWorld];      // per-tile counters at owner o: [tiles_per_seg][n_tiles]
   // reduce-scatter: owner side. The comm warps sum the partial tiles the peers pushed for this
   // rank's rows into this rank's own (otherwise unused) slot and raise a per-tile ready flag; the
   // epilogue of this rank's own tiles adds that sum to its accumulator and writes the result.
-  const float* rs_local_stage;  // [world][seg_rows][N] fp32 partials received by this rank
+  const float* rs_local_stage;  // [world] slots of seg_rows x N floats: partials received by this rank (16-bit ones fill half a slot)
   int* rs_local_cnt;            // this rank's arrival counters, [tiles]
   int* rs_local_ready;          // this rank's "remote partials summed" flags, [tiles]
   void* rs_out;                 // [seg_rows, N] result, type rs_out_type
@@ -144,7 +147,7 @@ struct SmemLayout {
   static constexpr int kBRows = CTA2 ? BN / 2 : BN;
   static constexpr int kBBytes = kBRows * kRowBytes;
   static constexpr int kStageBytes = kABytes + kBBytes;
-  // epilogue staging: per epilogue warp 32 x 32 fp32 blocks, 128-byte rows, 128-byte swizzle; two
+  // epilogue staging: per epilogue warp 4 KB blocks (32 x 32 fp32 or 32 x 64 16-bit), 128-byte rows, 128-byte swizzle; two
   // blocks per warp where shared memory allows, so that two pushes per warp can be in flight
   static constexpr int kEpiPitch = 128;
   static constexpr int kEpiBlockBytes = 32 * kEpiPitch;
