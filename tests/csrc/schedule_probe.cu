@@ -5,6 +5,7 @@
 #include <cstring>
 
 #include "../../flux_b200/csrc/gemm_kernel.cuh"
+#include "../../flux_b200/csrc/internal.h"
 
 using namespace fluxb;
 
@@ -65,4 +66,22 @@ extern "C" int probe_dense_schedule(int nseg, int seg_rows, int n, int block_n, 
   WALK(64) WALK(128) WALK(192) WALK(256)
 #undef WALK
   return -1;
+}
+
+// Tile shape the library would choose for a segmented launch (resolve_cta_group / resolve_block_n of
+// flux_b200/csrc/gemm_ops.cu, linked from libfluxb.so). tun_* = 0 leaves the choice to the library.
+extern "C" void probe_resolve(int nseg, int seg_rows, int n, int sm_count, int b_mn_major, int tun_bn, int tun_cg,
+                              int tun_ctas, int* bn, int* cg) {
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  p.nseg = nseg;
+  p.seg_rows = seg_rows;
+  p.N = n;
+  p.b_mn_major = b_mn_major;
+  fluxb_comm comm;
+  comm.sm_count = sm_count;
+  fluxb_tuning t{tun_bn, 0, tun_ctas, tun_cg};
+  const fluxb_tuning* tp = (tun_bn || tun_cg || tun_ctas) ? &t : nullptr;
+  *cg = resolve_cta_group(p, tp);
+  *bn = resolve_block_n(&comm, p, tp, 0);
 }

@@ -30,13 +30,20 @@ def probe():
     os.makedirs(out_dir, exist_ok=True)
     so = os.path.join(out_dir, "libschedule_probe.so")
     src = os.path.join(HERE, "csrc", "schedule_probe.cu")
-    deps = [src, os.path.join(ROOT, "flux_b200", "csrc", "gemm_kernel.cuh"), os.path.join(ROOT, "flux_b200", "csrc", "ptx.cuh")]
+    libdir = os.path.join(ROOT, "flux_b200")
+    if not os.path.exists(os.path.join(libdir, "libfluxb.so")):
+        pytest.skip("libfluxb.so has not been built")
+    deps = [src, os.path.join(libdir, "libfluxb.so")] + [os.path.join(libdir, "csrc", f) for f in
+                                                          ("gemm_kernel.cuh", "ptx.cuh", "internal.h")]
     if not os.path.exists(so) or any(os.path.getmtime(d) > os.path.getmtime(so) for d in deps):
         subprocess.run([nvcc, "-std=c++17", "-O1", "-gencode", "arch=compute_100a,code=sm_100a", "-shared", "-Xcompiler",
-                        "-fPIC", "-I" + os.path.join(ROOT, "include"), "-o", so, src], check=True)
+                        "-fPIC", "-I" + os.path.join(ROOT, "include"), "-o", so, src, "-L" + libdir, "-lfluxb",
+                        "-Xlinker", "-rpath=" + libdir], check=True)
     lib = C.CDLL(so)
     lib.probe_dense_schedule.restype = C.c_int
     lib.probe_dense_schedule.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int)] * 3 + [C.c_int]
+    lib.probe_resolve.restype = None
+    lib.probe_resolve.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int)] * 2
     return lib
 
 
@@ -111,3 +118,32 @@ def test_random_cases(probe):
         segs = walk(probe, nseg, seg_rows, n, bn, cg, seg_first, gm, bands)
         if bands:
             check_order(segs, nseg, seg_first, bands)
+
+
+def resolve(lib, nseg, seg_rows, n, sms=148, kn=0, bn=0, cg=0, ctas=0):
+    out_bn, out_cg = C.c_int(), C.c_int()
+    lib.probe_resolve(nseg, seg_rows, n, sms, kn, bn, cg, ctas, C.byref(out_bn), C.byref(out_cg))
+    return out_bn.value, out_cg.value
+
+
+def test_tile_shape_choice(probe):
+    """The library's own choice of tile shape for the benchmark shapes (the measured fast configuration is a
+    CTA pair on 256 x 256 tiles) and the rules around it."""
+    for nseg, seg_rows, n in [(8, 512, 6144), (8, 512, 12288), (4, 1024, 12288), (2, 2048, 24576), (1, 4096, 49152),
+                              (1, 4096, 12288)]:
+        assert resolve(probe, nseg, seg_rows, n) == (256, 2)
+    # segments shorter than a pair tile: one CTA per tile
+    assert resolve(probe, 8, 200, 4096)[1] == 1
+    # narrow outputs never get a tile more than twice their width
+    assert resolve(probe, 1, 128, 64)[0] == 64 and resolve(probe, 1, 128, 8)[0] == 64
+    # a [K,N] weight needs whole 64-column boxes per CTA: 128 or 256 for a pair, never 192 (96 per CTA) or 64 (32)
+    rng = random.Random(7)
+    for _ in range(500):
+        nseg, seg_rows, n = rng.choice([1, 2, 8]), rng.randint(1, 3000), 8 * rng.randint(8, 3000)
+        bn, cg = resolve(probe, nseg, seg_rows, n, kn=1)
+        assert bn in (64, 128, 192, 256) and (bn // cg) % 64 == 0
+        bn, cg = resolve(probe, nseg, seg_rows, n)
+        assert bn in (64, 128, 192, 256) and cg == (2 if seg_rows >= 256 else 1)
+    # the caller's tuning wins
+    assert resolve(probe, 8, 512, 6144, bn=128, cg=1) == (128, 1)
+    assert resolve(probe, 8, 512, 6144, cg=1)[1] == 1
