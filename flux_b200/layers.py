@@ -108,7 +108,11 @@ class ColumnParallelLinear(torch.nn.Module):
         return self._bwd_op
 
     def forward(self, x_shard: torch.Tensor) -> torch.Tensor:
-        return _ColumnParallelFn.apply(x_shard, self.weight, self.bias, self)
+        """`x_shard` is [tokens/TP, in_features] or sequence-first [s/TP, b, in_features] (the gather runs
+        along the first axis, so the output is [s, b, out_features/TP])."""
+        lead = x_shard.shape[:-1]
+        y = _ColumnParallelFn.apply(x_shard.reshape(-1, x_shard.shape[-1]), self.weight, self.bias, self)
+        return y if len(lead) == 1 else y.view(lead[0] * self.world, *lead[1:], y.shape[-1])
 
 
 class _RowParallelFn(torch.autograd.Function):
@@ -176,7 +180,14 @@ class RowParallelLinear(torch.nn.Module):
         return self._bwd_op
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
-        y = _RowParallelFn.apply(x, self.weight, self)
+        """`x` is [tokens, in_features/TP] or sequence-first [s, b, in_features/TP] (rows are scattered along
+        the first axis: the output is [s/TP, b, out_features])."""
+        lead = x.shape[:-1]
+        y = _RowParallelFn.apply(x.reshape(-1, x.shape[-1]), self.weight, self)
+        if len(lead) > 1:
+            if lead[0] % self.world != 0:
+                raise RuntimeError(f"RowParallelLinear: sequence length {lead[0]} is not a multiple of TP={self.world}")
+            y = y.view(lead[0] // self.world, *lead[1:], y.shape[-1])
         return y if self.bias is None else y + self.bias
 
 

@@ -243,3 +243,30 @@ def test_moe_block_world1():
 
 def test_moe_block_gated_world2():
     run_distributed(_moe_case, 2, True, use_cuda=False)
+
+
+def _seq_first_case(rank, world):
+    """Sequence-first [s, b, h] activations go through the same layers: flattening keeps the gather / scatter on
+    the sequence axis."""
+    from flux_b200 import layers
+
+    _patch(layers)
+    group = dist.group.WORLD
+    hidden, ffn, seq, batch = 16, 32, 4 * world, 3
+    torch.manual_seed(31 + rank)
+    mlp = layers.TensorParallelMLP(hidden, ffn, seq * batch, group, dtype=torch.float32, device="cpu")
+    x_shard = torch.randn(seq // world, batch, hidden)
+    y_shard = mlp(x_shard)
+    assert y_shard.shape == (seq // world, batch, hidden)
+    h = mlp.fc1(x_shard)
+    assert h.shape == (seq, batch, ffn // world)
+    w1 = torch.cat(_gather_rows(mlp.fc1.weight.detach(), group, world), dim=0)
+    w2 = torch.cat(_gather_rows(mlp.fc2.weight.detach(), group, world), dim=1)
+    x = torch.cat(_gather_rows(x_shard, group, world), dim=0)  # [s, b, h]
+    y = torch.nn.functional.gelu(x @ w1.t()) @ w2.t()
+    sl = seq // world
+    torch.testing.assert_close(y_shard.detach(), y[rank * sl:(rank + 1) * sl], rtol=1e-4, atol=1e-5)
+
+
+def test_sequence_first_activations_world2():
+    run_distributed(_seq_first_case, 2, use_cuda=False)
