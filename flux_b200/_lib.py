@@ -73,23 +73,28 @@ SIGNATURES = {
     "fluxb_symm_close": (_i, [_vp]),
     "fluxb_enable_peer_access": (_i, [_i, _i]),
     "fluxb_barrier_all": (_i, [_vp, _pp, _vp]),
+    "fluxb_comm_set_ranks_on_gpu": (_i, [_vp, _i]),
+    "fluxb_run_ranks": (_i, [_pp, _i, _vp]),
     "fluxb_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp, _i, _vp, _vp, _f, _i, _tun, _vp]),
     "fluxb_ag_gemm_gather_bytes": (_sz, [_i, _i, _i]),
     "fluxb_ag_gemm_flag_bytes": (_sz, [_i, _i]),
     "fluxb_ag_gemm_scale_bytes": (_sz, [_i]),
     "fluxb_ag_gemm_create": (_i, [_vp, _i, _i, _i, _i, _i, _pp, _pp, _pp, _pp]),
     "fluxb_ag_gemm_destroy": (_i, [_vp]),
+    "fluxb_ag_gemm_reset": (_i, [_vp, _vp]),
     "fluxb_ag_gemm_forward": (_i, [_vp, _vp, _i, _vp, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _i, _vp, _tun, _vp]),
     "fluxb_gemm_rs_stage_bytes": (_sz, [_i, _i, _i]),
     "fluxb_gemm_rs_cnt_bytes": (_sz, [_i, _i, _i]),
     "fluxb_gemm_rs_create": (_i, [_vp, _i, _i, _i, _i, _pp, _pp, _pp]),
     "fluxb_gemm_rs_destroy": (_i, [_vp]),
+    "fluxb_gemm_rs_reset": (_i, [_vp, _vp]),
     "fluxb_gemm_rs_forward": (_i, [_vp, _vp, _vp, _i, _i, _i, _vp, _vp, _i, _vp, _vp, _f, _i, _tun, _vp]),
     "fluxb_moe_scatter_index": (_i, [_vp, _i, _i, _i, _vp, _vp, _vp]),
     "fluxb_moe_gather_index": (_i, [_vp, _i, _i, _vp, _vp, _vp]),
     "fluxb_moe_ag_scatter_workspace_bytes": (_sz, [_i, _i, _i, _i, _i]),
     "fluxb_moe_ag_scatter_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _pp, _pp, _vp, _pp]),
     "fluxb_moe_ag_scatter_destroy": (_i, [_vp]),
+    "fluxb_moe_ag_scatter_reset": (_i, [_vp, _vp]),
     "fluxb_moe_ag_scatter_forward": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _tun, _vp]),
     "fluxb_moe_scatter_gemm_static": (_i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _tun, _vp]),
     "fluxb_moe_gather_rs_workspace_bytes": (_sz, [_i, _i, _i, _i]),
@@ -97,6 +102,7 @@ SIGNATURES = {
     "fluxb_moe_gather_rs_cnt_bytes": (_sz, [_i, _i, _i]),
     "fluxb_moe_gather_rs_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _pp, _pp, _vp, _pp]),
     "fluxb_moe_gather_rs_destroy": (_i, [_vp]),
+    "fluxb_moe_gather_rs_reset": (_i, [_vp, _vp]),
     "fluxb_moe_gather_rs_forward": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _tun, _vp]),
 }
 

@@ -46,7 +46,10 @@ constexpr int kRowBytes = 128;    // bytes of K per smem row (one swizzle span)
 constexpr int kThreads = 320;
 constexpr int kMaxWorld = 8;
 constexpr int kCommSliceBytes = 2048;  // bytes of one row handled by one comm unit
-constexpr int kAgSubRows = 32;         // rows of one all-gather push unit; kBM / kAgSubRows units signal one chunk flag
+constexpr int kAgUnitRows = 8;         // rows of one all-gather push unit (one warp: 8 rows x 2 KB)
+constexpr int kAgUnitsPerSlice = kBM / kAgUnitRows;  // units that signal one (128-row chunk, 2 KB slice)
+constexpr int kCommRowsInFlight = 2;   // rows (x 2 KB) a comm warp holds in registers between its loads and stores
+constexpr int kAgMaxGroups = 64;       // arrival counters per (source rank, chunk): one per group of 2 KB slices
 
 enum EpiMode : int {
   kEpiStore = 0,    // write D (out dtype) to p.out
@@ -88,9 +91,14 @@ struct GemmParams {
   float alpha;
   const float* alpha_ptr;  // optional device scalar multiplied into alpha
   // all-gather: consumer side
-  const int* ag_flags;  // [nseg][ag_flag_stride], null = no waits
-  int ag_flag_stride;
-  int ag_expected;
+  // Arrival counters [source rank][128-row chunk][slice group]: a group is `ag_spf` consecutive 2 KB slices
+  // of the rows (1 unless a row has more than kAgMaxGroups slices); every push unit of 8 rows x 2 KB adds 1,
+  // so a complete group counts kAgUnitsPerSlice x (slices in the group). The GEMM waits group by group as
+  // it walks along K, so a tile starts as soon as the first 2 KB of its rows are in.
+  const int* ag_flags;  // null = no waits
+  int ag_flag_stride;   // counters per source rank (= chunks of the buffer x ag_groups)
+  int ag_groups;        // counters per chunk
+  int ag_spf;           // 2 KB slices per counter
   // all-gather: producer side (comm warps)
   const uint8_t* ag_src;          // this rank's shard, row-major, row_bytes per row
   uint8_t* ag_dst[kMaxWorld];     // gather buffer of every rank (own included)
@@ -152,10 +160,10 @@ struct SmemLayout {
   static constexpr int kEpiPitch = 128;
   static constexpr int kEpiBlockBytes = 32 * kEpiPitch;
   static constexpr int kEpiOffset = STAGES * kStageBytes;
-  static constexpr int kEpiBufs = (kEpiOffset + 8 * kEpiBlockBytes + (2 * STAGES + 4) * 8 + 64 + 1024 <= 232448) ? 2 : 1;
+  static constexpr int kNumBars = 2 * STAGES + 5;  // full/empty per stage, 2 x accumulator full/empty, 1 x "UMMAs retired" (abort path)
+  static constexpr int kEpiBufs = (kEpiOffset + 8 * kEpiBlockBytes + kNumBars * 8 + 64 + 1024 <= 232448) ? 2 : 1;
   static constexpr int kEpiWarpBytes = kEpiBufs * kEpiBlockBytes;
   static constexpr int kBarOffset = kEpiOffset + 4 * kEpiWarpBytes;
-  static constexpr int kNumBars = 2 * STAGES + 4;
   static constexpr int kMiscOffset = kBarOffset + kNumBars * 8;
   static constexpr int kTotal = kMiscOffset + 64 + 1024;  // + slack for 1024-byte alignment
 };
@@ -259,9 +267,11 @@ __device__ __forceinline__ uint32_t pack_f16(float a, float b) {
 
 // KIND: 0 = 16-bit inputs (bf16/f16 chosen by the instruction descriptor), 1 = fp8
 // CTA2: false = one CTA per 128-row tile, true = CTA pair per 256-row tile (launch with cluster 2x1x1)
+// `cta_id` / `num_ctas`: this CTA's index and the number of CTAs that work on problem `p` (the whole grid for
+// an ordinary launch; a slice of it when one launch runs several ranks' problems side by side).
 template <int BN, int STAGES, int KIND, bool CTA2>
-__global__ void __launch_bounds__(kThreads, 1)
-fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
+__device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint32_t idesc, const int cta_id,
+                                                const int num_ctas) {
   using L = SmemLayout<BN, STAGES, CTA2>;
   constexpr int ELT = (KIND == 0) ? 2 : 1;
   constexpr int BKE = kRowBytes / ELT;  // K elements per stage
@@ -285,6 +295,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   auto bar_empty = [&](int s) { return bar_base + 8u * (STAGES + s); };
   auto bar_tfull = [&](int a) { return bar_base + 8u * (2 * STAGES + a); };
   auto bar_tempty = [&](int a) { return bar_base + 8u * (2 * STAGES + 2 + a); };
+  const uint32_t bar_retired = bar_base + 8u * (2 * STAGES + 4);
   auto smem_a = [&](int s) { return smem_base + s * L::kStageBytes; };
   auto smem_b = [&](int s) { return smem_base + s * L::kStageBytes + L::kABytes; };
 
@@ -293,10 +304,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   const uint64_t budget = p.timeout_ns;
   const int half = CTA2 ? static_cast<int>(cluster_ctarank()) : 0;  // rank inside the CTA pair
   const bool leader = half == 0;
-  const int tile_first = CTA2 ? static_cast<int>(blockIdx.x >> 1) : static_cast<int>(blockIdx.x);
-  const int tile_step = CTA2 ? static_cast<int>(gridDim.x >> 1) : static_cast<int>(gridDim.x);
+  const int tile_first = CTA2 ? (cta_id >> 1) : cta_id;
+  const int tile_step = CTA2 ? (num_ctas >> 1) : num_ctas;
+  // raised by any role that gives up; in a CTA pair the partner's word is raised too
+  const AbortWord ab{s_abort, CTA2 ? mapa_u32(smem_u32(const_cast<int*>(s_abort)), static_cast<uint32_t>(half ^ 1)) : 0u};
 
-  unsigned long long* tr = p.trace != nullptr ? p.trace + static_cast<size_t>(blockIdx.x) * 8 : nullptr;
+  unsigned long long* tr = p.trace != nullptr ? p.trace + static_cast<size_t>(cta_id) * 8 : nullptr;
   if (threadIdx.x == 0) {
     if (tr != nullptr) {
       tr[0] = globaltimer_ns();
@@ -312,6 +325,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       mbar_init(bar_tfull(a), 1);
       mbar_init(bar_tempty(a), CTA2 ? 8 : 4);  // one arrival per epilogue warp (of both CTAs)
     }
+    mbar_init(bar_retired, 1);
     mbar_init_fence();
     tma_prefetch_desc(&p.tmap_a);
     tma_prefetch_desc(&p.tmap_b);
@@ -341,6 +355,9 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   }
   const int total_tiles = m_tiles * n_tiles;
   const int num_kb = (p.K + BKE - 1) / BKE;
+  // all-gather bookkeeping: a K block is 128 bytes of a row, a push slice 2 KB, a counter covers ag_spf slices
+  const int ag_nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+  const int kb_per_group = (kCommSliceBytes / kRowBytes) * (p.ag_spf > 0 ? p.ag_spf : 1);
 
   // Work schedule, identical in every role: worker w (a CTA, or a CTA pair) takes tiles w, w+P, ...
   // of the full waves; if the last wave is at most half full, each of its tiles is cut along K into
@@ -375,6 +392,18 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     return true;
   };
 
+  // Abort path of the producer: every stage it armed still has copies in flight or has been filled; wait
+  // (1 ms per stage at most) until each armed phase completes, so that no copy outlives the CTA's shared
+  // memory. Stages [0, stage) were last armed in phase `phase`, the others one round earlier. In a CTA pair
+  // the leader's barriers count both CTAs' bytes, and the final cluster barrier keeps the partner alive
+  // until the leader is through here.
+  auto drain_loads = [&](int stage, uint32_t phase) {
+    if (!leader) return;
+    const AbortWord none{nullptr, 0u};
+    for (int s2 = 0; s2 < STAGES; ++s2)
+      mbar_wait(bar_full(s2), s2 < stage ? phase : (phase ^ 1u), none, 0, 1000000ull);
+  };
+
   if (warp == 0 && p.g_gather != nullptr) {
     // ------------------------------------------------- TMA, row-gather form (MoE layer 0)
     // All 32 lanes work: lane l keeps the four source rows of rows 4l..4l+3 of the tile in registers
@@ -385,22 +414,6 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     for (int t = tile_first; ok && t < total_tiles; t += tile_step) {
       TileCoord tc;
       decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
-      if (p.ag_flags != nullptr) {
-        // wait for every chunk of every source rank the tile touches (lane 0 polls, all lanes follow)
-        int okw = 1;
-        if (lane == 0) {
-          const int chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
-          for (int r = 0; okw && r < p.world; ++r) {
-            if (!((tc.need_mask >> r) & 1)) continue;
-            for (int c = 0; okw && c < chunks; ++c)
-              okw = flag_wait_eq(p.ag_flags + r * p.ag_flag_stride + c, p.ag_expected, s_abort,
-                                 kStatusTimeoutFlag, budget) ? 1 : 0;
-          }
-        }
-        okw = __shfl_sync(0xffffffffu, okw, 0);
-        if (!okw) break;
-        fence_proxy_async();
-      }
       // rows past the tile end re-read a valid row (their results are never stored)
       const int* gi = p.g_gather + (tc.rows > 0 ? tc.row0 : 0);
       const int nr = tc.rows > 0 ? tc.rows : 1;
@@ -410,7 +423,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       const int i2 = gi[r0 + 2 < nr ? r0 + 2 : 0];
       const int i3 = gi[r0 + 3 < nr ? r0 + 3 : 0];
       for (int kb = 0; kb < num_kb; ++kb) {
-        if (!mbar_wait(bar_empty(stage), phase ^ 1u, s_abort, kStatusTimeoutSmemEmpty, budget, 40)) {
+        if (!mbar_wait(bar_empty(stage), phase ^ 1u, ab, kStatusTimeoutSmemEmpty, budget, 40)) {
           ok = false;
           break;
         }
@@ -434,6 +447,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       }
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0 && ok;
     }
+    if (lane == 0 && *s_abort != 0) drain_loads(stage, phase);
   } else if (warp == 0) {
     // ------------------------------------------------------------------ TMA
     if (lane == 0) {
@@ -444,30 +458,36 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       for (int wi = 0; ok && get_item(wi, t, kb0, kb1, part); ++wi) {
         TileCoord tc;
         decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
-        if (p.ag_flags != nullptr && p.g_tiles == nullptr) {
-          {
-            if (tc.rows > 0 && !(p.a_own_valid && tc.seg == p.rank)) {
-              const uint64_t w0 = tr != nullptr ? globaltimer_ns() : 0;
-              ok = flag_wait_eq(p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk, p.ag_expected,
-                                s_abort, kStatusTimeoutFlag, budget);
-              if (tr != nullptr) tr[5] += globaltimer_ns() - w0;
-            }
-          }
-          if (!ok) break;
-          fence_proxy_async();
-        }
+        // all-gather: the rows of this tile arrive slice group by slice group along K
+        const int* tile_flags = nullptr;
+        if (p.ag_flags != nullptr && p.g_tiles == nullptr && tc.rows > 0 && !(p.a_own_valid && tc.seg == p.rank))
+          tile_flags = p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk * p.ag_groups;
         if (p.g_perm_done != nullptr) {
           // grouped, permute form: every source rank the tile reads must be fully permuted
-          const int expected = ((p.g_rows_per_rank + kBM - 1) / kBM) *
+          const int expected = ((p.g_rows_per_rank + kBM - 1) / kBM) * kAgUnitsPerSlice *
                                static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
           for (int r = 0; ok && r < p.world; ++r)
             if ((tc.need_mask >> r) & 1)
-              ok = flag_wait_eq(p.g_perm_done + r, expected, s_abort, kStatusTimeoutFlag, budget);
+              ok = flag_wait_eq(p.g_perm_done + r, expected, ab, kStatusTimeoutFlag, budget);
           if (!ok) break;
           fence_proxy_async();
         }
+        // K block at which the next slice group of the rows begins (never, if there is nothing to wait for):
+        // one compare per K block on the producer's critical path, the arithmetic only when a group begins
+        int next_group_kb = tile_flags != nullptr ? kb0 : 0x7fffffff;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_empty(stage), phase ^ 1u, s_abort, kStatusTimeoutSmemEmpty, budget, 40)) {
+          if (kb == next_group_kb) {
+            // entering a new slice group of the rows: wait (bounded) until all of its push units are in
+            const int grp = kb / kb_per_group;
+            next_group_kb = (grp + 1) * kb_per_group;
+            const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
+            const uint64_t w0 = tr != nullptr ? globaltimer_ns() : 0;
+            ok = flag_wait_eq(tile_flags + grp, kAgUnitsPerSlice * in_group, ab, kStatusTimeoutFlag, budget);
+            if (tr != nullptr) tr[5] += globaltimer_ns() - w0;
+            if (!ok) break;
+            fence_proxy_async();
+          }
+          if (!mbar_wait(bar_empty(stage), phase ^ 1u, ab, kStatusTimeoutSmemEmpty, budget, 40)) {
             ok = false;
             break;
           }
@@ -523,6 +543,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
           }
         }
       }
+      if (*s_abort != 0) drain_loads(stage, phase);
     }
   } else if (warp == 1) {
     // ----------------------------------------------------------------- UMMA
@@ -535,12 +556,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       for (; ok && get_item(it, t, kb0, kb1, part); ++it) {
         const int acc = it & 1;
         const uint32_t acc_phase = (it >> 1) & 1;
-        if (!mbar_wait(bar_tempty(acc), acc_phase ^ 1u, s_abort, kStatusTimeoutTmemEmpty, budget))
+        if (!mbar_wait(bar_tempty(acc), acc_phase ^ 1u, ab, kStatusTimeoutTmemEmpty, budget))
           break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_full(stage), phase, s_abort, kStatusTimeoutSmemFull, budget)) {
+          if (!mbar_wait(bar_full(stage), phase, ab, kStatusTimeoutSmemFull, budget)) {
             ok = false;
             break;
           }
@@ -577,6 +598,12 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         tr[2] = globaltimer_ns();
         tr[7] = static_cast<unsigned long long>(it);
       }
+      if (*s_abort != 0) {
+        // abort path: the UMMAs issued so far still read shared memory and write tensor memory; let them
+        // retire (bounded) before the CTA tears both down
+        if (CTA2) umma_commit_2cta(bar_retired, 1); else umma_commit(bar_retired);
+        mbar_wait(bar_retired, 0, AbortWord{nullptr, 0u}, 0, 2000000ull);
+      }
     }
   } else if (warp < 6) {
     // ------------------------------------------------------------- epilogue
@@ -591,7 +618,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       const uint32_t acc_phase = (it >> 1) & 1;
       TileCoord tc;
       decode_tile<BN, TILE_M>(p, t, m_tiles, n_tiles, tps, half, tc);
-      if (!mbar_wait(bar_tfull(acc), acc_phase, s_abort, kStatusTimeoutTmemFull, budget, 300)) break;
+      if (!mbar_wait(bar_tfull(acc), acc_phase, ab, kStatusTimeoutTmemFull, budget, 300)) break;
       tc_fence_after();
       // split-K tail: where this warp's 32 rows of a tail tile's partial accumulators live
       const bool is_tail = split > 1 && it == full_waves;
@@ -628,7 +655,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         // finisher: every other part of this warp's rows must have been parked
         int okw = 1;
         if (lane == 0) {
-          okw = flag_wait_eq(sk_cnt, split - 1, s_abort, kStatusTimeoutTmemFull, budget) ? 1 : 0;
+          okw = flag_wait_eq(sk_cnt, split - 1, ab, kStatusTimeoutTmemFull, budget) ? 1 : 0;
           if (okw) *sk_cnt = 0;  // this warp is the only reader: clear for the next launch
         }
         okw = __shfl_sync(0xffffffffu, okw, 0);
@@ -656,7 +683,7 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
         int okw = 1;
         if (lane == 0) {
           const uint64_t w0 = (tr != nullptr && warp == 2) ? globaltimer_ns() : 0;
-          okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 4, s_abort, kStatusTimeoutReduce,
+          okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 4, ab, kStatusTimeoutReduce,
                              budget) ? 1 : 0;
           if (tr != nullptr && warp == 2) tr[6] += globaltimer_ns() - w0;
         }
@@ -899,121 +926,125 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
     }
   } else {
     // ----------------------------------------------------------------- comm
-    if (p.ag_src != nullptr) {
-      const int ctid = threadIdx.x - 6 * 32;  // 0..127
-      const int chunks = (p.seg_rows + kBM - 1) / kBM;
-      const int nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
-      // Unit = 32 rows x 2 KB of the shard for one destination. Units are ordered destination by
-      // destination (the rank that needs this shard soonest first: rank-1, rank-2, ...), and one
-      // destination's units are spread over all CTAs, so that at any moment every rank sends to one peer
-      // and receives from one peer at full link rate and the shards land in the order they are consumed.
-      constexpr int kSubs = kBM / kAgSubRows;
-      const int per_dest = chunks * kSubs * nslices;
-      const int d_first = p.a_own_valid ? 1 : 0;  // own tiles read the caller's tensor: nothing to copy
-      const int total_units = (p.world - d_first) * per_dest;
-      for (int u = blockIdx.x; u < total_units; u += gridDim.x) {
-        const int d = d_first + u / per_dest;
-        const int rem = u - (d - d_first) * per_dest;
-        const int chunk = rem / (kSubs * nslices);
-        const int rem2 = rem - chunk * (kSubs * nslices);
-        const int sub = rem2 / nslices;
-        const int ks = rem2 - sub * nslices;
-        int dest = p.rank - d;
-        if (dest < 0) dest += p.world;
-        const int r0 = imin(chunk * kBM + sub * kAgSubRows, p.seg_rows);
-        const int r1 = imin(r0 + kAgSubRows, p.seg_rows);
-        const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
-        const long long b1 = (b0 + kCommSliceBytes < p.ag_row_bytes) ? b0 + kCommSliceBytes : p.ag_row_bytes;
-        const int vec_per_row = static_cast<int>((b1 - b0) >> 4);
-        const uint8_t* src = p.ag_src + static_cast<long long>(r0) * p.ag_row_bytes + b0;
-        uint8_t* dst = p.ag_dst[dest] +
-                       (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0;
-        // one 16-byte column of the slice per thread, 8 rows in flight
-        const int nrows = r1 - r0;  // 0 for a unit past the shard's last row: it still signals
-        if (ctid < vec_per_row) {
-          const uint8_t* s0 = src + ctid * 16;
-          uint8_t* d0 = dst + ctid * 16;
-          for (int rr = 0; rr < nrows; rr += 8) {
-            uint4 val[8];
+    // All-gather push and (MoE layer 0) permute. The four comm warps of a CTA work independently: a unit
+    // is 8 rows x 2 KB handled by ONE warp (four 512-byte row pieces per row, 16 x 16 bytes in flight per
+    // lane), followed by that warp's own system-scope fence and counter update, so one warp's wait for
+    // its stores to be acknowledged over NVLink overlaps the other warps' copies.
+    // Steps d = 0 .. world-1 interleave the two jobs: push this rank's shard to the rank that needs it
+    // d-th soonest (rank-1, rank-2, ...; one destination at a time, so every link carries one stream at
+    // full rate and shards land in the order they are consumed), then permute the tokens of source
+    // rank+d (own tokens first), which that source pushed during its own step d-1.
+    if (p.ag_src != nullptr || p.g_sorted != nullptr) {
+      const int cw = warp - 6;                       // comm warp of this CTA, 0..3
+      const int gw = cta_id * 4 + cw;                // comm warp of the launch
+      const int gw_step = num_ctas * 4;
+      const int d_first = (p.ag_src != nullptr && p.a_own_valid) ? 1 : 0;  // own tiles read the caller's tensor
+      const int push_chunks = (p.seg_rows + kBM - 1) / kBM;
+      const int units_per_dest = ag_nslices * push_chunks * kAgUnitsPerSlice;
+      const int perm_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
+      const int units_per_src = ag_nslices * perm_chunks * kAgUnitsPerSlice;
+      bool comm_ok = true;
+      for (int d = 0; comm_ok && d < p.world; ++d) {
+        if (p.ag_src != nullptr && d + d_first < p.world) {
+          int dest = p.rank - (d + d_first);
+          if (dest < 0) dest += p.world;
+          // units of one destination in slice-major order: the first 2 KB of every row go out first, so
+          // that the consumer's walk along K can begin after a fraction of the shard has crossed
+          for (int u = gw; u < units_per_dest; u += gw_step) {
+            const int ks = u / (push_chunks * kAgUnitsPerSlice);
+            const int rem = u - ks * (push_chunks * kAgUnitsPerSlice);
+            const int chunk = rem / kAgUnitsPerSlice;
+            const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.seg_rows);
+            const int nrows = imin(kAgUnitRows, p.seg_rows - r0);  // 0 for a unit past the shard's last row: it still signals
+            const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
+            const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
+            const uint8_t* src = p.ag_src + static_cast<long long>(r0) * p.ag_row_bytes + b0 + lane * 16;
+            uint8_t* dst = p.ag_dst[dest] + (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0 + lane * 16;
+#pragma unroll 1
+            for (int rr = 0; rr < nrows; rr += kCommRowsInFlight) {
+              uint4 val[kCommRowsInFlight][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (rr + j < nrows)
-                val[j] = __ldg(reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes));
+              for (int j = 0; j < kCommRowsInFlight; ++j)
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (rr + j < nrows)
-                *reinterpret_cast<uint4*>(d0 + (rr + j) * p.ag_row_bytes) = val[j];
+                for (int q = 0; q < 4; ++q)
+                  if (rr + j < nrows && q * 512 + lane * 16 < slice_bytes)
+                    val[j][q] = __ldg(reinterpret_cast<const uint4*>(src + (rr + j) * p.ag_row_bytes + q * 512));
+#pragma unroll
+              for (int j = 0; j < kCommRowsInFlight; ++j)
+#pragma unroll
+                for (int q = 0; q < 4; ++q)
+                  if (rr + j < nrows && q * 512 + lane * 16 < slice_bytes)
+                    *reinterpret_cast<uint4*>(dst + (rr + j) * p.ag_row_bytes + q * 512) = val[j][q];
+            }
+            if (ks == 0 && p.ag_src_scale != nullptr && lane < nrows)
+              p.ag_dst_scale[dest][static_cast<long long>(p.rank) * p.seg_rows + r0 + lane] = p.ag_src_scale[r0 + lane];
+            __syncwarp();
+            if (lane == 0) {
+              fence_acq_rel_sys();
+              red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk * p.ag_groups + ks / p.ag_spf, 1);
+            }
           }
         }
-        if (ks == 0 && p.ag_src_scale != nullptr) {
-          float* sd = p.ag_dst_scale[dest] + static_cast<long long>(p.rank) * p.seg_rows;
-          for (int rr = r0 + ctid; rr < r1; rr += 128) sd[rr] = p.ag_src_scale[rr];
-        }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ctid == 0) {
-          fence_acq_rel_sys();
-          red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk, 1);
-        }
-      }
-    }
-    if (p.g_sorted != nullptr) {
-      // MoE layer 0, permute form. Work item = (source rank, 128-token chunk, 2 KB slice of the row):
-      // wait (bounded) for the chunk's arrival counter, then copy every token row of the chunk to its
-      // top-k rows of the expert-sorted buffer (one load, top-k stores) and count the item as done for
-      // that source rank. Source ranks are taken in arrival order, this rank's own tokens first.
-      const int ctid = threadIdx.x - 6 * 32;
-      const int chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
-      const int nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
-      const int per_src = chunks * nslices;
-      const int total_items = p.world * per_src;
-      volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
-      for (int u = blockIdx.x; u < total_items; u += gridDim.x) {
-        const int d = u / per_src;
-        const int rem = u - d * per_src;
-        const int chunk = rem / nslices;
-        const int ks = rem - chunk * nslices;
-        int src_rank = p.rank + d;
-        if (src_rank >= p.world) src_rank -= p.world;
-        if (p.ag_flags != nullptr) {
-          if (ctid == 0)
-            *s_flag = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk, p.ag_expected, s_abort,
-                                   kStatusTimeoutFlag, budget) ? 1 : 0;
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          const int okp = *s_flag;
-          asm volatile("bar.sync 1, 128;" ::: "memory");
-          if (!okp) break;
-        }
-        const int r0 = chunk * kBM;
-        const int r1 = imin(r0 + kBM, p.g_rows_per_rank);
-        const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
-        const long long b1 = (b0 + kCommSliceBytes < p.ag_row_bytes) ? b0 + kCommSliceBytes : p.ag_row_bytes;
-        const int vec_per_row = static_cast<int>((b1 - b0) >> 4);
-        if (ctid < vec_per_row) {
+        if (p.g_sorted != nullptr) {
+          // MoE layer 0, permute form: copy every token row of source rank+d to its top-k rows of the
+          // expert-sorted buffer (one load, top-k stores per 16-byte piece) and count the unit as done
+          // for that source; a tile waits until every source rank it reads is complete.
+          int src_rank = p.rank + d;
+          if (src_rank >= p.world) src_rank -= p.world;
           const long long tok0 = static_cast<long long>(src_rank) * p.g_rows_per_rank;
-          const uint8_t* s0 = p.g_tokens + (tok0 + r0) * p.ag_row_bytes + b0 + ctid * 16;
-          uint8_t* d0 = p.g_sorted + b0 + ctid * 16;
-          const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
-          const int nrows = r1 - r0;
-          for (int rr = 0; rr < nrows; rr += 8) {
-            uint4 val[8];
+          for (int u = gw; comm_ok && u < units_per_src; u += gw_step) {
+            const int ks = u / (perm_chunks * kAgUnitsPerSlice);
+            const int rem = u - ks * (perm_chunks * kAgUnitsPerSlice);
+            const int chunk = rem / kAgUnitsPerSlice;
+            const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.g_rows_per_rank);
+            const int nrows = imin(kAgUnitRows, p.g_rows_per_rank - r0);
+            if (p.ag_flags != nullptr) {
+              int okp = 1;
+              if (lane == 0) {
+                const int grp = ks / p.ag_spf;
+                const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
+                okp = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk * p.ag_groups + grp,
+                                   kAgUnitsPerSlice * in_group, ab, kStatusTimeoutFlag, budget) ? 1 : 0;
+              }
+              okp = __shfl_sync(0xffffffffu, okp, 0);
+              if (!okp) {
+                comm_ok = false;
+                break;
+              }
+            }
+            const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
+            const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
+            const uint8_t* s0 = p.g_tokens + (tok0 + r0) * p.ag_row_bytes + b0 + lane * 16;
+            uint8_t* d0 = p.g_sorted + b0 + lane * 16;
+            const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
+#pragma unroll 1
+            for (int rr = 0; rr < nrows; rr += kCommRowsInFlight) {
+              uint4 val[kCommRowsInFlight][4];
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (rr + j < nrows) val[j] = *reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes);
+              for (int j = 0; j < kCommRowsInFlight; ++j)
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              if (rr + j < nrows)
-                for (int k = 0; k < p.g_topk; ++k) {
-                  const long long drow = si[(rr + j) * p.g_topk + k];
-                  if (drow >= 0 && drow < p.M)  // a corrupt routing entry must not become a wild store
-                    *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
-                }
+                for (int q = 0; q < 4; ++q)
+                  if (rr + j < nrows && q * 512 + lane * 16 < slice_bytes)
+                    val[j][q] = *reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes + q * 512);
+#pragma unroll
+              for (int j = 0; j < kCommRowsInFlight; ++j)
+                if (rr + j < nrows)
+                  for (int k = 0; k < p.g_topk; ++k) {
+                    const long long drow = si[(rr + j) * p.g_topk + k];
+                    if (drow >= 0 && drow < p.M) {  // a corrupt routing entry must not become a wild store
+#pragma unroll
+                      for (int q = 0; q < 4; ++q)
+                        if (q * 512 + lane * 16 < slice_bytes)
+                          *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes + q * 512) = val[j][q];
+                    }
+                  }
+            }
+            __syncwarp();
+            if (lane == 0) {
+              __threadfence();
+              red_add_release_sys(p.g_perm_done + src_rank, 1);
+            }
           }
-        }
-        __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");
-        if (ctid == 0) {
-          __threadfence();
-          red_add_release_sys(p.g_perm_done + src_rank, 1);
         }
       }
     }
@@ -1032,14 +1063,14 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
       const long long slot = static_cast<long long>(p.seg_rows) * p.N;
       float* sum_base = p.rs_stage[p.rank];  // this rank's slot in its own staging
       volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
-      for (int item = blockIdx.x; item < total_items; item += gridDim.x) {
+      for (int item = cta_id; item < total_items; item += num_ctas) {
         const int quarter = item & 3;
         const int rt = item >> 2;
         const int c = rt % m_chunks;
         const int nt = rt / m_chunks;
         const int tix = c * n_tiles + nt;
         if (ctid == 0)
-          *s_flag = flag_wait_eq(p.rs_local_cnt + tix, 4 * (p.world - 1), s_abort, kStatusTimeoutReduce, budget) ? 1 : 0;
+          *s_flag = flag_wait_eq(p.rs_local_cnt + tix, 4 * (p.world - 1), ab, kStatusTimeoutReduce, budget) ? 1 : 0;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int okr = *s_flag;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1141,18 +1172,35 @@ fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
   if (CTA2) cluster_sync_all(); else __syncthreads();
   const int err = *s_abort;
   if (err != 0) {
+    // (copies and UMMAs that were in flight have been waited for by the roles that issued them)
     if (threadIdx.x == 0) {
       *reinterpret_cast<volatile int*>(p.status) = err;
       __threadfence_system();
     }
-    // let copies and MMAs that are still in flight land before the CTA's memory goes away
-    __nanosleep(200000);
   }
   if (warp == 1) {
     __syncwarp();
     tc_fence_after();
     if (CTA2) tmem_dealloc_2cta(tmem_base, TMEM_COLS); else tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+template <int BN, int STAGES, int KIND, bool CTA2>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_kernel(const __grid_constant__ GemmParams p, const uint32_t idesc) {
+  fused_gemm_body<BN, STAGES, KIND, CTA2>(p, idesc, static_cast<int>(blockIdx.x), static_cast<int>(gridDim.x));
+}
+
+// Several ranks' problems in ONE launch on one GPU: CTAs [r * ctas_per_rank, (r + 1) * ctas_per_rank) work on
+// problem `ps[r]` exactly as a launch of their own would. Kernels of different ranks wait on one another's
+// flags, so they can only share a GPU inside a single (cooperative) launch whose CTAs are all resident; this
+// is how a single-GPU machine exercises the multi-rank protocol (pushes, counters, owner-side sums).
+// `ps` lives in global memory (64-byte aligned: it holds tensor maps).
+template <int BN, int STAGES, int KIND, bool CTA2>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_ranks_kernel(const GemmParams* __restrict__ ps, const int ctas_per_rank, const uint32_t idesc) {
+  const int r = static_cast<int>(blockIdx.x) / ctas_per_rank;
+  fused_gemm_body<BN, STAGES, KIND, CTA2>(ps[r], idesc, static_cast<int>(blockIdx.x) - r * ctas_per_rank, ctas_per_rank);
 }
 
 }  // namespace fluxb

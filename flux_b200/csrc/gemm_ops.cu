@@ -75,6 +75,12 @@ static int pick_block_n(long long m_tiles, int n, int ctas, int per_cta_div, boo
   return best;
 }
 
+int ag_slices_per_flag(long long row_bytes) {
+  const long long nslices = (row_bytes + kCommSliceBytes - 1) / kCommSliceBytes;
+  const long long spf = (nslices + kAgMaxGroups - 1) / kAgMaxGroups;
+  return spf < 1 ? 1 : static_cast<int>(spf);
+}
+
 int resolve_cta_group(const GemmParams& p, const fluxb_tuning* tuning) {
   if (tuning != nullptr && (tuning->cta_group == 1 || tuning->cta_group == 2)) return tuning->cta_group;
   if (p.g_tiles != nullptr) return 1;
@@ -90,13 +96,23 @@ int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tun
     const int tile_m = cg == 2 ? 2 * kBM : kBM;
     long long m_tiles = m_tiles_hint;
     if (m_tiles <= 0) m_tiles = static_cast<long long>(p.nseg) * ((p.seg_rows + tile_m - 1) / tile_m);
-    int ctas = (tuning != nullptr && tuning->num_ctas > 0) ? tuning->num_ctas : comm->sm_count;
+    int share = comm->ranks_on_gpu > 1 ? ((comm->sm_count / comm->ranks_on_gpu) & ~1) : comm->sm_count;
+    int ctas = (tuning != nullptr && tuning->num_ctas > 0 && tuning->num_ctas < share) ? tuning->num_ctas : share;
     bn = pick_block_n(m_tiles, p.N, cg == 2 ? ctas / 2 : ctas, cg == 2 ? 2 : 1, p.b_mn_major != 0);
   }
   return bn;
 }
 
-int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
+int enqueue_or_defer(fluxb_comm* comm, cudaStream_t stream, std::function<int(cudaStream_t)> fn) {
+  if (comm->ranks_on_gpu <= 1) return fn(stream);
+  DeferredItem it;
+  it.fused = false;
+  it.plain = std::move(fn);
+  comm->deferred.push_back(std::move(it));
+  return FLUXB_OK;
+}
+
+int launch_fused_gemm(fluxb_comm* comm, GemmParams& p, int in_dtype,
                       const fluxb_tuning* tuning, cudaStream_t stream) {
   const int cg = resolve_cta_group(p, tuning);
   const int bn = resolve_block_n(comm, p, tuning, p.g_tiles != nullptr ? 1024 : 0);
@@ -104,6 +120,7 @@ int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
   FLUXB_REQUIRE(!p.b_mn_major || (bn / (cg == 2 ? 2 : 1)) % 64 == 0,
                 "a [K,N] weight needs a tile width whose per-CTA share is a multiple of 64 (block_n=%d, cta_group=%d)", bn, cg);
   int grid = comm->sm_count;
+  if (comm->ranks_on_gpu > 1) grid = (grid / comm->ranks_on_gpu) & ~1;  // this rank's share of the GPU
   if (tuning != nullptr && tuning->num_ctas > 0) grid = tuning->num_ctas < grid ? tuning->num_ctas : grid;
   if (p.g_tiles == nullptr) {
     const int tile_m = cg == 2 ? 2 * kBM : kBM;
@@ -114,6 +131,8 @@ int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
   }
   if (grid < 1) grid = 1;
   if (p.group_m <= 0) p.group_m = (tuning != nullptr && tuning->group_m > 0) ? tuning->group_m : 8;
+  if (p.ag_spf <= 0) p.ag_spf = 1;
+  if (p.ag_groups <= 0) p.ag_groups = kAgMaxGroups;
   p.status = comm->status_dev;
   p.timeout_ns = comm->timeout_ns;
   p.trace = comm->trace;
@@ -131,16 +150,28 @@ int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
     default: FLUXB_FAIL(FLUXB_ERR_INVALID, "input dtype %d is not bf16/f16/e4m3/e5m2", in_dtype);
   }
   const uint32_t idesc = make_idesc(fmt, cg == 2 ? 2 * kBM : kBM, static_cast<uint32_t>(bn), p.b_mn_major ? 1u : 0u);
+  if (comm->ranks_on_gpu > 1) {
+    DeferredItem it;
+    it.fused = true;
+    it.p = p;
+    it.idesc = idesc;
+    it.bn = bn;
+    it.kind = kind;
+    it.cta_group = cg;
+    it.grid = cg == 2 ? (grid & ~1) : grid;
+    comm->deferred.push_back(std::move(it));
+    return FLUXB_OK;
+  }
 #define FLUXB_LAUNCH(BN_, ST1_, ST2_)                                                              \
   (cg == 2 ? (kind == 0 ? launch_inst<BN_, ST2_, 0, true>(comm, p, idesc, grid, stream)            \
                         : launch_inst<BN_, ST2_, 1, true>(comm, p, idesc, grid, stream))           \
            : (kind == 0 ? launch_inst<BN_, ST1_, 0, false>(comm, p, idesc, grid, stream)           \
                         : launch_inst<BN_, ST1_, 1, false>(comm, p, idesc, grid, stream)))
   switch (bn) {
-    case 256: return FLUXB_LAUNCH(256, 4, 6);
-    case 192: return FLUXB_LAUNCH(192, 5, 7);
-    case 128: return FLUXB_LAUNCH(128, 6, 8);
-    default: return FLUXB_LAUNCH(64, 8, 8);
+    case 256: return FLUXB_LAUNCH(256, stages_for(256, false), stages_for(256, true));
+    case 192: return FLUXB_LAUNCH(192, stages_for(192, false), stages_for(192, true));
+    case 128: return FLUXB_LAUNCH(128, stages_for(128, false), stages_for(128, true));
+    default: return FLUXB_LAUNCH(64, stages_for(64, false), stages_for(64, true));
   }
 #undef FLUXB_LAUNCH
 }
@@ -204,9 +235,10 @@ struct fluxb_gemm_rs {
   unsigned long long calls;
 };
 
+// arrival counters per source rank: one per (128-row chunk, slice group)
 static int ag_flag_stride(int full_m, int world) {
   const int per_rank = (full_m + world - 1) / world;
-  return (per_rank + kBM - 1) / kBM;
+  return ((per_rank + kBM - 1) / kBM) * kAgMaxGroups;
 }
 
 extern "C" {
@@ -299,6 +331,14 @@ int fluxb_ag_gemm_destroy(fluxb_ag_gemm_t op) {
   return FLUXB_OK;
 }
 
+int fluxb_ag_gemm_reset(fluxb_ag_gemm_t op, fluxb_stream_t stream) {
+  FLUXB_REQUIRE(op != nullptr, "ag_gemm_reset: op is NULL");
+  FLUXB_CUDA(cudaMemsetAsync(op->flags[op->comm->rank], 0, fluxb_ag_gemm_flag_bytes(op->full_m, op->comm->world),
+                             static_cast<cudaStream_t>(stream)));
+  op->calls = 0;
+  return FLUXB_OK;
+}
+
 int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, const void* b,
                           int n, int k, void* c, const void* bias, int bias_mode,
                           const float* scale_a_shard, const float* scale_b, float alpha, int flags,
@@ -358,7 +398,8 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   p.alpha = alpha;
   p.ag_flags = op->flags[comm->rank] + parity * half_flags;
   p.ag_flag_stride = op->flag_stride;
-  p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes) * (kBM / kAgSubRows);
+  p.ag_groups = kAgMaxGroups;
+  p.ag_spf = ag_slices_per_flag(row_bytes);
   p.ag_src = static_cast<const uint8_t*>(a_shard);
   p.ag_row_bytes = row_bytes;
   p.ag_src_scale = scale_a_shard;
@@ -394,9 +435,13 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   op->calls += 1;
   if (gathered_out != nullptr) {
     // peers' shards come from the gather buffer, this rank's own shard from the caller's tensor
-    FLUXB_CUDA(cudaMemcpyAsync(gathered_out, local_gather, m * row_bytes, cudaMemcpyDeviceToDevice, stream));
-    FLUXB_CUDA(cudaMemcpyAsync(static_cast<uint8_t*>(gathered_out) + static_cast<size_t>(comm->rank) * m_local * row_bytes,
-                               a_shard, m_local * row_bytes, cudaMemcpyDeviceToDevice, stream));
+    const size_t all_bytes = static_cast<size_t>(m) * row_bytes, own_bytes = static_cast<size_t>(m_local) * row_bytes;
+    uint8_t* own_dst = static_cast<uint8_t*>(gathered_out) + static_cast<size_t>(comm->rank) * own_bytes;
+    return enqueue_or_defer(comm, stream, [=](cudaStream_t st) -> int {
+      FLUXB_CUDA(cudaMemcpyAsync(gathered_out, local_gather, all_bytes, cudaMemcpyDeviceToDevice, st));
+      FLUXB_CUDA(cudaMemcpyAsync(own_dst, a_shard, own_bytes, cudaMemcpyDeviceToDevice, st));
+      return FLUXB_OK;
+    });
   }
   return FLUXB_OK;
 }
@@ -447,6 +492,14 @@ int fluxb_gemm_rs_create(fluxb_comm_t comm, int max_m, int n_dim, int in_dtype, 
 
 int fluxb_gemm_rs_destroy(fluxb_gemm_rs_t op) {
   delete op;
+  return FLUXB_OK;
+}
+
+int fluxb_gemm_rs_reset(fluxb_gemm_rs_t op, fluxb_stream_t stream) {
+  FLUXB_REQUIRE(op != nullptr, "gemm_rs_reset: op is NULL");
+  FLUXB_CUDA(cudaMemsetAsync(op->cnt[op->comm->rank], 0, fluxb_gemm_rs_cnt_bytes(op->max_m, op->n_dim, op->comm->world),
+                             static_cast<cudaStream_t>(stream)));
+  op->calls = 0;
   return FLUXB_OK;
 }
 

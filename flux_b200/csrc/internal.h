@@ -6,7 +6,9 @@
 #include <stdarg.h>
 #include <stdio.h>
 
+#include <functional>
 #include <string>
+#include <vector>
 
 #include "../../include/fluxb.h"
 #include "gemm_kernel.cuh"
@@ -53,6 +55,19 @@ inline bool is_16bit(int dt) { return dt == FLUXB_BF16 || dt == FLUXB_F16; }
 
 }  // namespace fluxb
 
+namespace fluxb {
+// One piece of work a forward call would have put on the stream, kept back while several ranks share one
+// GPU (fluxb_comm_set_ranks_on_gpu): either a launch of the fused kernel (its parameters and template
+// choice) or any other stream work (a closure).
+struct DeferredItem {
+  bool fused = false;
+  GemmParams p;
+  uint32_t idesc = 0;
+  int bn = 0, kind = 0, cta_group = 1, grid = 0;
+  std::function<int(cudaStream_t)> plain;
+};
+}  // namespace fluxb
+
 struct fluxb_comm {
   int rank = 0;
   int world = 1;
@@ -65,6 +80,11 @@ struct fluxb_comm {
   unsigned long long* trace = nullptr;  // optional per-CTA timeline buffer (caller-owned device memory)
   float* splitk_scratch = nullptr;  // sm_count x 128 x 256 fp32: parked partial accumulators of split tail tiles
   int* splitk_cnt = nullptr;        // per (tail tile, half, epilogue warp) arrivals, zero between launches
+  // several ranks on one GPU (test harness): forwards queue their stream work here, fluxb_run_ranks issues it
+  int ranks_on_gpu = 1;
+  std::vector<fluxb::DeferredItem> deferred;
+  fluxb::GemmParams* ranks_params_dev = nullptr;   // [kMaxRankItems][kMaxWorld] parameter blocks of merged launches
+  fluxb::GemmParams* ranks_params_host = nullptr;  // pinned staging of the same
 };
 
 namespace fluxb {
@@ -87,11 +107,29 @@ int encode_tmap_b16_store(CUtensorMap* out, const void* base, long long rows, lo
 int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tuning* tuning,
                     long long m_tiles_hint);
 
+// 2 KB slices of a row that share one arrival counter (1 unless the row has more than kAgMaxGroups slices)
+int ag_slices_per_flag(long long row_bytes);
+
 // 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile (the caller's choice or a heuristic).
 int resolve_cta_group(const GemmParams& p, const fluxb_tuning* tuning);
 
-// Fill the problem-independent fields and launch the fused kernel.
-int launch_fused_gemm(const fluxb_comm* comm, GemmParams& p, int in_dtype,
+// Fill the problem-independent fields and launch the fused kernel (or queue the launch while several
+// ranks share the GPU).
+int launch_fused_gemm(fluxb_comm* comm, GemmParams& p, int in_dtype,
                       const fluxb_tuning* tuning, cudaStream_t stream);
+
+// Run `fn(stream)` now, or queue it behind the queued launches while several ranks share the GPU.
+int enqueue_or_defer(fluxb_comm* comm, cudaStream_t stream, std::function<int(cudaStream_t)> fn);
+
+constexpr int kMaxRankItems = 16;  // queued fused launches per fluxb_run_ranks call
+
+// pipeline depth of each tile width: one CTA per tile / CTA pair
+constexpr int stages_for(int bn, bool cta2) {
+  return bn == 256 ? (cta2 ? 6 : 4) : bn == 192 ? (cta2 ? 7 : 5) : bn == 128 ? (cta2 ? 8 : 6) : 8;
+}
+
+// One launch that runs `nranks` problems side by side (loopback.cu).
+int launch_ranks_kernel(int bn, int kind, int cta_group, const GemmParams* ps_dev, int nranks, int ctas_per_rank,
+                        uint32_t idesc, cudaStream_t stream);
 
 }  // namespace fluxb

@@ -5,9 +5,10 @@
 // shard is pushed to every peer by the kernel's comm warps, the routing tables
 // (inverse permutation, per-expert M tiles, which source ranks a tile reads)
 // are built on the device - no device-to-host copy or host scheduling per call
-// (the reference does both, :323-363) - and A rows are fetched by token index
-// with TMA gather4, so the gathered-and-permuted activation matrix is never
-// materialised.
+// (the reference does both, :323-363) - and the comm warps copy arriving tokens
+// into an expert-sorted activation buffer that the GEMM reads with plain tiled
+// loads. (The entry point without a workspace, at the end of this file, has no
+// room for that buffer and fetches A rows by token index with TMA gather4.)
 //
 // Layer 1 (grouped GEMM + top-k gather + reduce-scatter) replaces
 // src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:595-820: grouped GEMM
@@ -209,7 +210,7 @@ moe_rs_reduce_kernel(const T* __restrict__ stage, int* cnt, T* out, int n, int t
   const long long slot = static_cast<long long>(tokens_per_rank) * n;
   for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
     if (threadIdx.x == 0)
-      s_ok = flag_wait_eq(cnt + blk, world, nullptr, kStatusTimeoutReduce, budget_ns) ? 1 : 0;
+      s_ok = flag_wait_eq(cnt + blk, world, AbortWord{nullptr, 0u}, kStatusTimeoutReduce, budget_ns) ? 1 : 0;
     __syncthreads();
     if (!s_ok) {
       if (threadIdx.x == 0) {
@@ -277,7 +278,7 @@ struct fluxb_moe_gather_rs {
 
 static int flag_stride_of(int full_m, int world) {
   const int per_rank = (full_m + world - 1) / world;
-  return (per_rank + kBM - 1) / kBM;
+  return ((per_rank + kBM - 1) / kBM) * kAgMaxGroups;  // same layout as the dense all-gather counters
 }
 
 extern "C" {
@@ -331,6 +332,15 @@ int fluxb_moe_ag_scatter_create(fluxb_comm_t comm, int max_ntokens, int hidden, 
 
 int fluxb_moe_ag_scatter_destroy(fluxb_moe_ag_scatter_t op) {
   delete op;
+  return FLUXB_OK;
+}
+
+int fluxb_moe_ag_scatter_reset(fluxb_moe_ag_scatter_t op, fluxb_stream_t stream) {
+  FLUXB_REQUIRE(op != nullptr, "moe_ag_scatter_reset: op is NULL");
+  FLUXB_CUDA(cudaMemsetAsync(op->flags[op->comm->rank], 0, fluxb_ag_gemm_flag_bytes(op->max_ntokens, op->comm->world),
+                             static_cast<cudaStream_t>(stream)));
+  op->calls = 0;
+  op->last_parity = -1;
   return FLUXB_OK;
 }
 
@@ -422,7 +432,8 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   if (world > 1 && !reuse) {
     p.ag_flags = op->flags[comm->rank] + parity * half_flags;
     p.ag_flag_stride = op->flag_stride;
-    p.ag_expected = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes) * (kBM / kAgSubRows);
+    p.ag_groups = kAgMaxGroups;
+    p.ag_spf = ag_slices_per_flag(row_bytes);
     p.ag_src = static_cast<const uint8_t*>(tokens_shard);
     for (int r = 0; r < world; ++r) {
       p.ag_dst[r] = op->gather[r] + parity * half_gather;
@@ -450,9 +461,14 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
     op->last_ntokens = ntokens_local;
     op->calls += 1;
   }
-  if (gathered_out != nullptr)
-    FLUXB_CUDA(cudaMemcpyAsync(gathered_out, op->gather[comm->rank] + parity * half_gather, ntokens * row_bytes,
-                               cudaMemcpyDeviceToDevice, stream));
+  if (gathered_out != nullptr) {
+    const uint8_t* src = op->gather[comm->rank] + parity * half_gather;
+    const size_t bytes = static_cast<size_t>(ntokens) * row_bytes;
+    return enqueue_or_defer(comm, stream, [=](cudaStream_t st) -> int {
+      FLUXB_CUDA(cudaMemcpyAsync(gathered_out, src, bytes, cudaMemcpyDeviceToDevice, st));
+      return FLUXB_OK;
+    });
+  }
   return FLUXB_OK;
 }
 
@@ -507,6 +523,14 @@ int fluxb_moe_gather_rs_create(fluxb_comm_t comm, int nexperts, int max_m, int n
 
 int fluxb_moe_gather_rs_destroy(fluxb_moe_gather_rs_t op) {
   delete op;
+  return FLUXB_OK;
+}
+
+int fluxb_moe_gather_rs_reset(fluxb_moe_gather_rs_t op, fluxb_stream_t stream) {
+  FLUXB_REQUIRE(op != nullptr, "moe_gather_rs_reset: op is NULL");
+  FLUXB_CUDA(cudaMemsetAsync(op->cnt[op->comm->rank], 0, fluxb_moe_gather_rs_cnt_bytes(op->max_m, op->topk, op->comm->world),
+                             static_cast<cudaStream_t>(stream)));
+  op->calls = 0;
   return FLUXB_OK;
 }
 
@@ -605,22 +629,34 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   int rgrid = blocks_per_owner < 2 * comm->sm_count ? blocks_per_owner : 2 * comm->sm_count;
   const void* local_stage = static_cast<uint8_t*>(op->stage[comm->rank]) + parity * half_stage_elems * 2;
   int* local_cnt = op->cnt[comm->rank] + parity * op->cnt_cap;
-  if (op->out_dtype == FLUXB_BF16) {
-    moe_topk_push_kernel<__nv_bfloat16><<<pgrid, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(inter), routing_idx_dev, topk, n, m, tpr, comm->rank, world, tg);
+  const int out_dtype = op->out_dtype;
+  const int rank = comm->rank;
+  int* status_dev = comm->status_dev;
+  const unsigned long long budget = comm->timeout_ns;
+  // every rank's pushes are issued before any rank's owner-side sum (two queue entries when ranks share a GPU)
+  rc = enqueue_or_defer(comm, stream, [=](cudaStream_t st) -> int {
+    if (out_dtype == FLUXB_BF16)
+      moe_topk_push_kernel<__nv_bfloat16><<<pgrid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(inter), routing_idx_dev,
+                                                                 topk, n, m, tpr, rank, world, tg);
+    else
+      moe_topk_push_kernel<__half><<<pgrid, 256, 0, st>>>(static_cast<const __half*>(inter), routing_idx_dev, topk, n, m,
+                                                          tpr, rank, world, tg);
     FLUXB_CUDA(cudaGetLastError());
-    moe_rs_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, stream>>>(
-        static_cast<const __nv_bfloat16*>(local_stage), local_cnt, static_cast<__nv_bfloat16*>(out), n, tpr, world,
-        comm->status_dev, comm->timeout_ns);
-  } else {
-    moe_topk_push_kernel<__half><<<pgrid, 256, 0, stream>>>(static_cast<const __half*>(inter), routing_idx_dev, topk,
-                                                           n, m, tpr, comm->rank, world, tg);
+    return FLUXB_OK;
+  });
+  if (rc != FLUXB_OK) return rc;
+  rc = enqueue_or_defer(comm, stream, [=](cudaStream_t st) -> int {
+    if (out_dtype == FLUXB_BF16)
+      moe_rs_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(local_stage), local_cnt,
+                                                                 static_cast<__nv_bfloat16*>(out), n, tpr, world, status_dev,
+                                                                 budget);
+    else
+      moe_rs_reduce_kernel<__half><<<rgrid, 256, 0, st>>>(static_cast<const __half*>(local_stage), local_cnt,
+                                                          static_cast<__half*>(out), n, tpr, world, status_dev, budget);
     FLUXB_CUDA(cudaGetLastError());
-    moe_rs_reduce_kernel<__half><<<rgrid, 256, 0, stream>>>(static_cast<const __half*>(local_stage), local_cnt,
-                                                           static_cast<__half*>(out), n, tpr, world, comm->status_dev,
-                                                           comm->timeout_ns);
-  }
-  FLUXB_CUDA(cudaGetLastError());
+    return FLUXB_OK;
+  });
+  if (rc != FLUXB_OK) return rc;
   op->calls += 1;
   return FLUXB_OK;
 }

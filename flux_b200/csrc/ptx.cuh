@@ -78,11 +78,28 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded mbarrier wait. `s_abort` is a CTA-shared word: non-zero means some
-// role has given up, and every other role must leave its loop too.
+// The abort word of a CTA: non-zero means some role has given up, and every other role must leave
+// its loop too. In a CTA pair the word of the partner CTA is raised as well (a store through
+// distributed shared memory; `peer` is the cluster address of the partner's word, 0 = no partner),
+// so that the partner does not have to run into a timeout of its own.
+struct AbortWord {
+  volatile int* local;
+  uint32_t peer;
+};
+__device__ __forceinline__ void abort_raise(const AbortWord& ab, int code) {
+  if (ab.local == nullptr) return;
+  atomicCAS(const_cast<int*>(ab.local), 0, code);
+  if (ab.peer != 0u)
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(ab.peer), "r"(code) : "memory");
+}
+__device__ __forceinline__ bool abort_seen(const AbortWord& ab) {
+  return ab.local != nullptr && *ab.local != 0;
+}
+
+// Bounded mbarrier wait.
 // `backoff_ns` > 0 sleeps between polls: for waits that normally last many microseconds (an
 // accumulator that is still being computed), so that idle warps do not burn issue slots and power.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* s_abort,
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const AbortWord& ab,
                                           int code, uint64_t budget_ns, uint32_t backoff_ns = 0) {
   if (mbar_try_wait(bar, parity)) return true;
   const uint64_t t0 = globaltimer_ns();
@@ -90,9 +107,9 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   while (!mbar_try_wait(bar, parity)) {
     if (backoff_ns != 0) __nanosleep(backoff_ns);
     if ((++n & 31u) == 0u) {
-      if (*s_abort != 0) return false;
+      if (abort_seen(ab)) return false;
       if (globaltimer_ns() - t0 > budget_ns) {
-        atomicCAS(const_cast<int*>(s_abort), 0, code);
+        abort_raise(ab, code);
         return false;
       }
     }
@@ -131,7 +148,7 @@ __device__ __forceinline__ void red_add_release_sys(int* p, int v) {
 }
 
 // Bounded wait until *flag == want (acquire, system scope).
-__device__ __forceinline__ bool flag_wait_eq(const int* flag, int want, volatile int* s_abort,
+__device__ __forceinline__ bool flag_wait_eq(const int* flag, int want, const AbortWord& ab,
                                              int code, uint64_t budget_ns) {
   if (ld_acquire_sys(flag) == want) return true;
   const uint64_t t0 = globaltimer_ns();
@@ -139,9 +156,9 @@ __device__ __forceinline__ bool flag_wait_eq(const int* flag, int want, volatile
   while (ld_acquire_sys(flag) != want) {
     __nanosleep(64);
     if ((++n & 15u) == 0u) {
-      if (s_abort != nullptr && *s_abort != 0) return false;
+      if (abort_seen(ab)) return false;
       if (globaltimer_ns() - t0 > budget_ns) {
-        if (s_abort != nullptr) atomicCAS(const_cast<int*>(s_abort), 0, code);
+        abort_raise(ab, code);
         return false;
       }
     }

@@ -217,6 +217,8 @@ int fluxb_comm_destroy(fluxb_comm_t comm) {
   if (comm == nullptr) return FLUXB_OK;
   if (comm->splitk_scratch != nullptr) cudaFree(comm->splitk_scratch);
   if (comm->splitk_cnt != nullptr) cudaFree(comm->splitk_cnt);
+  if (comm->ranks_params_dev != nullptr) cudaFree(comm->ranks_params_dev);
+  if (comm->ranks_params_host != nullptr) cudaFreeHost(comm->ranks_params_host);
   if (comm->status_host != nullptr) cudaFreeHost(comm->status_host);
   delete comm;
   return FLUXB_OK;

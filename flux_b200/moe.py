@@ -148,8 +148,11 @@ class GemmGroupedV3AGScatter:
         return outs
 
     def clear_buffers(self):
-        """Arrival counters clear themselves; kept for API compatibility."""
-        return None
+        """`clear_buffers` of the reference op: clears the arrival counters of both buffer parities and restarts
+        the parity sequence (the recovery call after a bounded wait expired; in normal operation the counters are
+        cleared by the calls themselves). Collective; ends with a host barrier."""
+        _lib.check(_lib.load().fluxb_moe_ag_scatter_reset(self._h, _cur_stream()))
+        self.comm.host_barrier()
 
     def profiling(self, inputs_shard, weights, splits_gpu, scatter_index, output_scale=None, outputs_buf=None,
                   allgather_output=None, fast_accum=False, sm_margin=0, prof_ctx=None):
@@ -247,7 +250,10 @@ class GemmGroupedV3GatherRS:
         return out
 
     def ep_zero_buffer(self):
-        return None
+        """Clears the per-token-block arrival counters (the recovery call after a bounded wait expired).
+        Collective; ends with a host barrier."""
+        _lib.check(_lib.load().fluxb_moe_gather_rs_reset(self._h, _cur_stream()))
+        self.comm.host_barrier()
 
     def profiling(self, input, weight, splits_cpu, routing_idx, *args, prof_ctx=None, **kwargs):
         return self.forward_gather_rs(input, weight, splits_cpu, routing_idx, *args, **kwargs)

@@ -209,6 +209,12 @@ class AGKernel:
         except Exception:
             pass
 
+    def reset(self):
+        """Re-arm the op after a call that ended with a device status (a bounded wait expired): clears the
+        arrival counters and restarts the buffer-parity sequence. Collective; ends with a host barrier."""
+        _lib.check(_lib.load().fluxb_ag_gemm_reset(self._h, _cur_stream()))
+        self.comm.host_barrier()
+
     def _prep(self, input, weight, bias, output, input_scale, weight_scale, output_scale, transpose_weight, world):
         _check(input.is_cuda and weight.is_cuda, "AGKernel: tensors must be CUDA tensors")
         _check(input.dim() == 2 and weight.dim() == 2, "AGKernel: input and weight must be 2-D")
@@ -390,15 +396,22 @@ class GemmRS:
         return out
 
     def forward_barrier(self, *args, **kwargs):
-        """Kept for API compatibility (src/pybind/gemm_rs.cc:61-75): the push epilogue needs no barrier."""
-        return None
+        """`GemmRS.forward_barrier` (src/pybind/gemm_rs.cc:61-75) is the all-rank stream barrier the reference
+        puts before its GEMM. The push epilogue needs none (counters are double-buffered by call parity), so
+        this only issues the library's barrier on the current stream for callers that rely on the ordering."""
+        self.comm.barrier_on_stream()
 
     def forward_reduce_scatter(self, *args, **kwargs):
         raise RuntimeError("GemmRS.forward_reduce_scatter: the reduction is fused; call forward()")
 
     def zero_buffers(self):
-        """Counters clear themselves after every call; nothing to zero (gemm_reduce_scatter.cc:654-657)."""
-        return None
+        """`GemmRS.zero_buffers` (gemm_reduce_scatter.cc:654-657): clears the arrival counters and ready flags
+        of both buffer parities and restarts the parity sequence. In normal operation the counters clear
+        themselves; this is the recovery call after a bounded wait expired. Collective; ends with a host barrier."""
+        _lib.check(_lib.load().fluxb_gemm_rs_reset(self._h, _cur_stream()))
+        self.comm.host_barrier()
+
+    reset = zero_buffers
 
     def profiling(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
                   fast_accum=False, prof_ctx=None, reduce_scatter_option=None):

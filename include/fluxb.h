@@ -104,6 +104,17 @@ int fluxb_enable_peer_access(int device, int peer_device);
  * the status word and the kernel returns. */
 int fluxb_barrier_all(fluxb_comm_t comm, int* const* sync_bufs, fluxb_stream_t stream);
 
+/* Several ranks on ONE GPU (machines with fewer GPUs than ranks; the reference's C++ unit test drives all
+ * ranks from one process in the same spirit, src/gemm_rs/test/test_gemm_rs.cc:43-130). Kernels of different
+ * ranks wait on one another's flags, so they cannot be separate launches on one GPU. After
+ * fluxb_comm_set_ranks_on_gpu(comm, n) on each of the n communicators (rank r of world n, all on the current
+ * device, pointer tables filled with local allocations), the forward calls only queue their stream work;
+ * fluxb_run_ranks(comms, n, stream) then issues every rank's queued fused launch as ONE cooperative launch in
+ * which each rank owns 1/n of the grid, and the other queued work rank by rank. Every rank must have made
+ * the same calls in the same order. The call synchronises the stream. n = 1 switches back to normal. */
+int fluxb_comm_set_ranks_on_gpu(fluxb_comm_t comm, int nranks);
+int fluxb_run_ranks(fluxb_comm_t const* comms, int nranks, fluxb_stream_t stream);
+
 /* -------------------------------------------------------------- plain GEMM
  * C[M,N] = alpha * (A[M,K] . B[N,K]^T) * scale_a[m] * scale_b[n] + bias.
  * The TP=1 degenerate of both fused ops; also what AGKernel.gemm_only runs
@@ -131,6 +142,12 @@ int fluxb_ag_gemm_create(fluxb_comm_t comm, int full_m, int n_dim, int k_dim, in
                          int out_dtype, void* const* gather_bufs, int* const* flag_bufs,
                          float* const* scale_bufs, fluxb_ag_gemm_t* out);
 int fluxb_ag_gemm_destroy(fluxb_ag_gemm_t op);
+/* Re-arm after a call that ended with a non-zero status word (a bounded wait expired, so arrival counters
+ * hold partial counts): clears this rank's counters of both buffer parities and restarts the parity
+ * sequence. Collective: every rank calls it, with an all-rank barrier (fluxb_barrier_all or the caller's)
+ * before the next forward. The reference has no recovery path: its waits are unbounded
+ * (include/flux/cuda/system_barrier.hpp:66-103). The other ops have the same call. */
+int fluxb_ag_gemm_reset(fluxb_ag_gemm_t op, fluxb_stream_t stream);
 /* c[M, n] = all_gather(a_shard)[M, k] . b[n, k]^T, M = m_local * world.
  * scale_a_shard: [m_local] fp32 or NULL; scale_b: [n] fp32 or NULL.
  * gathered_out: optional [M,k] device buffer that receives the gathered input
@@ -151,6 +168,8 @@ size_t fluxb_gemm_rs_cnt_bytes(int max_m, int n_dim, int world);
 int fluxb_gemm_rs_create(fluxb_comm_t comm, int max_m, int n_dim, int in_dtype, int out_dtype,
                          float* const* stage_bufs, int* const* cnt_bufs, fluxb_gemm_rs_t* out);
 int fluxb_gemm_rs_destroy(fluxb_gemm_rs_t op);
+/* GemmRS::zero_buffers (src/gemm_rs/ths_op/gemm_reduce_scatter.cc:654-657); see fluxb_ag_gemm_reset. */
+int fluxb_gemm_rs_reset(fluxb_gemm_rs_t op, fluxb_stream_t stream);
 /* out[m/world, n] = reduce_scatter_rows( a[m, k_local] . b[n, k_local]^T (+ bias) ).
  * With a 16-bit output the partials travel to the owner of their rows in that
  * format, as in the reference, are summed there in fp32 and rounded once more;
@@ -184,6 +203,9 @@ int fluxb_moe_ag_scatter_create(fluxb_comm_t comm, int max_ntokens, int hidden, 
                                 void* const* gather_bufs, int* const* flag_bufs, void* workspace,
                                 fluxb_moe_ag_scatter_t* out);
 int fluxb_moe_ag_scatter_destroy(fluxb_moe_ag_scatter_t op);
+/* GemmGroupedV3AGScatterOp::clear_buffers (src/moe_ag_scatter/ths_op/gemm_grouped_v3_ag_scatter.cc:112-126);
+ * see fluxb_ag_gemm_reset. */
+int fluxb_moe_ag_scatter_reset(fluxb_moe_ag_scatter_t op, fluxb_stream_t stream);
 int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_shard,
                                  int ntokens_local, const void* weights, const int* splits_dev,
                                  const int* scatter_index_dev, const float* out_scale, void* out,
@@ -229,6 +251,9 @@ int fluxb_moe_gather_rs_create(fluxb_comm_t comm, int nexperts, int max_m, int n
                                int in_dtype, int out_dtype, float* const* stage_bufs,
                                int* const* cnt_bufs, void* workspace, fluxb_moe_gather_rs_t* out);
 int fluxb_moe_gather_rs_destroy(fluxb_moe_gather_rs_t op);
+/* GemmGroupedV3GatherRS::ep_zero_buffer (src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:549-584); see
+ * fluxb_ag_gemm_reset. */
+int fluxb_moe_gather_rs_reset(fluxb_moe_gather_rs_t op, fluxb_stream_t stream);
 int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, int k_local,
                                 const void* weights, const int* splits_host,
                                 const int* routing_idx_dev, const float* in_scale,

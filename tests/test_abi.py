@@ -34,9 +34,9 @@ def test_size_helpers():
     # two parities of [full_m + one tile, k] elements
     assert lib.fluxb_ag_gemm_gather_bytes(4096, 12288, _lib.BF16) == 2 * (4096 + 128) * 12288 * 2
     assert lib.fluxb_ag_gemm_gather_bytes(8192, 8192, _lib.E4M3) == 2 * (8192 + 128) * 8192
-    # two parities x world x ceil(ceil(full_m/world)/128) counters
-    assert lib.fluxb_ag_gemm_flag_bytes(4096, 8) == 2 * 8 * 4 * 4
-    assert lib.fluxb_ag_gemm_flag_bytes(100, 8) == 2 * 8 * 1 * 4
+    # two parities x world x ceil(ceil(full_m/world)/128) chunks x 64 slice groups of counters
+    assert lib.fluxb_ag_gemm_flag_bytes(4096, 8) == 2 * 8 * 4 * 64 * 4
+    assert lib.fluxb_ag_gemm_flag_bytes(100, 8) == 2 * 8 * 1 * 64 * 4
     assert lib.fluxb_ag_gemm_scale_bytes(4096) == 2 * 4096 * 4
     # fp32 partial tiles, two parities
     assert lib.fluxb_gemm_rs_stage_bytes(4096, 12288, 8) == 2 * 4096 * 12288 * 4
