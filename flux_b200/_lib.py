@@ -40,7 +40,17 @@ STATUS_NAMES = {
 
 
 class Tuning(C.Structure):
-    _fields_ = [("block_n", C.c_int), ("group_m", C.c_int), ("num_ctas", C.c_int), ("cta_group", C.c_int)]
+    _fields_ = [("block_n", C.c_int), ("group_m", C.c_int), ("num_ctas", C.c_int), ("cta_group", C.c_int),
+                ("ag_mode", C.c_int)]
+
+
+TUNING_FIELDS = ("block_n", "group_m", "num_ctas", "cta_group", "ag_mode")
+AG_MODE_KERNEL_PUSH, AG_MODE_COPY_ENGINE = 1, 2
+
+
+def make_tuning(t) -> "Tuning":
+    """A `Tuning` from a dict of its fields (missing fields = 0 = the library's choice)."""
+    return Tuning(*[int(t.get(f, 0)) for f in TUNING_FIELDS])
 
 
 class FluxbError(RuntimeError):

@@ -46,9 +46,8 @@ constexpr int kRowBytes = 128;    // bytes of K per smem row (one swizzle span)
 constexpr int kThreads = 320;
 constexpr int kMaxWorld = 8;
 constexpr int kCommSliceBytes = 2048;  // bytes of one row handled by one comm unit
-constexpr int kAgUnitRows = 8;         // rows of one all-gather push unit (one warp: 8 rows x 2 KB)
+constexpr int kAgUnitRows = 32;        // rows of one all-gather push unit (32 rows x 2 KB by the 128 comm threads)
 constexpr int kAgUnitsPerSlice = kBM / kAgUnitRows;  // units that signal one (128-row chunk, 2 KB slice)
-constexpr int kCommRowsInFlight = 2;   // rows (x 2 KB) a comm warp holds in registers between its loads and stores
 constexpr int kAgMaxGroups = 64;       // arrival counters per (source rank, chunk): one per group of 2 KB slices
 
 enum EpiMode : int {
@@ -92,7 +91,7 @@ struct GemmParams {
   const float* alpha_ptr;  // optional device scalar multiplied into alpha
   // all-gather: consumer side
   // Arrival counters [source rank][128-row chunk][slice group]: a group is `ag_spf` consecutive 2 KB slices
-  // of the rows (1 unless a row has more than kAgMaxGroups slices); every push unit of 8 rows x 2 KB adds 1,
+  // of the rows (1 unless a row has more than kAgMaxGroups slices); every push unit of 32 rows x 2 KB adds 1,
   // so a complete group counts kAgUnitsPerSlice x (slices in the group). The GEMM waits group by group as
   // it walks along K, so a tile starts as soon as the first 2 KB of its rows are in.
   const int* ag_flags;  // null = no waits
@@ -926,23 +925,23 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
     }
   } else {
     // ----------------------------------------------------------------- comm
-    // All-gather push and (MoE layer 0) permute. The four comm warps of a CTA work independently: a unit
-    // is 8 rows x 2 KB handled by ONE warp (four 512-byte row pieces per row, 16 x 16 bytes in flight per
-    // lane), followed by that warp's own system-scope fence and counter update, so one warp's wait for
-    // its stores to be acknowledged over NVLink overlaps the other warps' copies.
+    // All-gather push and (MoE layer 0) permute by the 128 comm threads of the CTA. A unit is 32 rows x 2 KB:
+    // one 16-byte column per thread, 8 rows in flight, then ONE system-scope release per unit (measured on 8
+    // GPUs: the release waits for the unit's stores to be acknowledged over NVLink, so a release per 8 rows
+    // per warp halved the push rate; per 32 rows per CTA it is affordable).
     // Steps d = 0 .. world-1 interleave the two jobs: push this rank's shard to the rank that needs it
     // d-th soonest (rank-1, rank-2, ...; one destination at a time, so every link carries one stream at
     // full rate and shards land in the order they are consumed), then permute the tokens of source
     // rank+d (own tokens first), which that source pushed during its own step d-1.
+    // The push is skipped when the copy engines carry the all-gather (p.ag_src == nullptr).
     if (p.ag_src != nullptr || p.g_sorted != nullptr) {
-      const int cw = warp - 6;                       // comm warp of this CTA, 0..3
-      const int gw = cta_id * 4 + cw;                // comm warp of the launch
-      const int gw_step = num_ctas * 4;
+      const int ctid = threadIdx.x - 6 * 32;  // 0..127
       const int d_first = (p.ag_src != nullptr && p.a_own_valid) ? 1 : 0;  // own tiles read the caller's tensor
       const int push_chunks = (p.seg_rows + kBM - 1) / kBM;
       const int units_per_dest = ag_nslices * push_chunks * kAgUnitsPerSlice;
       const int perm_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
       const int units_per_src = ag_nslices * perm_chunks * kAgUnitsPerSlice;
+      volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
       bool comm_ok = true;
       for (int d = 0; comm_ok && d < p.world; ++d) {
         if (p.ag_src != nullptr && d + d_first < p.world) {
@@ -950,7 +949,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           if (dest < 0) dest += p.world;
           // units of one destination in slice-major order: the first 2 KB of every row go out first, so
           // that the consumer's walk along K can begin after a fraction of the shard has crossed
-          for (int u = gw; u < units_per_dest; u += gw_step) {
+          for (int u = cta_id; u < units_per_dest; u += num_ctas) {
             const int ks = u / (push_chunks * kAgUnitsPerSlice);
             const int rem = u - ks * (push_chunks * kAgUnitsPerSlice);
             const int chunk = rem / kAgUnitsPerSlice;
@@ -958,31 +957,26 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             const int nrows = imin(kAgUnitRows, p.seg_rows - r0);  // 0 for a unit past the shard's last row: it still signals
             const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
             const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
-            const uint8_t* src = p.ag_src + static_cast<long long>(r0) * p.ag_row_bytes + b0 + lane * 16;
-            uint8_t* dst = p.ag_dst[dest] + (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0 + lane * 16;
+            if (ctid * 16 < slice_bytes) {
+              const uint8_t* src = p.ag_src + static_cast<long long>(r0) * p.ag_row_bytes + b0 + ctid * 16;
+              uint8_t* dst = p.ag_dst[dest] + (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0 + ctid * 16;
 #pragma unroll 1
-            for (int rr = 0; rr < nrows; rr += kCommRowsInFlight) {
-              uint4 val[kCommRowsInFlight][4];
+              for (int rr = 0; rr < nrows; rr += 8) {
+                uint4 val[8];
 #pragma unroll
-              for (int j = 0; j < kCommRowsInFlight; ++j)
+                for (int j = 0; j < 8; ++j)
+                  if (rr + j < nrows) val[j] = __ldg(reinterpret_cast<const uint4*>(src + (rr + j) * p.ag_row_bytes));
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  if (rr + j < nrows && q * 512 + lane * 16 < slice_bytes)
-                    val[j][q] = __ldg(reinterpret_cast<const uint4*>(src + (rr + j) * p.ag_row_bytes + q * 512));
-#pragma unroll
-              for (int j = 0; j < kCommRowsInFlight; ++j)
-#pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  if (rr + j < nrows && q * 512 + lane * 16 < slice_bytes)
-                    *reinterpret_cast<uint4*>(dst + (rr + j) * p.ag_row_bytes + q * 512) = val[j][q];
+                for (int j = 0; j < 8; ++j)
+                  if (rr + j < nrows) *reinterpret_cast<uint4*>(dst + (rr + j) * p.ag_row_bytes) = val[j];
+              }
             }
-            if (ks == 0 && p.ag_src_scale != nullptr && lane < nrows)
-              p.ag_dst_scale[dest][static_cast<long long>(p.rank) * p.seg_rows + r0 + lane] = p.ag_src_scale[r0 + lane];
-            __syncwarp();
-            if (lane == 0) {
-              fence_acq_rel_sys();
+            if (ks == 0 && p.ag_src_scale != nullptr && ctid < nrows)
+              p.ag_dst_scale[dest][static_cast<long long>(p.rank) * p.seg_rows + r0 + ctid] = p.ag_src_scale[r0 + ctid];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // the release covers every thread's stores (ordered before it by the barrier)
+            if (ctid == 0)
               red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk * p.ag_groups + ks / p.ag_spf, 1);
-            }
           }
         }
         if (p.g_sorted != nullptr) {
@@ -992,21 +986,22 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           int src_rank = p.rank + d;
           if (src_rank >= p.world) src_rank -= p.world;
           const long long tok0 = static_cast<long long>(src_rank) * p.g_rows_per_rank;
-          for (int u = gw; comm_ok && u < units_per_src; u += gw_step) {
+          for (int u = cta_id; comm_ok && u < units_per_src; u += num_ctas) {
             const int ks = u / (perm_chunks * kAgUnitsPerSlice);
             const int rem = u - ks * (perm_chunks * kAgUnitsPerSlice);
             const int chunk = rem / kAgUnitsPerSlice;
             const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.g_rows_per_rank);
             const int nrows = imin(kAgUnitRows, p.g_rows_per_rank - r0);
             if (p.ag_flags != nullptr) {
-              int okp = 1;
-              if (lane == 0) {
+              if (ctid == 0) {
                 const int grp = ks / p.ag_spf;
                 const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
-                okp = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk * p.ag_groups + grp,
-                                   kAgUnitsPerSlice * in_group, ab, kStatusTimeoutFlag, budget) ? 1 : 0;
+                *s_flag = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk * p.ag_groups + grp,
+                                       kAgUnitsPerSlice * in_group, ab, kStatusTimeoutFlag, budget) ? 1 : 0;
               }
-              okp = __shfl_sync(0xffffffffu, okp, 0);
+              asm volatile("bar.sync 1, 128;" ::: "memory");
+              const int okp = *s_flag;
+              asm volatile("bar.sync 1, 128;" ::: "memory");
               if (!okp) {
                 comm_ok = false;
                 break;
@@ -1014,36 +1009,29 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             }
             const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
             const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
-            const uint8_t* s0 = p.g_tokens + (tok0 + r0) * p.ag_row_bytes + b0 + lane * 16;
-            uint8_t* d0 = p.g_sorted + b0 + lane * 16;
-            const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
+            if (ctid * 16 < slice_bytes) {
+              const uint8_t* s0 = p.g_tokens + (tok0 + r0) * p.ag_row_bytes + b0 + ctid * 16;
+              uint8_t* d0 = p.g_sorted + b0 + ctid * 16;
+              const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
 #pragma unroll 1
-            for (int rr = 0; rr < nrows; rr += kCommRowsInFlight) {
-              uint4 val[kCommRowsInFlight][4];
+              for (int rr = 0; rr < nrows; rr += 8) {
+                uint4 val[8];
 #pragma unroll
-              for (int j = 0; j < kCommRowsInFlight; ++j)
+                for (int j = 0; j < 8; ++j)
+                  if (rr + j < nrows) val[j] = *reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes);
 #pragma unroll
-                for (int q = 0; q < 4; ++q)
-                  if (rr + j < nrows && q * 512 + lane * 16 < slice_bytes)
-                    val[j][q] = *reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes + q * 512);
-#pragma unroll
-              for (int j = 0; j < kCommRowsInFlight; ++j)
-                if (rr + j < nrows)
-                  for (int k = 0; k < p.g_topk; ++k) {
-                    const long long drow = si[(rr + j) * p.g_topk + k];
-                    if (drow >= 0 && drow < p.M) {  // a corrupt routing entry must not become a wild store
-#pragma unroll
-                      for (int q = 0; q < 4; ++q)
-                        if (q * 512 + lane * 16 < slice_bytes)
-                          *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes + q * 512) = val[j][q];
+                for (int j = 0; j < 8; ++j)
+                  if (rr + j < nrows)
+                    for (int k = 0; k < p.g_topk; ++k) {
+                      const long long drow = si[(rr + j) * p.g_topk + k];
+                      if (drow >= 0 && drow < p.M)  // a corrupt routing entry must not become a wild store
+                        *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
                     }
-                  }
+              }
             }
-            __syncwarp();
-            if (lane == 0) {
-              __threadfence();
-              red_add_release_sys(p.g_perm_done + src_rank, 1);
-            }
+            __threadfence();
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ctid == 0) red_add_release_sys(p.g_perm_done + src_rank, 1);
           }
         }
       }

@@ -2,6 +2,8 @@
 // GEMM entry point, AG-GEMM and GEMM-RS (with the owner-side fp32 reduction).
 #include <string.h>
 
+#include <vector>
+
 #include "internal.h"
 
 namespace fluxb {
@@ -79,6 +81,73 @@ int ag_slices_per_flag(long long row_bytes) {
   const long long nslices = (row_bytes + kCommSliceBytes - 1) / kCommSliceBytes;
   const long long spf = (nslices + kAgMaxGroups - 1) / kAgMaxGroups;
   return spf < 1 ? 1 : static_cast<int>(spf);
+}
+
+int resolve_ag_mode(const fluxb_tuning* tuning) {
+  if (tuning != nullptr && (tuning->ag_mode == kAgModeKernelPush || tuning->ag_mode == kAgModeCopyEngine))
+    return tuning->ag_mode;
+  return kAgModeCopyEngine;
+}
+
+int ag_dma_create(AgDma* d, int flag_stride) {
+  int lo = 0, hi = 0;
+  FLUXB_CUDA(cudaDeviceGetStreamPriorityRange(&lo, &hi));
+  FLUXB_CUDA(cudaStreamCreateWithPriority(&d->side, cudaStreamNonBlocking, hi));
+  FLUXB_CUDA(cudaEventCreateWithFlags(&d->ev_start, cudaEventDisableTiming));
+  FLUXB_CUDA(cudaEventCreateWithFlags(&d->ev_done, cudaEventDisableTiming));
+  FLUXB_CUDA(cudaMalloc(reinterpret_cast<void**>(&d->expected_dev), static_cast<size_t>(flag_stride) * sizeof(int)));
+  d->flag_stride = flag_stride;
+  d->expected_row_bytes = -1;
+  return FLUXB_OK;
+}
+
+void ag_dma_destroy(AgDma* d) {
+  if (d->side != nullptr) cudaStreamDestroy(d->side);
+  if (d->ev_start != nullptr) cudaEventDestroy(d->ev_start);
+  if (d->ev_done != nullptr) cudaEventDestroy(d->ev_done);
+  if (d->expected_dev != nullptr) cudaFree(d->expected_dev);
+  *d = AgDma();
+}
+
+int ag_dma_push(const fluxb_comm* comm, AgDma* d, const void* src, int m_local, long long row_bytes,
+                uint8_t* const* gather, int* const* flags, const float* src_scale, float* const* dst_scale,
+                bool include_self, cudaStream_t main) {
+  const int world = comm->world, rank = comm->rank;
+  if (d->expected_row_bytes != row_bytes) {
+    // counter values of a complete shard: every used slice group of every chunk holds its unit count
+    const int nslices = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+    const int spf = ag_slices_per_flag(row_bytes);
+    std::vector<int> v(static_cast<size_t>(d->flag_stride), 0);
+    for (int i = 0; i < d->flag_stride; ++i) {
+      const int g = i % kAgMaxGroups;
+      const int left = nslices - g * spf;
+      if (left > 0) v[i] = kAgUnitsPerSlice * (left < spf ? left : spf);
+    }
+    FLUXB_CUDA(cudaMemcpy(d->expected_dev, v.data(), v.size() * sizeof(int), cudaMemcpyHostToDevice));
+    d->expected_row_bytes = row_bytes;
+  }
+  FLUXB_CUDA(cudaEventRecord(d->ev_start, main));
+  FLUXB_CUDA(cudaStreamWaitEvent(d->side, d->ev_start, 0));
+  const int piece = 2 * kBM;
+  for (int dd = include_self ? 0 : 1; dd < world; ++dd) {
+    const int dest = (rank - dd + world) % world;
+    for (int r0 = 0; r0 < m_local; r0 += piece) {
+      const int rows = m_local - r0 < piece ? m_local - r0 : piece;
+      const size_t row_off = static_cast<size_t>(rank) * m_local + r0;
+      FLUXB_CUDA(cudaMemcpyAsync(gather[dest] + row_off * row_bytes, static_cast<const uint8_t*>(src) + static_cast<size_t>(r0) * row_bytes,
+                                 static_cast<size_t>(rows) * row_bytes, cudaMemcpyDeviceToDevice, d->side));
+      if (src_scale != nullptr)
+        FLUXB_CUDA(cudaMemcpyAsync(dst_scale[dest] + row_off, src_scale + r0, static_cast<size_t>(rows) * sizeof(float),
+                                   cudaMemcpyDeviceToDevice, d->side));
+      // the piece's chunks are complete: publish their counters (stream order puts this after the data)
+      const int c0 = r0 / kBM, c1 = (r0 + rows + kBM - 1) / kBM;
+      FLUXB_CUDA(cudaMemcpyAsync(flags[dest] + static_cast<size_t>(rank) * d->flag_stride + static_cast<size_t>(c0) * kAgMaxGroups,
+                                 d->expected_dev + static_cast<size_t>(c0) * kAgMaxGroups,
+                                 static_cast<size_t>(c1 - c0) * kAgMaxGroups * sizeof(int), cudaMemcpyDeviceToDevice, d->side));
+    }
+  }
+  FLUXB_CUDA(cudaEventRecord(d->ev_done, d->side));
+  return FLUXB_OK;
 }
 
 int resolve_cta_group(const GemmParams& p, const fluxb_tuning* tuning) {
@@ -224,6 +293,7 @@ struct fluxb_ag_gemm {
   float* scales[kMaxWorld];
   bool has_scales;
   unsigned long long calls;
+  AgDma dma;
 };
 
 struct fluxb_gemm_rs {
@@ -276,7 +346,7 @@ int fluxb_gemm(fluxb_comm_t comm, const void* a, const void* b, void* c, int m, 
   if (rc != FLUXB_OK) return rc;
   rc = encode_b(p, b, in_dtype, n, k, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn, flags);
   if (rc != FLUXB_OK) return rc;
-  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   return launch_fused_gemm(comm, p, in_dtype, &t, static_cast<cudaStream_t>(stream));
 }
@@ -303,7 +373,7 @@ int fluxb_ag_gemm_create(fluxb_comm_t comm, int full_m, int n_dim, int k_dim, in
   rc = out_type_of(out_dtype, &ot);
   if (rc != FLUXB_OK) return rc;
   fluxb_ag_gemm* op = new fluxb_ag_gemm();
-  memset(op, 0, sizeof(*op));
+  op->calls = 0;
   op->comm = comm;
   op->full_m = full_m;
   op->n_dim = n_dim;
@@ -322,11 +392,20 @@ int fluxb_ag_gemm_create(fluxb_comm_t comm, int full_m, int n_dim, int k_dim, in
     op->flags[r] = flag_bufs[r];
     op->scales[r] = scale_bufs != nullptr ? scale_bufs[r] : nullptr;
   }
+  if (comm->world > 1) {
+    rc = ag_dma_create(&op->dma, op->flag_stride);
+    if (rc != FLUXB_OK) {
+      ag_dma_destroy(&op->dma);
+      delete op;
+      return rc;
+    }
+  }
   *out = op;
   return FLUXB_OK;
 }
 
 int fluxb_ag_gemm_destroy(fluxb_ag_gemm_t op) {
+  if (op != nullptr) ag_dma_destroy(&op->dma);
   delete op;
   return FLUXB_OK;
 }
@@ -409,6 +488,25 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
     p.ag_dst_scale[r] = op->has_scales ? op->scales[r] + parity * op->full_m : nullptr;
   }
   if (scale_a_shard != nullptr) p.scale_a = op->scales[comm->rank] + parity * op->full_m;
+  const bool dma = resolve_ag_mode(tuning) == kAgModeCopyEngine;
+  if (dma) {
+    // the copy engines carry the shard to the peers; the kernel's comm warps have nothing to push
+    uint8_t* gather_p[kMaxWorld];
+    int* flags_p[kMaxWorld];
+    float* scale_p[kMaxWorld];
+    for (int r = 0; r < world; ++r) {
+      gather_p[r] = p.ag_dst[r];
+      flags_p[r] = p.ag_dst_flags[r];
+      scale_p[r] = p.ag_dst_scale[r];
+    }
+    if (scale_a_shard != nullptr)  // this rank's own rows of the gathered scale vector
+      FLUXB_CUDA(cudaMemcpyAsync(scale_p[comm->rank] + static_cast<size_t>(comm->rank) * m_local, scale_a_shard,
+                                 static_cast<size_t>(m_local) * sizeof(float), cudaMemcpyDeviceToDevice, stream));
+    rc = ag_dma_push(comm, &op->dma, a_shard, m_local, row_bytes, gather_p, flags_p, scale_a_shard, scale_p, false, stream);
+    if (rc != FLUXB_OK) return rc;
+    p.ag_src = nullptr;
+    p.ag_src_scale = nullptr;
+  }
   p.b_mn_major = (flags & FLUXB_WEIGHT_KN) ? 1 : 0;
   if (tuning == nullptr || tuning->group_m <= 0) {
     // own shard first, then bands that double (1, 2, 4 shards ...) so that tiles follow the arrival order
@@ -423,16 +521,18 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   if (rc != FLUXB_OK) return rc;
   rc = encode_tmap_2d(&p.tmap_a_own, a_shard, op->in_dtype, m_local, k, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
-  // per-row scales travel through the scale buffer under the same flags as the data: keep the
-  // flagged path for the own shard too in that case
-  p.a_own_valid = scale_a_shard == nullptr ? 1 : 0;
+  // kernel push: per-row scales travel through the scale buffer under the same flags as the data, so the
+  // own shard takes the flagged path too in that case (the copy-engine form has put the own scales in place)
+  p.a_own_valid = (scale_a_shard == nullptr || dma) ? 1 : 0;
   rc = encode_b(p, b, op->in_dtype, n, k, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn, flags);
   if (rc != FLUXB_OK) return rc;
-  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;
   op->calls += 1;
+  // the caller's tensor and this call's counters stay in use until the copies are done
+  if (dma) FLUXB_CUDA(cudaStreamWaitEvent(stream, op->dma.ev_done, 0));
   if (gathered_out != nullptr) {
     // peers' shards come from the gather buffer, this rank's own shard from the caller's tensor
     const size_t all_bytes = static_cast<size_t>(m) * row_bytes, own_bytes = static_cast<size_t>(m_local) * row_bytes;
@@ -577,7 +677,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   if (rc != FLUXB_OK) return rc;
   rc = encode_b(p, b, op->in_dtype, n, k_local, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn, flags);
   if (rc != FLUXB_OK) return rc;
-  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   // the owner-side reduction runs in the same kernel (comm warps)
   p.rs_local_stage = op->stage[comm->rank] + parity * half_stage;

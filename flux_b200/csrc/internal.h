@@ -110,6 +110,32 @@ int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tun
 // 2 KB slices of a row that share one arrival counter (1 unless the row has more than kAgMaxGroups slices)
 int ag_slices_per_flag(long long row_bytes);
 
+// All-gather carried by the copy engines instead of the kernel's comm warps: a side stream copies this rank's
+// shard into every peer's gather buffer, piece by piece (256 rows), in the order the peers consume it
+// (rank-1 first), and after each piece copies the piece's expected counter values into the peer's arrival
+// counters, so the consuming kernel cannot tell the two transports apart. This is the reference's default
+// transport (cudaMemcpyAsync per peer + flag writes, src/coll/ths_op/all_gather_op.cc:529-574).
+struct AgDma {
+  cudaStream_t side = nullptr;
+  cudaEvent_t ev_start = nullptr, ev_done = nullptr;
+  int* expected_dev = nullptr;       // [flag_stride] counter values of a complete shard for `expected_row_bytes`
+  long long expected_row_bytes = -1;
+  int flag_stride = 0;
+};
+int ag_dma_create(AgDma* d, int flag_stride);
+void ag_dma_destroy(AgDma* d);
+// Queue the copies (after everything already on `main`) and record d->ev_done behind them; the caller launches
+// its kernel on `main` and then makes `main` wait for d->ev_done. `gather` / `flags` / `dst_scale` are the
+// per-rank bases of the buffer parity in use.
+// `include_self`: also copy the shard into this rank's own gather buffer (consumers that read every shard from
+// the buffer), before the peers'.
+int ag_dma_push(const fluxb_comm* comm, AgDma* d, const void* src, int m_local, long long row_bytes,
+                uint8_t* const* gather, int* const* flags, const float* src_scale, float* const* dst_scale,
+                bool include_self, cudaStream_t main);
+
+enum : int { kAgModeDefault = 0, kAgModeKernelPush = 1, kAgModeCopyEngine = 2 };
+int resolve_ag_mode(const fluxb_tuning* tuning);
+
 // 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile (the caller's choice or a heuristic).
 int resolve_cta_group(const GemmParams& p, const fluxb_tuning* tuning);
 

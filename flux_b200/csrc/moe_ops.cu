@@ -264,6 +264,7 @@ struct fluxb_moe_ag_scatter {
   unsigned long long calls;
   int last_parity;      // parity of the buffers the last push filled
   int last_ntokens;     // tokens gathered by the last push
+  AgDma dma;
 };
 
 struct fluxb_moe_gather_rs {
@@ -306,7 +307,7 @@ int fluxb_moe_ag_scatter_create(fluxb_comm_t comm, int max_ntokens, int hidden, 
   FLUXB_REQUIRE((static_cast<long long>(hidden) * dtype_bytes(in_dtype)) % 16 == 0,
                 "moe_ag_scatter_create: hidden=%d gives a row pitch that is not a multiple of 16 bytes", hidden);
   fluxb_moe_ag_scatter* op = new fluxb_moe_ag_scatter();
-  memset(op, 0, sizeof(*op));
+  op->calls = 0;
   op->comm = comm;
   op->max_ntokens = max_ntokens;
   op->hidden = hidden;
@@ -326,11 +327,20 @@ int fluxb_moe_ag_scatter_create(fluxb_comm_t comm, int max_ntokens, int hidden, 
     op->gather[r] = static_cast<uint8_t*>(gather_bufs[r]);
     op->flags[r] = flag_bufs[r];
   }
+  if (comm->world > 1) {
+    int rc = ag_dma_create(&op->dma, op->flag_stride);
+    if (rc != FLUXB_OK) {
+      ag_dma_destroy(&op->dma);
+      delete op;
+      return rc;
+    }
+  }
   *out = op;
   return FLUXB_OK;
 }
 
 int fluxb_moe_ag_scatter_destroy(fluxb_moe_ag_scatter_t op) {
+  if (op != nullptr) ag_dma_destroy(&op->dma);
   delete op;
   return FLUXB_OK;
 }
@@ -388,6 +398,7 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
 
   const size_t half_gather = (static_cast<size_t>(op->max_ntokens) + kBM) * op->hidden * eb;
   const size_t half_flags = static_cast<size_t>(world) * op->flag_stride;
+  bool dma = false;
   int parity;
   if (reuse) {
     parity = op->last_parity;
@@ -439,6 +450,15 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
       p.ag_dst[r] = op->gather[r] + parity * half_gather;
       p.ag_dst_flags[r] = op->flags[r] + parity * half_flags;
     }
+    if (resolve_ag_mode(tuning) == kAgModeCopyEngine) {
+      // the copy engines carry the tokens (this rank's own ones included: the permute reads every source
+      // from the gather buffer); the comm warps only permute what arrives
+      dma = true;
+      int rc2 = ag_dma_push(comm, &op->dma, tokens_shard, ntokens_local, row_bytes, p.ag_dst, p.ag_dst_flags, nullptr, nullptr,
+                            true, stream);
+      if (rc2 != FLUXB_OK) return rc2;
+      p.ag_src = nullptr;
+    }
   }
   const int bn = resolve_block_n(comm, p, tuning, max_tiles);
   int rc = encode_tmap_2d(&p.tmap_a, p.g_sorted, op->in_dtype, rows, op->hidden, row_bytes, kBM);
@@ -446,11 +466,12 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * op->ffn_local,
                       op->hidden, row_bytes, cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
-  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   t.cta_group = cg;
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;
+  if (dma) FLUXB_CUDA(cudaStreamWaitEvent(stream, op->dma.ev_done, 0));
   if (!reuse) {
     if (world == 1) {
       // keep a copy so that further weight groups and `gathered_out` see the same tokens
@@ -608,7 +629,7 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * n, k_local, row_bytes,
                       cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
-  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   t.cta_group = cg;
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
@@ -769,7 +790,7 @@ extern "C" int fluxb_moe_scatter_gemm_static(fluxb_comm_t comm, const void* toke
   rc = encode_tmap_2d(&p.tmap_b, weights, in_dtype, static_cast<long long>(nexperts) * ffn, hidden, row_bytes,
                       cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
-  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0};
+  fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   t.cta_group = cg;
   return launch_fused_gemm(comm, p, in_dtype, &t, stream);

@@ -42,7 +42,7 @@ def _tuning(t) -> Optional[C.Array]:
         return None
     if isinstance(t, _lib.Tuning):
         return C.byref(t)
-    return C.byref(_lib.Tuning(int(t.get("block_n", 0)), int(t.get("group_m", 0)), int(t.get("num_ctas", 0)), int(t.get("cta_group", 0))))
+    return C.byref(_lib.make_tuning(t))
 
 
 class AGRingMode(enum.IntEnum):
@@ -62,9 +62,10 @@ class RingMode(enum.IntEnum):
 
 
 class AllGatherOption:
-    """All fields optional (src/coll/ths_op/all_gather_types.h:35-43). On an NVSwitch domain the
-    transfer is always an all-to-all push from the fused kernel; the PCIe-oriented knobs are
-    accepted and ignored."""
+    """All fields optional (src/coll/ths_op/all_gather_types.h:35-43). `use_cuda_core_ag` chooses the transport
+    of the all-gather as in the reference: True = pushed by the communication warps of the fused kernel, False =
+    copy engines on a side stream, None = the library's default. On an NVSwitch domain the transfer is always a
+    direct all-to-all; the PCIe-oriented knobs (ring modes, `use_read`) are accepted and ignored."""
 
     def __init__(self):
         self.input_buffer_copied = None
@@ -265,6 +266,9 @@ class AGKernel:
                    and gathered_input.is_contiguous(), "AGKernel: gathered_input has the wrong shape, dtype or layout")
         if tuning is None and _tune.TABLE.records:
             tuning = _tune.TABLE.get(_tune.record_key("ag_gemm", m_local * w, n, k, self.input_dtype, w))
+        if all_gather_option is not None and all_gather_option.use_cuda_core_ag is not None:
+            tuning = dict(tuning) if isinstance(tuning, dict) else {}
+            tuning["ag_mode"] = _lib.AG_MODE_KERNEL_PUSH if all_gather_option.use_cuda_core_ag else _lib.AG_MODE_COPY_ENGINE
         lib = _lib.load()
         _lib.check(
             lib.fluxb_ag_gemm_forward(

@@ -31,6 +31,9 @@ DEFAULT_CANDIDATES: Tuple[Tuning, ...] = (
     {"block_n": 256, "cta_group": 1},
     {"block_n": 192, "cta_group": 1},
     {"block_n": 128, "cta_group": 1},
+    # transport of the all-gather (ignored by ops without one): kernel push / copy engines
+    {"ag_mode": 1},
+    {"ag_mode": 2},
 )
 
 

@@ -72,7 +72,7 @@ class Ranks:
                         gathered=None, tuning=None, flags=0):
         m_local, k = shards[0].shape
         n = weights[0].shape[1] if flags & _lib.WEIGHT_KN else weights[0].shape[0]
-        tun = C.byref(_lib.Tuning(*[int(tuning.get(f, 0)) for f in ("block_n", "group_m", "num_ctas", "cta_group")])) if tuning else None
+        tun = C.byref(_lib.make_tuning(tuning)) if tuning else None
         for r in range(self.n):
             _lib.check(self.lib.fluxb_ag_gemm_forward(
                 ops[r], _p(shards[r]), m_local, _p(weights[r]), n, k, _p(outs[r]),
@@ -96,7 +96,7 @@ class Ranks:
     def gemm_rs_forward(self, ops, inputs, weights, outs, biases=None, scales_a=None, scales_b=None, flags=0, tuning=None):
         m, k_local = inputs[0].shape
         n = weights[0].shape[0]
-        tun = C.byref(_lib.Tuning(*[int(tuning.get(f, 0)) for f in ("block_n", "group_m", "num_ctas", "cta_group")])) if tuning else None
+        tun = C.byref(_lib.make_tuning(tuning)) if tuning else None
         for r in range(self.n):
             _lib.check(self.lib.fluxb_gemm_rs_forward(
                 ops[r], _p(inputs[r]), _p(weights[r]), m, n, k_local, _p(outs[r]),
@@ -128,12 +128,14 @@ class Ranks:
             l1.append(h1)
         return l0, l1
 
-    def moe_l0_forward(self, ops, tokens, weights, splits_dev, scatter_index, outs, out_scales=None, gathered=None):
+    def moe_l0_forward(self, ops, tokens, weights, splits_dev, scatter_index, outs, out_scales=None, gathered=None,
+                       tuning=None):
         nlocal = tokens[0].shape[0]
+        tun = C.byref(_lib.make_tuning(tuning)) if tuning else None
         for r in range(self.n):
             _lib.check(self.lib.fluxb_moe_ag_scatter_forward(
                 ops[r], _p(tokens[r]), nlocal, _p(weights[r]), _p(splits_dev), _p(scatter_index),
-                _p(out_scales[r]) if out_scales else None, _p(outs[r]), _p(gathered[r]) if gathered else None, None, _stream()))
+                _p(out_scales[r]) if out_scales else None, _p(outs[r]), _p(gathered[r]) if gathered else None, tun, _stream()))
         self.run()
 
     def moe_l1_forward(self, ops, xs, weights, splits_cpu, routing_idx, outs, vec_scale=None):

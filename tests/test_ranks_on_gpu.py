@@ -35,8 +35,10 @@ def _cpu_inputs(rank, rows, n, k, dtype, seed):
     return a, b
 
 
+# transport of the all-gather: 1 = pushed by the kernel's communication warps, 2 = copy engines
+@pytest.mark.parametrize("ag_mode", [1, 2])
 @pytest.mark.parametrize("world", [2, 4, 8])
-def test_ag_gemm_all_ranks_on_one_gpu(world):
+def test_ag_gemm_all_ranks_on_one_gpu(world, ag_mode):
     shapes = [(256, 512, 512), (200, 264, 512), (128, 136, 512), (256, 512, 512), (37, 72, 512)]
     rk = Ranks(world)
     try:
@@ -52,7 +54,7 @@ def test_ag_gemm_all_ranks_on_one_gpu(world):
             gathered = [torch.empty((m_local * world, k), dtype=BF16, device="cuda") for _ in range(world)]
             rk.ag_gemm_forward(ops, [a.cuda() for a in shards], [b.cuda() for _, b in ab], outs,
                                biases=[b.cuda() for b in biases] if biases else None,
-                               bias_mode=1 if biases else 0, gathered=gathered)
+                               bias_mode=1 if biases else 0, gathered=gathered, tuning={"ag_mode": ag_mode})
             for r in range(world):
                 ref, ref_g = golden.ag_gemm_single(shards, ab[r][1], bias=biases[r] if biases else None)
                 _close(outs[r], ref, 1e-2, 1e-2, f"AG-GEMM world {world} call {it} rank {r}")
@@ -88,7 +90,8 @@ def test_gemm_rs_all_ranks_on_one_gpu(world, fp32_wire):
         rk.close()
 
 
-def test_fp8_all_ranks_on_one_gpu():
+@pytest.mark.parametrize("ag_mode", [1, 2])
+def test_fp8_all_ranks_on_one_gpu(ag_mode):
     world, m_local, n, k = 4, 256, 392, 1024
     f8 = torch.float8_e4m3fn
     rk = Ranks(world)
@@ -104,7 +107,8 @@ def test_fp8_all_ranks_on_one_gpu():
         outs = [torch.empty((m_local * world, n), dtype=BF16, device="cuda") for _ in range(world)]
         for _ in range(2):  # both buffer parities
             rk.ag_gemm_forward(ops, [q.cuda() for q in qa], [q.cuda() for q in qb], outs,
-                               scales_a=[s.cuda() for s in sa], scales_b=[s.cuda() for s in sb])
+                               scales_a=[s.cuda() for s in sa], scales_b=[s.cuda() for s in sb],
+                               tuning={"ag_mode": ag_mode})
             for r in range(world):
                 ref, _ = golden.ag_gemm_single(qa, qb[r], input_scales=sa, weight_scale=sb[r])
                 _close(outs[r], ref, 3e-2, 3e-2, f"fp8 AG-GEMM rank {r}")
@@ -126,8 +130,9 @@ def test_fp8_all_ranks_on_one_gpu():
         rk.close()
 
 
+@pytest.mark.parametrize("ag_mode", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
-def test_moe_all_ranks_on_one_gpu(world):
+def test_moe_all_ranks_on_one_gpu(world, ag_mode):
     ntokens, topk, nexperts, hidden, ffn = 128 * world, 2, 4, 256, 128 * world
     ffn_local = ffn // world
     rk = Ranks(world)
@@ -152,7 +157,7 @@ def test_moe_all_ranks_on_one_gpu(world):
             out0 = [torch.empty((ntokens * topk, ffn_local), dtype=BF16, device="cuda") for _ in range(world)]
             gathered = [torch.empty((ntokens, hidden), dtype=BF16, device="cuda") for _ in range(world)]
             rk.moe_l0_forward(l0, [t.cuda() for t in toks], [w.cuda() for w in w0s], splits.cuda(), si.cuda(), out0,
-                              out_scales=[oscale.cuda()] * world, gathered=gathered)
+                              out_scales=[oscale.cuda()] * world, gathered=gathered, tuning={"ag_mode": ag_mode})
             ref0 = []
             for r in range(world):
                 ref, ref_g = golden.moe_ag_scatter_single(toks, w0s[r], splits, si, oscale)
@@ -205,8 +210,10 @@ def test_dense_baseline_shapes_tp8_on_one_gpu():
         rows_l, cols = _spread(m_local, 8), _spread(n_local, 16)
         grows = (torch.arange(world, device="cuda")[:, None] * m_local + rows_l[None, :]).reshape(-1)
         a_rows = torch.cat([s[rows_l] for s in shards]).double()
-        for call in range(2):
-            rk.ag_gemm_forward(ops, shards, b0, c0)
+        for call in range(2):  # all-gather pushed by the kernel, then carried by the copy engines
+            for t in c0:
+                t.zero_()
+            rk.ag_gemm_forward(ops, shards, b0, c0, tuning={"ag_mode": 1 + call})
             for r in range(world):
                 _cmp64(c0[r][grows][:, cols], a_rows @ b0[r][cols].double().t(), 1e-2, 1e-2, f"D0 call {call} rank {r}")
         del ops, b0
