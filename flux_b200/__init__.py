@@ -19,6 +19,8 @@ from .ops import (
     MoeArguments,
     ProfilingContext,
     ReduceScatterOption,
+    TuningRecord,
+    load_tuning_record,
     RingMode,
     bitwise_check,
     is_fp8_dtype,
@@ -36,6 +38,6 @@ __all__ = [
     "ProfilingContext", "ReduceScatterOption", "RingMode", "bitwise_check", "is_fp8_dtype", "uniform_initialize",
     "GroupBarrier", "flux_create_tensor_list", "create_tensor_list", "get_comm", "init_flux_shm", "bench_func",
     "get_arch", "group_profile", "GemmGroupedV3AGScatter", "GemmGroupedV3GatherRS", "calc_scatter_index",
-    "calc_gather_index", "default_comm", "torch_allclose", "with_torch_deterministic", "FluxbError", "Tuning", "util",
+    "calc_gather_index", "default_comm", "torch_allclose", "with_torch_deterministic", "FluxbError", "Tuning", "util", "TuningRecord", "load_tuning_record",
     "layers", "tune", "ColumnParallelLinear", "RowParallelLinear", "TensorParallelMLP", "MoEMLP",
 ]

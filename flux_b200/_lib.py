@@ -109,7 +109,7 @@ SIGNATURES = {
     "fluxb_moe_scatter_gemm_static": (_i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _tun, _vp]),
     "fluxb_moe_gather_rs_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "fluxb_moe_gather_rs_stage_bytes": (_sz, [_i, _i, _i, _i]),
-    "fluxb_moe_gather_rs_cnt_bytes": (_sz, [_i, _i, _i]),
+    "fluxb_moe_gather_rs_cnt_bytes": (_sz, [_i, _i, _i, _i]),
     "fluxb_moe_gather_rs_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _pp, _pp, _vp, _pp]),
     "fluxb_moe_gather_rs_destroy": (_i, [_vp]),
     "fluxb_moe_gather_rs_reset": (_i, [_vp, _vp]),

@@ -48,6 +48,7 @@ constexpr int kMaxWorld = 8;
 constexpr int kCommSliceBytes = 2048;  // bytes of one row handled by one comm unit
 constexpr int kAgUnitRows = 32;        // rows of one all-gather push unit (32 rows x 2 KB by the 128 comm threads)
 constexpr int kAgUnitsPerSlice = kBM / kAgUnitRows;  // units that signal one (128-row chunk, 2 KB slice)
+constexpr int kGrTokBlock = 32;        // tokens per combine / reduce work item of MoE layer 1
 constexpr int kAgMaxGroups = 64;       // arrival counters per (source rank, chunk): one per group of 2 KB slices
 
 enum EpiMode : int {
@@ -135,6 +136,20 @@ struct GemmParams {
   const int* g_scatter_index;     // [tokens, topk]
   const uint8_t* g_tokens;        // gathered tokens [tokens, K] (this rank's gather buffer, or the input at world 1)
   int g_topk;
+  // MoE layer 1: the comm warps combine every token's top-k rows of D column slab by column slab (a slab =
+  // one tile column, BN wide) as soon as all tiles of the slab are stored, push the combined rows (16-bit) to
+  // the token's owner and, on the owner, sum the per-source partials: grouped GEMM, gather and reduce-scatter
+  // in one launch. Tiles are walked slab by slab (one rasterisation band over all M tiles).
+  int* gr_slab_done;             // [n_tiles] one arrival per epilogue warp per tile (local, zeroed per call); null = off
+  int gr_slab_expected;          // arrivals of a complete slab
+  const int* gr_scatter_index;   // [tokens * topk]: row of D that holds (token, k)
+  int gr_topk;
+  int gr_tokens_per_rank;
+  void* gr_stage[kMaxWorld];     // owner o's staging slot of THIS rank: [tokens_per_rank][N], 16-bit
+  int* gr_cnt[kMaxWorld];        // owner o's arrival counters [n_tiles][token blocks]
+  const void* gr_local_stage;    // this rank's staging: [world][tokens_per_rank][N]
+  int* gr_local_cnt;
+  void* gr_out;                  // [tokens_per_rank][N]
   // split-K tail: the tiles of the last, partial wave are split along K over the otherwise idle
   // workers; parts 1.. park their fp32 accumulators here, part 0 adds them before its epilogue
   float* splitk_scratch;  // null = never split
@@ -176,6 +191,7 @@ struct TileCoord {
   int n_idx;
   int need_mask;
   int expert;
+  int band;        // rasterisation band of the tile (explicit bands only, else 0)
 };
 
 __host__ __device__ __forceinline__ int imin(int a, int b) { return a < b ? a : b; }
@@ -211,9 +227,11 @@ __host__ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t,
   // Rasterisation: M tiles are grouped into bands; inside a band consecutive work items walk down the
   // band's M tiles first, then move to the next column block (A band stays in L2, B streams once per band).
   int m_idx, n_idx;
+  tc.band = 0;
   if (p.n_bands > 0) {
     int b = 0;
     while (b + 1 < p.n_bands && t >= p.band_end[b] * n_tiles) ++b;
+    tc.band = b;
     const int m_lo = b > 0 ? p.band_end[b - 1] : 0;
     const int h = p.band_end[b] - m_lo;
     const int r = t - m_lo * n_tiles;
@@ -888,6 +906,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       if (lane == 0) {
         if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
         else mbar_arrive(bar_tempty(acc));
+        // MoE layer 1: this warp's rows of the tile are stored (release covers the whole warp's stores)
+        if (p.gr_slab_done != nullptr) red_add_release_gpu(p.gr_slab_done + tc.n_idx, 1);
       }
       if (p.epi_mode == kEpiRsPush) {
         // Publish the PREVIOUS pushed tile of this warp: its stores were issued a whole tile ago, so
@@ -902,10 +922,14 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             red_add_release_sys(pending_cnt, 1);
           }
           pending_cnt = (!own && tc.rows > 0) ? p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx : nullptr;
-          // Exception: rows of the previous rank are the last ones it is waiting for before it starts its
-          // own tiles (every rank computes its own rows last), so their publish is latency-critical.
+          // Exception: the tiles of the last band of peer-owned rows are the ones their owners are waiting
+          // for when they reach their own rows (every rank computes its own rows last), so their publish is
+          // latency-critical: a tile-time of delay there showed up as 50-75 us of waiting in the owners'
+          // last epilogues on 8 GPUs. The accumulator has been released already, so waiting for these
+          // stores holds up nothing but this warp. (Without explicit bands: the rows of the previous rank.)
           const int prev_rank = p.rank == 0 ? p.nseg - 1 : p.rank - 1;
-          if (pending_cnt != nullptr && tc.seg == prev_rank) {
+          const bool urgent = p.n_bands >= 2 ? tc.band == p.n_bands - 2 : tc.seg == prev_rank;
+          if (pending_cnt != nullptr && urgent) {
             bulk_wait_all();
             fence_acq_rel_sys();
             red_add_release_sys(pending_cnt, 1);
@@ -1035,6 +1059,166 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           }
         }
       }
+    }
+    if (p.gr_slab_done != nullptr) {
+      // MoE layer 1, combine + reduce-scatter. For slab s (in the order the GEMM produces them): wait until
+      // every tile of the slab is stored, then item = (owner, block of 32 of its tokens): sum each token's
+      // top-k rows of the slab in fp32, round, store into the owner's staging slot of this rank and add 1 to
+      // the owner's counter of (slab, block). One slab behind, the owner side: item = (block of this rank's
+      // tokens): wait (bounded) for `world` arrivals, sum the per-source partials in fp32, write the result.
+      // A warp handles 8 tokens of an item, four at a time, one 16-byte column piece per lane.
+      const int ctid = threadIdx.x - 6 * 32;
+      const int cw = ctid >> 5;
+      const int tpr = p.gr_tokens_per_rank;
+      const int bpo = (tpr + kGrTokBlock - 1) / kGrTokBlock;  // token blocks per owner
+      const int osz = 2;                                       // 16-bit staging and output
+      const bool out_bf16 = p.out_type == kOutBf16;
+      volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
+      bool gr_ok = true;
+      for (int slab = 0; gr_ok && slab <= n_tiles; ++slab) {
+        if (slab < n_tiles) {
+          if (ctid == 0)
+            *s_flag = flag_wait_eq(p.gr_slab_done + slab, p.gr_slab_expected, ab, kStatusTimeoutReduce, budget) ? 1 : 0;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          const int oks = *s_flag;
+          asm volatile("bar.sync 1, 128;" ::: "memory");
+          if (!oks) break;
+          const int col0 = slab * BN;
+          const int cols = imin(BN, p.N - col0);
+          const bool lane_on = lane * 8 < cols;
+          const int first = (cta_id + slab * 61) % num_ctas;  // rotate, so that slabs do not load the same CTAs
+          for (int item = first; item < p.world * bpo; item += num_ctas) {
+            const int oi = item / bpo;
+            const int blk = item - oi * bpo;
+            int owner = p.rank + 1 + oi;
+            while (owner >= p.world) owner -= p.world;
+            uint16_t* dst = static_cast<uint16_t*>(p.gr_stage[owner]);
+#pragma unroll 1
+            for (int b4 = 0; b4 < 8; b4 += 4) {
+              float acc4[4][8];
+              int tl[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                tl[j] = blk * kGrTokBlock + cw * 8 + b4 + j;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc4[j][e] = 0.f;
+              }
+              for (int k = 0; k < p.gr_topk; ++k) {
+                uint4 raw[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  raw[j] = make_uint4(0u, 0u, 0u, 0u);
+                  if (tl[j] < tpr && lane_on) {
+                    const int row = p.gr_scatter_index[(static_cast<long long>(owner) * tpr + tl[j]) * p.gr_topk + k];
+                    if (row >= 0 && row < p.M)  // a corrupt routing entry must not become a wild load
+                      raw[j] = ld_relaxed_gpu_v4(static_cast<const uint16_t*>(p.out) + static_cast<long long>(row) * p.ldo + col0 + lane * 8);
+                  }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (out_bf16) {
+                      acc4[j][2 * e] += __uint_as_float(w[e] << 16);
+                      acc4[j][2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+                    } else {
+                      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                      acc4[j][2 * e] += f.x;
+                      acc4[j][2 * e + 1] += f.y;
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (tl[j] < tpr && lane_on) {
+                  uint4 o;
+                  if (out_bf16) {
+                    o = make_uint4(pack_bf16(acc4[j][0], acc4[j][1]), pack_bf16(acc4[j][2], acc4[j][3]),
+                                   pack_bf16(acc4[j][4], acc4[j][5]), pack_bf16(acc4[j][6], acc4[j][7]));
+                  } else {
+                    o = make_uint4(pack_f16(acc4[j][0], acc4[j][1]), pack_f16(acc4[j][2], acc4[j][3]),
+                                   pack_f16(acc4[j][4], acc4[j][5]), pack_f16(acc4[j][6], acc4[j][7]));
+                  }
+                  *reinterpret_cast<uint4*>(dst + static_cast<long long>(tl[j]) * p.N + col0 + lane * 8) = o;
+                }
+            }
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (ctid == 0) red_add_release_sys(p.gr_cnt[owner] + slab * bpo + blk, 1);
+          }
+        }
+        if (slab >= 1) {
+          const int rs = slab - 1;
+          const int col0 = rs * BN;
+          const int cols = imin(BN, p.N - col0);
+          const bool lane_on = lane * 8 < cols;
+          const long long slot = static_cast<long long>(tpr) * p.N;
+          const int first = (cta_id + rs * 61) % num_ctas;
+          for (int blk = first; gr_ok && blk < bpo; blk += num_ctas) {
+            if (ctid == 0)
+              *s_flag = flag_wait_eq(p.gr_local_cnt + rs * bpo + blk, p.world, ab, kStatusTimeoutReduce, budget) ? 1 : 0;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            const int okr = *s_flag;
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            if (!okr) {
+              gr_ok = false;
+              break;
+            }
+#pragma unroll 1
+            for (int b4 = 0; b4 < 8; b4 += 4) {
+              float acc4[4][8];
+              int tl[4];
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                tl[j] = blk * kGrTokBlock + cw * 8 + b4 + j;
+#pragma unroll
+                for (int e = 0; e < 8; ++e) acc4[j][e] = 0.f;
+              }
+              for (int sr = 0; sr < p.world; ++sr) {
+                uint4 raw[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  raw[j] = make_uint4(0u, 0u, 0u, 0u);
+                  if (tl[j] < tpr && lane_on)
+                    raw[j] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.gr_local_stage) + sr * slot +
+                                                             static_cast<long long>(tl[j]) * p.N + col0 + lane * 8);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
+#pragma unroll
+                  for (int e = 0; e < 4; ++e) {
+                    if (out_bf16) {
+                      acc4[j][2 * e] += __uint_as_float(w[e] << 16);
+                      acc4[j][2 * e + 1] += __uint_as_float(w[e] & 0xFFFF0000u);
+                    } else {
+                      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[e]));
+                      acc4[j][2 * e] += f.x;
+                      acc4[j][2 * e + 1] += f.y;
+                    }
+                  }
+                }
+              }
+#pragma unroll
+              for (int j = 0; j < 4; ++j)
+                if (tl[j] < tpr && lane_on) {
+                  uint4 o;
+                  if (out_bf16) {
+                    o = make_uint4(pack_bf16(acc4[j][0], acc4[j][1]), pack_bf16(acc4[j][2], acc4[j][3]),
+                                   pack_bf16(acc4[j][4], acc4[j][5]), pack_bf16(acc4[j][6], acc4[j][7]));
+                  } else {
+                    o = make_uint4(pack_f16(acc4[j][0], acc4[j][1]), pack_f16(acc4[j][2], acc4[j][3]),
+                                   pack_f16(acc4[j][4], acc4[j][5]), pack_f16(acc4[j][6], acc4[j][7]));
+                  }
+                  *reinterpret_cast<uint4*>(static_cast<uint16_t*>(p.gr_out) + static_cast<long long>(tl[j]) * p.N + col0 +
+                                            lane * 8) = o;
+                }
+            }
+          }
+        }
+      }
+      (void)osz;
     }
       if (p.epi_mode == kEpiRsPush) {
       // Owner side of the reduce-scatter. Work item = 32 rows of one 128 x BN tile of this rank's rows:

@@ -11,19 +11,22 @@
 // room for that buffer and fetches A rows by token index with TMA gather4.)
 //
 // Layer 1 (grouped GEMM + top-k gather + reduce-scatter) replaces
-// src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:595-820: grouped GEMM
-// into a local [rows, N] buffer with the per-row / per-expert scales applied in
-// the epilogue, then every token's top-k rows are summed in fp32 and pushed to
-// the token's owner, which sums the per-source partials in fp32.
+// src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:595-820 in ONE launch,
+// like the reference's threadblock-specialised kernel
+// (src/moe_gather_rs/sm90_gemm_array_threadblock_specialized.hpp:1315-1514):
+// the grouped GEMM writes a local [rows, N] buffer with the per-row /
+// per-expert scales applied in the epilogue, column slab by column slab; as
+// soon as a slab is complete the kernel's comm warps sum every token's top-k
+// rows of it in fp32, push the rounded rows to the token's owner, and the
+// owner's comm warps sum the per-source partials in fp32.
 #include <string.h>
 
+#include <mutex>
 #include <vector>
 
 #include "internal.h"
 
 namespace fluxb {
-
-constexpr int kTokBlock = 8;  // tokens per push / reduce work item of layer 1
 
 struct MoeTables {
   GroupTile* tiles;
@@ -34,9 +37,10 @@ struct MoeTables {
   int* order;       // [max tiles] visiting order of the tiles
 };
 
-static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+static constexpr size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-static size_t tables_bytes(long long max_rows, int nexperts) {
+// bytes of the tables carve_tables() lays out (the two must change together)
+static constexpr size_t tables_bytes(long long max_rows, int nexperts) {
   size_t b = 0;
   b += align_up((max_rows / kBM + nexperts + 1) * sizeof(GroupTile), 256);
   b += 256;                                                 // num_tiles
@@ -141,106 +145,6 @@ __global__ void moe_order_tiles_kernel(MoeTables t, int rank, int world) {
   for (int i = 0; i < n; ++i) count[key_of(t.tiles[i].need_mask) + 1] += 1;
   for (int i = 1; i <= kMaxWorld; ++i) count[i] += count[i - 1];
   for (int i = 0; i < n; ++i) t.order[count[key_of(t.tiles[i].need_mask)]++] = i;
-}
-
-template <typename T> __device__ __forceinline__ float to_f32(T v);
-template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
-template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
-template <typename T> __device__ __forceinline__ T from_f32(float v);
-template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
-template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
-
-struct PushTargets {
-  void* stage[kMaxWorld];  // owner o's staging slot of this source rank: [tokens_per_rank][n]
-  int* cnt[kMaxWorld];     // owner o's per-token-block counters
-};
-
-// For every token: sum its top-k rows of `inter` in fp32, round once, store into the owner's
-// staging slot; one counter increment per finished block of kTokBlock tokens. Owners are visited
-// starting with rank+1 so that at any time the ranks push to different owners.
-template <typename T>
-__global__ void __launch_bounds__(256)
-moe_topk_push_kernel(const T* __restrict__ inter, const int* __restrict__ scatter_index, int topk, int n,
-                     int total_rows, int tokens_per_rank, int rank, int world, PushTargets tg) {
-  const int blocks_per_owner = (tokens_per_rank + kTokBlock - 1) / kTokBlock;
-  const int total = world * blocks_per_owner;
-  const int nvec = n / 8;
-  for (int w = blockIdx.x; w < total; w += gridDim.x) {
-    const int oi = w / blocks_per_owner;
-    const int blk = w - oi * blocks_per_owner;
-    const int owner = (rank + 1 + oi) % world;
-    const int t0 = blk * kTokBlock;
-    const int t1 = imin(t0 + kTokBlock, tokens_per_rank);
-    T* dst = static_cast<T*>(tg.stage[owner]);
-    for (int tl = t0; tl < t1; ++tl) {
-      const int token = owner * tokens_per_rank + tl;
-      for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        for (int k = 0; k < topk; ++k) {
-          const int row = scatter_index[token * topk + k];
-          if (row < 0 || row >= total_rows) continue;  // a corrupt routing entry must not become a wild load
-          const uint4 raw = *reinterpret_cast<const uint4*>(inter + static_cast<long long>(row) * n + v * 8);
-          const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
-        }
-        uint4 outv;
-        T* o = reinterpret_cast<T*>(&outv);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(acc[j]);
-        *reinterpret_cast<uint4*>(dst + static_cast<long long>(tl) * n + v * 8) = outv;
-      }
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) {
-      fence_acq_rel_sys();
-      red_add_release_sys(tg.cnt[owner] + blk, 1);
-    }
-  }
-}
-
-// Owner side: once every source has published a token block, sum the per-source partials in fp32.
-template <typename T>
-__global__ void __launch_bounds__(256)
-moe_rs_reduce_kernel(const T* __restrict__ stage, int* cnt, T* out, int n, int tokens_per_rank, int world,
-                     int* status, unsigned long long budget_ns) {
-  __shared__ int s_ok;
-  const int blocks = (tokens_per_rank + kTokBlock - 1) / kTokBlock;
-  const int nvec = n / 8;
-  const long long slot = static_cast<long long>(tokens_per_rank) * n;
-  for (int blk = blockIdx.x; blk < blocks; blk += gridDim.x) {
-    if (threadIdx.x == 0)
-      s_ok = flag_wait_eq(cnt + blk, world, AbortWord{nullptr, 0u}, kStatusTimeoutReduce, budget_ns) ? 1 : 0;
-    __syncthreads();
-    if (!s_ok) {
-      if (threadIdx.x == 0) {
-        *reinterpret_cast<volatile int*>(status) = kStatusTimeoutReduce;
-        __threadfence_system();
-      }
-      return;
-    }
-    const int t0 = blk * kTokBlock;
-    const int t1 = imin(t0 + kTokBlock, tokens_per_rank);
-    for (int i = threadIdx.x; i < (t1 - t0) * nvec; i += blockDim.x) {
-      const int tl = t0 + i / nvec;
-      const int v = i % nvec;
-      const long long off = static_cast<long long>(tl) * n + v * 8;
-      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-      for (int s = 0; s < world; ++s) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(stage + s * slot + off);
-        const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) acc[j] += to_f32<T>(e[j]);
-      }
-      uint4 outv;
-      T* o = reinterpret_cast<T*>(&outv);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) o[j] = from_f32<T>(acc[j]);
-      *reinterpret_cast<uint4*>(out + off) = outv;
-    }
-    __syncthreads();
-    if (threadIdx.x == 0) cnt[blk] = 0;
-  }
 }
 
 }  // namespace fluxb
@@ -494,17 +398,20 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
 }
 
 // ------------------------------------------------------------------ layer 1
+// [grouped GEMM output: max_m x n_dim, 16-bit][tile table][slab counters: one per 64 columns]
 size_t fluxb_moe_gather_rs_workspace_bytes(int max_m, int n_dim, int topk, int nexperts) {
   (void)topk;
-  return align_up(static_cast<size_t>(max_m) * n_dim * 2, 256) + tables_bytes(max_m, nexperts);
+  return align_up(static_cast<size_t>(max_m) * n_dim * 2, 256) + tables_bytes(max_m, nexperts) +
+         align_up(static_cast<size_t>((n_dim + 63) / 64) * sizeof(int), 256);
 }
 size_t fluxb_moe_gather_rs_stage_bytes(int max_m, int n_dim, int topk, int world) {
   (void)world;
   return 2ull * (static_cast<size_t>(max_m) / topk) * n_dim * 2;
 }
-size_t fluxb_moe_gather_rs_cnt_bytes(int max_m, int topk, int world) {
+// two parities x (column slabs of 64) x (blocks of 32 tokens per rank)
+size_t fluxb_moe_gather_rs_cnt_bytes(int max_m, int n_dim, int topk, int world) {
   const long long tpr = (static_cast<long long>(max_m) / topk + world - 1) / world;
-  return 2ull * ((tpr + kTokBlock - 1) / kTokBlock) * sizeof(int);
+  return 2ull * ((n_dim + 63) / 64) * ((tpr + kGrTokBlock - 1) / kGrTokBlock) * sizeof(int);
 }
 
 int fluxb_moe_gather_rs_create(fluxb_comm_t comm, int nexperts, int max_m, int n_dim, int topk,
@@ -529,7 +436,7 @@ int fluxb_moe_gather_rs_create(fluxb_comm_t comm, int nexperts, int max_m, int n
   op->in_dtype = in_dtype;
   op->out_dtype = out_dtype;
   op->workspace = workspace;
-  op->cnt_cap = static_cast<long long>(fluxb_moe_gather_rs_cnt_bytes(max_m, topk, comm->world) / (2 * sizeof(int)));
+  op->cnt_cap = static_cast<long long>(fluxb_moe_gather_rs_cnt_bytes(max_m, n_dim, topk, comm->world) / (2 * sizeof(int)));
   for (int r = 0; r < comm->world; ++r) {
     if (stage_bufs[r] == nullptr || cnt_bufs[r] == nullptr) {
       delete op;
@@ -549,7 +456,7 @@ int fluxb_moe_gather_rs_destroy(fluxb_moe_gather_rs_t op) {
 
 int fluxb_moe_gather_rs_reset(fluxb_moe_gather_rs_t op, fluxb_stream_t stream) {
   FLUXB_REQUIRE(op != nullptr, "moe_gather_rs_reset: op is NULL");
-  FLUXB_CUDA(cudaMemsetAsync(op->cnt[op->comm->rank], 0, fluxb_moe_gather_rs_cnt_bytes(op->max_m, op->topk, op->comm->world),
+  FLUXB_CUDA(cudaMemsetAsync(op->cnt[op->comm->rank], 0, fluxb_moe_gather_rs_cnt_bytes(op->max_m, op->n_dim, op->topk, op->comm->world),
                              static_cast<cudaStream_t>(stream)));
   op->calls = 0;
   return FLUXB_OK;
@@ -615,8 +522,9 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   p.ldo = n;
   p.alpha = 1.0f;
   // scales follow python/flux/testing/moe_gather_rs_utils.py:76-79,99: weight_scale[e] * input_scale, then the row vector
-  p.alpha_ptr = (in_scale != nullptr && w_scale != nullptr) ? in_scale : nullptr;
-  p.g_expert_scale = (in_scale != nullptr && w_scale != nullptr) ? w_scale : nullptr;
+  // (each scale applies on its own; a missing one counts as 1)
+  p.alpha_ptr = in_scale;
+  p.g_expert_scale = w_scale;
   p.scale_a = vec_scale;
   p.g_tiles = tb.tiles;
   p.g_num_tiles = tb.num_tiles;
@@ -629,54 +537,44 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * n, k_local, row_bytes,
                       cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
+  // combine + reduce-scatter run inside the same launch (comm warps), column slab by column slab
+  const int parity = static_cast<int>(op->calls & 1ull);
+  const size_t half_stage_elems = (static_cast<size_t>(op->max_m) / topk) * n;
+  const int n_tiles = (n + bn - 1) / bn;
+  const int bpo = (tpr + kGrTokBlock - 1) / kGrTokBlock;
+  FLUXB_REQUIRE(static_cast<long long>(n_tiles) * bpo <= op->cnt_cap, "moe_gather_rs_forward: counter buffer too small");
+  int* slab_done = reinterpret_cast<int*>(ws + align_up(static_cast<size_t>(op->max_m) * n * 2, 256) +
+                                          tables_bytes(op->max_m, op->nexperts));
+  FLUXB_CUDA(cudaMemsetAsync(slab_done, 0, static_cast<size_t>(n_tiles) * sizeof(int), stream));
+  // The other parity's counters were consumed by the previous call and are next written by peers only after
+  // they have seen this call's pushes: clear them now.
+  FLUXB_CUDA(cudaMemsetAsync(op->cnt[comm->rank] + (parity ^ 1) * op->cnt_cap, 0, op->cnt_cap * sizeof(int), stream));
+  p.gr_slab_done = slab_done;
+  p.gr_slab_expected = num_tiles * (cg == 2 ? 2 : 1) * 4;
+  p.gr_scatter_index = routing_idx_dev;
+  p.gr_topk = topk;
+  p.gr_tokens_per_rank = tpr;
+  for (int r = 0; r < world; ++r) {
+    p.gr_stage[r] = static_cast<uint8_t*>(op->stage[r]) +
+                    (parity * half_stage_elems + static_cast<size_t>(comm->rank) * tpr * n) * 2;
+    p.gr_cnt[r] = op->cnt[r] + parity * op->cnt_cap;
+  }
+  p.gr_local_stage = static_cast<uint8_t*>(op->stage[comm->rank]) + parity * half_stage_elems * 2;
+  p.gr_local_cnt = op->cnt[comm->rank] + parity * op->cnt_cap;
+  p.gr_out = out;
+  // Tile order. If the activations fit in L2 with room to spare, one rasterisation band over all M tiles:
+  // the output is produced slab by slab and the combine + reduce-scatter of slab s overlaps the GEMM of slab
+  // s+1 (A is re-read once per slab, from L2). Otherwise the usual bands of 8 M tiles (A streams from HBM
+  // once); the slabs then complete together at the end and the combine follows the GEMM inside the launch.
+  const bool slab_order = static_cast<double>(m) * k_local * eb <= 64.0 * 1024 * 1024;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   t.cta_group = cg;
-  rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
-  if (rc != FLUXB_OK) return rc;
-
-  const int parity = static_cast<int>(op->calls & 1ull);
-  const size_t half_stage_elems = (static_cast<size_t>(op->max_m) / topk) * n;
-  PushTargets tg;
-  memset(&tg, 0, sizeof(tg));
-  for (int r = 0; r < world; ++r) {
-    tg.stage[r] = static_cast<uint8_t*>(op->stage[r]) +
-                  (parity * half_stage_elems + static_cast<size_t>(comm->rank) * tpr * n) * 2;
-    tg.cnt[r] = op->cnt[r] + parity * op->cnt_cap;
+  if (slab_order) {
+    p.group_m = 1 << 20;
+    t.group_m = p.group_m;
   }
-  const int blocks_per_owner = (tpr + kTokBlock - 1) / kTokBlock;
-  int pgrid = world * blocks_per_owner;
-  if (pgrid > 4 * comm->sm_count) pgrid = 4 * comm->sm_count;
-  int rgrid = blocks_per_owner < 2 * comm->sm_count ? blocks_per_owner : 2 * comm->sm_count;
-  const void* local_stage = static_cast<uint8_t*>(op->stage[comm->rank]) + parity * half_stage_elems * 2;
-  int* local_cnt = op->cnt[comm->rank] + parity * op->cnt_cap;
-  const int out_dtype = op->out_dtype;
-  const int rank = comm->rank;
-  int* status_dev = comm->status_dev;
-  const unsigned long long budget = comm->timeout_ns;
-  // every rank's pushes are issued before any rank's owner-side sum (two queue entries when ranks share a GPU)
-  rc = enqueue_or_defer(comm, stream, [=](cudaStream_t st) -> int {
-    if (out_dtype == FLUXB_BF16)
-      moe_topk_push_kernel<__nv_bfloat16><<<pgrid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(inter), routing_idx_dev,
-                                                                 topk, n, m, tpr, rank, world, tg);
-    else
-      moe_topk_push_kernel<__half><<<pgrid, 256, 0, st>>>(static_cast<const __half*>(inter), routing_idx_dev, topk, n, m,
-                                                          tpr, rank, world, tg);
-    FLUXB_CUDA(cudaGetLastError());
-    return FLUXB_OK;
-  });
-  if (rc != FLUXB_OK) return rc;
-  rc = enqueue_or_defer(comm, stream, [=](cudaStream_t st) -> int {
-    if (out_dtype == FLUXB_BF16)
-      moe_rs_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(local_stage), local_cnt,
-                                                                 static_cast<__nv_bfloat16*>(out), n, tpr, world, status_dev,
-                                                                 budget);
-    else
-      moe_rs_reduce_kernel<__half><<<rgrid, 256, 0, st>>>(static_cast<const __half*>(local_stage), local_cnt,
-                                                          static_cast<__half*>(out), n, tpr, world, status_dev, budget);
-    FLUXB_CUDA(cudaGetLastError());
-    return FLUXB_OK;
-  });
+  rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;
   op->calls += 1;
   return FLUXB_OK;
@@ -690,13 +588,10 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
 // ---------------------------------------------------------------------------
 namespace fluxb {
 
-// worst-case table bytes for FLUXB_STATIC_MAX_ROWS routed rows and FLUXB_STATIC_MAX_EXPERTS experts:
-// tiles (rows/128 + experts + 1) * 16 B, one counter, two offset arrays, rows * 4 B of gather index
-constexpr size_t kStaticTableBytes =
-    ((FLUXB_STATIC_MAX_ROWS / kBM + FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(GroupTile) + 255) / 256 * 256 + 256 +
-    2 * (((FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(int) + 255) / 256 * 256) +
-    (static_cast<size_t>(FLUXB_STATIC_MAX_ROWS) * sizeof(int) + 255) / 256 * 256 +
-    ((FLUXB_STATIC_MAX_ROWS / kBM + FLUXB_STATIC_MAX_EXPERTS + 1) * sizeof(int) + 255) / 256 * 256;
+// table bytes for FLUXB_STATIC_MAX_ROWS routed rows and FLUXB_STATIC_MAX_EXPERTS experts, from the same
+// function that sizes the caller-provided workspace
+constexpr size_t kStaticTableBytes = tables_bytes(FLUXB_STATIC_MAX_ROWS, FLUXB_STATIC_MAX_EXPERTS);
+static_assert(kStaticTableBytes < (1u << 20), "the built-in routing tables are meant to stay modest");
 
 // In host code this name is only a handle for cudaGetSymbolAddress, never a device pointer.
 static __device__ __align__(256) unsigned char g_static_tables[kStaticTableBytes];
@@ -704,7 +599,9 @@ static __device__ __align__(256) unsigned char g_static_tables[kStaticTableBytes
 // Device address of the array on the current device, looked up once per device.
 static int static_tables_ptr(int device, void** out) {
   static void* ptrs[64] = {};
+  static std::mutex mu;  // first calls on a device may come from several host threads
   FLUXB_REQUIRE(device >= 0 && device < 64, "device index %d not supported", device);
+  std::lock_guard<std::mutex> lock(mu);
   if (ptrs[device] == nullptr) {
     void* ptr = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&ptr, g_static_tables);

@@ -147,6 +147,19 @@ __device__ __forceinline__ void red_add_release_sys(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
+__device__ __forceinline__ void red_add_release_gpu(int* p, int v) {
+  asm volatile("red.release.gpu.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+// 16-byte load that is not served from a stale L1 line (data another SM stored earlier in this launch)
+__device__ __forceinline__ uint4 ld_relaxed_gpu_v4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.gpu.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
 // Bounded wait until *flag == want (acquire, system scope).
 __device__ __forceinline__ bool flag_wait_eq(const int* flag, int want, const AbortWord& ab,
                                              int code, uint64_t budget_ns) {

@@ -15,7 +15,9 @@ from typing import List, Optional, Sequence
 import torch
 
 from . import _lib
-from .ops import DistEnvTPWithEP, MoeArguments, _check, _cur_stream, _out_dtype, _ptr, _tuning, is_fp8_dtype
+from . import tune as _tune
+from .ops import (DistEnvTPWithEP, MoeArguments, _check, _cur_stream, _out_dtype, _profile, _ptr, _tuning,
+                  is_fp8_dtype)
 from .shm import SymmBuffer, default_comm, fluxb_dtype, get_comm
 
 
@@ -130,6 +132,9 @@ class GemmGroupedV3AGScatter:
 
     def forward(self, inputs_shard, weights, splits_gpu, scatter_index, output_scale=None, outputs_buf=None,
                 allgather_output=None, fast_accum=False, sm_margin=0, tuning=None):
+        if tuning is None and _tune.TABLE.records:
+            tuning = _tune.TABLE.get(_tune.record_key("moe_ag_scatter", scatter_index.shape[0] * self.args.topk,
+                                                      self.ffn_local, self.args.hidden, self.input_dtype, self.comm.world))
         return self._one(inputs_shard, weights, splits_gpu, scatter_index, output_scale, outputs_buf,
                          allgather_output, tuning, reuse=False)
 
@@ -156,7 +161,18 @@ class GemmGroupedV3AGScatter:
 
     def profiling(self, inputs_shard, weights, splits_gpu, scatter_index, output_scale=None, outputs_buf=None,
                   allgather_output=None, fast_accum=False, sm_margin=0, prof_ctx=None):
-        return self.forward(inputs_shard, weights, splits_gpu, scatter_index, output_scale, outputs_buf, allgather_output)
+        """Sweep tile shapes and all-gather transports for this problem (every rank times every candidate, the
+        slowest rank decides), remember the winner for later `forward` calls of the same shape and return its
+        output (src/moe_ag_scatter/ths_op/gemm_grouped_v3_ag_scatter.cc:450-604)."""
+        a = self.args
+        key = _tune.record_key("moe_ag_scatter", scatter_index.shape[0] * a.topk, self.ffn_local, a.hidden,
+                               self.input_dtype, self.comm.world)
+
+        def run(t):
+            return self.forward(inputs_shard, weights, splits_gpu, scatter_index, output_scale, outputs_buf,
+                                allgather_output, tuning=t if t else {})
+
+        return _profile(run, self.comm.group, key, prof_ctx)
 
 
 class GemmGroupedV3GatherRS:
@@ -180,7 +196,7 @@ class GemmGroupedV3GatherRS:
         lib = _lib.load()
         w = self.comm.world
         self._stage = SymmBuffer(self.comm, lib.fluxb_moe_gather_rs_stage_bytes(self.max_m, self.n_dim, self.topk, w))
-        self._cnt = SymmBuffer(self.comm, lib.fluxb_moe_gather_rs_cnt_bytes(self.max_m, self.topk, w))
+        self._cnt = SymmBuffer(self.comm, lib.fluxb_moe_gather_rs_cnt_bytes(self.max_m, self.n_dim, self.topk, w))
         self._ws = torch.zeros(lib.fluxb_moe_gather_rs_workspace_bytes(self.max_m, self.n_dim, self.topk, self.nexperts),
                                dtype=torch.uint8, device=self.comm.device)
         h = C.c_void_p()
@@ -222,6 +238,8 @@ class GemmGroupedV3GatherRS:
                        f"{name} must be a contiguous CUDA float32 tensor with {numel} element(s)")
         out = torch.empty((m // self.topk // w, self.n_dim), dtype=self.output_dtype, device=input.device)
         splits = splits_cpu.contiguous()
+        if tuning is None and _tune.TABLE.records:
+            tuning = _tune.TABLE.get(_tune.record_key("moe_gather_rs", m, self.n_dim, k, self.input_dtype, w))
         _lib.check(_lib.load().fluxb_moe_gather_rs_forward(
             self._h, input.data_ptr(), m, k, weight.data_ptr(), splits.data_ptr(), routing_idx.contiguous().data_ptr(),
             _ptr(input_scale), _ptr(weight_scale), _ptr(output_vec_scale), out.data_ptr(), _tuning(tuning),
@@ -256,4 +274,12 @@ class GemmGroupedV3GatherRS:
         self.comm.host_barrier()
 
     def profiling(self, input, weight, splits_cpu, routing_idx, *args, prof_ctx=None, **kwargs):
-        return self.forward_gather_rs(input, weight, splits_cpu, routing_idx, *args, **kwargs)
+        """Sweep the tile shapes of the grouped GEMM for this problem; see `GemmGroupedV3AGScatter.profiling`
+        (src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc:822-1040)."""
+        key = _tune.record_key("moe_gather_rs", input.shape[0], self.n_dim, input.shape[1], self.input_dtype,
+                               self.comm.world)
+
+        def run(t):
+            return self.forward_gather_rs(input, weight, splits_cpu, routing_idx, *args, tuning=t if t else {}, **kwargs)
+
+        return _profile(run, self.comm.group, key, prof_ctx)

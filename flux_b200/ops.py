@@ -142,12 +142,43 @@ class MoeArguments:
         self.output_dtype = output_dtype if output_dtype is not None else input_dtype
 
 
+class TuningRecord:
+    """One tuned launch configuration: the problem key (op, M, N, K, dtype, TP size - the reference's
+    `UnifiedGemmMeta` + `RuntimeConfig`) and the winning `fluxb_tuning` fields (its `UnifiedGemmHParams`);
+    src/ths_op/ths_op.cc:208-210 `PyTuningRecord`."""
+
+    def __init__(self, key: str, tuning, ms: float = float("nan")):
+        self.key = key
+        self.tuning = dict(tuning) if tuning else None
+        self.ms = float(ms)
+
+    def __repr__(self):
+        return _tune.record_line(self.key, {"tuning": self.tuning, "ms": self.ms})
+
+
+def load_tuning_record(record: "TuningRecord") -> None:
+    """`flux.load_tuning_record(record)` (src/ths_op/ths_op.cc:212-215): later forwards of the record's problem
+    use its configuration."""
+    _tune.TABLE.put(record.key, record.tuning, record.ms)
+
+
 class ProfilingContext:
-    """API-compatible carrier (src/ths_op/ths_op.cc:217-318); tile choice is a run-time table here."""
+    """`flux.ProfilingContext(name)` (src/ths_op/ths_op.cc:217-318): collects what the `profiling()` methods
+    measured. The reference records generated C++ registration code; here a record is the `fluxb_tuning` fields
+    of the winner, printed as one line of text, and `get_all_records()` / `load_tuning_record` carry them into
+    another process (or `flux_b200.tune.TABLE.save/load` as JSON)."""
 
     def __init__(self, name: str):
         self.name = name
-        self.records: List[str] = []
+        self.records: List[str] = []          # one line per profiled problem (the winner)
+        self._results: List[tuple] = []       # (key, [(tuning, ms), ...] sorted by time)
+
+    def add(self, key: str, table) -> "TuningRecord":
+        ranked = sorted(table, key=lambda kv: kv[1])
+        self._results.append((key, ranked))
+        best, ms = ranked[0]
+        self.records.append(_tune.record_line(key, {"tuning": best, "ms": ms}))
+        return TuningRecord(key, best, ms)
 
     def get_code(self) -> str:
         return "\n".join(self.records)
@@ -155,8 +186,32 @@ class ProfilingContext:
     def get_all_record_codes(self) -> List[str]:
         return list(self.records)
 
+    def get_all_prof_results(self, topk: int = 5) -> List[str]:
+        out = []
+        for key, ranked in self._results:
+            lines = [key] + [f" * TopK={i + 1} ({ms:.3f} ms): {t}" for i, (t, ms) in enumerate(ranked[:topk])]
+            out.append("\n".join(lines))
+        return out
+
+    def get_latest_prof_result(self) -> str:
+        _check(bool(self._results), "no latest prof results found")
+        return self.get_all_prof_results()[-1]
+
+    def get_all_records(self) -> List["TuningRecord"]:
+        return [TuningRecord(key, ranked[0][0], ranked[0][1]) for key, ranked in self._results]
+
     def get_latest_record(self):
-        return self.records[-1] if self.records else None
+        _check(bool(self._results), "no latest prof results found")
+        return self.get_all_records()[-1]
+
+
+def _profile(run, group, key: str, prof_ctx):
+    """Shared body of the `profiling()` methods: sweep, remember the winner, report it, run it once more."""
+    best, table = _tune.sweep(run, group)
+    _tune.TABLE.put(key, best, min(ms for _, ms in table))
+    if prof_ctx is not None:
+        prof_ctx.add(key, table)
+    return run(best)
 
 
 def _out_dtype(input_dtype: torch.dtype, output_dtype: Optional[torch.dtype]) -> torch.dtype:
@@ -310,11 +365,7 @@ class AGKernel:
             return self.forward(input, weight, bias, output, input_scale, weight_scale, output_scale, fast_accum,
                                 transpose_weight, all_gather_option, gathered_input, tuning=t if t else {})
 
-        best, table = _tune.sweep(run, self.comm.group)
-        rec = _tune.TABLE.put(key, best, min(ms for _, ms in table))
-        if prof_ctx is not None:
-            prof_ctx.records.append(_tune.record_line(key, rec))
-        return run(best)
+        return _profile(run, self.comm.group, key, prof_ctx)
 
 
 class GemmRS:
@@ -429,11 +480,7 @@ class GemmRS:
             return self.forward(input, weight, bias, input_scale, weight_scale, output_scale, fast_accum,
                                 reduce_scatter_option, tuning=t if t else {})
 
-        best, table = _tune.sweep(run, self.comm.group)
-        rec = _tune.TABLE.put(key, best, min(ms for _, ms in table))
-        if prof_ctx is not None:
-            prof_ctx.records.append(_tune.record_line(key, rec))
-        return run(best)
+        return _profile(run, self.comm.group, key, prof_ctx)
 
 
 class GemmOnly:
@@ -496,7 +543,16 @@ class GemmOnly:
 
     def profiling(self, input, weight, bias=None, output_buf=None, input_scale=None, weight_scale=None,
                   output_scale=None, fast_accum=False, prof_ctx=None):
-        return self.forward(input, weight, bias, output_buf, input_scale, weight_scale, output_scale, fast_accum)
+        """Sweep the tile shapes for this problem and return the output of the fastest one."""
+        m, k = input.shape
+        n = weight.shape[1] if self.transpose_weight else weight.shape[0]
+        key = _tune.record_key("gemm_only", m, n, k, self.input_dtype, 1)
+
+        def run(t):
+            return self.forward(input, weight, bias, output_buf, input_scale, weight_scale, output_scale, fast_accum,
+                                tuning=t if t else {})
+
+        return _profile(run, None, key, prof_ctx)
 
 
 def bitwise_check(a: torch.Tensor, b: torch.Tensor) -> bool:

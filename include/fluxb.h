@@ -249,7 +249,7 @@ int fluxb_moe_scatter_gemm_static(fluxb_comm_t comm, const void* tokens, int nto
  *     (x[scatter_index[t,k], :] . W[expert]^T) * in_scale * w_scale[expert] * vec_scale[row]. */
 size_t fluxb_moe_gather_rs_workspace_bytes(int max_m, int n_dim, int topk, int nexperts);
 size_t fluxb_moe_gather_rs_stage_bytes(int max_m, int n_dim, int topk, int world);
-size_t fluxb_moe_gather_rs_cnt_bytes(int max_m, int topk, int world);
+size_t fluxb_moe_gather_rs_cnt_bytes(int max_m, int n_dim, int topk, int world);
 int fluxb_moe_gather_rs_create(fluxb_comm_t comm, int nexperts, int max_m, int n_dim, int topk,
                                int in_dtype, int out_dtype, float* const* stage_bufs,
                                int* const* cnt_bufs, void* workspace, fluxb_moe_gather_rs_t* out);

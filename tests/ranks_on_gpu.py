@@ -111,7 +111,7 @@ class Ranks:
         _, ft = self.symm(lib.fluxb_ag_gemm_flag_bytes(max_ntokens, self.n))
         max_m = max_ntokens * topk
         _, st = self.symm(lib.fluxb_moe_gather_rs_stage_bytes(max_m, hidden, topk, self.n))
-        _, ct = self.symm(lib.fluxb_moe_gather_rs_cnt_bytes(max_m, topk, self.n))
+        _, ct = self.symm(lib.fluxb_moe_gather_rs_cnt_bytes(max_m, hidden, topk, self.n))
         l0, l1 = [], []
         for r in range(self.n):
             ws0 = torch.zeros(lib.fluxb_moe_ag_scatter_workspace_bytes(max_ntokens, topk, nexperts, hidden, dt),

@@ -66,3 +66,24 @@ def _agree_case(rank, world):
 
 def test_sweep_ranks_agree_world2():
     run_distributed(_agree_case, 2, use_cuda=False)
+
+
+def test_profiling_context_and_load_tuning_record():
+    """`ProfilingContext` keeps every candidate's time per problem, reports the top ones as text and hands out
+    records that `load_tuning_record` installs (src/ths_op/ths_op.cc:208-318)."""
+    from flux_b200 import ops, tune
+
+    ctx = ops.ProfilingContext("x")
+    with pytest.raises(RuntimeError):
+        ctx.get_latest_record()
+    table = [(None, 0.50), ({"block_n": 128, "cta_group": 2}, 0.42), ({"ag_mode": 2}, 0.47)]
+    rec = ctx.add("ag_gemm|m=8|n=8|k=8|bfloat16|tp=2", table)
+    assert rec.tuning == {"block_n": 128, "cta_group": 2} and rec.ms == 0.42
+    text = ctx.get_latest_prof_result()
+    assert text.splitlines()[0] == rec.key and "TopK=1 (0.420 ms)" in text and "TopK=3 (0.500 ms)" in text
+    assert ctx.get_code() == repr(rec) and len(ctx.get_all_records()) == 1
+    try:
+        ops.load_tuning_record(rec)
+        assert tune.TABLE.get(rec.key) == rec.tuning
+    finally:
+        tune.TABLE.records.clear()

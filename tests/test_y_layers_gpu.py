@@ -110,7 +110,13 @@ def test_profiling_records_a_tuning():
         torch.cuda.synchronize()
         assert golden.max_rel_err(out, ref) <= 1e-2
         key = tune.record_key("ag_gemm", m, n, k, torch.bfloat16, 1)
-        assert key in tune.TABLE.records and ctx.get_latest_record().startswith(f"fluxb_tuning[{key}]")
+        rec = ctx.get_latest_record()
+        assert key in tune.TABLE.records and rec.key == key and repr(rec).startswith(f"fluxb_tuning[{key}]")
+        assert ctx.get_latest_prof_result().startswith(key) and " * TopK=1" in ctx.get_latest_prof_result()
+        # a record travels: forget it, load it again, and forward() picks it up
+        tune.TABLE.records.clear()
+        flux.load_tuning_record(rec)
+        assert tune.TABLE.get(key) == rec.tuning
         out2 = ag.forward(a.cuda(), b.cuda())
         torch.cuda.synchronize()
         assert golden.max_rel_err(out2, ref) <= 1e-2
@@ -118,6 +124,7 @@ def test_profiling_records_a_tuning():
         out3 = rs.profiling(a.cuda(), b.cuda(), prof_ctx=ctx)
         torch.cuda.synchronize()
         assert golden.max_rel_err(out3, ref) <= 1e-2 and len(ctx.get_all_record_codes()) == 2
+        assert len(ctx.get_all_records()) == 2 and len(ctx.get_all_prof_results()) == 2
     finally:
         tune.TABLE.records.clear()
 

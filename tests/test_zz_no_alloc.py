@@ -72,6 +72,77 @@ def test_static_entry_point_matches_workspace_entry_point():
         assert golden.max_rel_err(out, oracle) <= TOL, f"call {call}: differs from the oracle"
 
 
+def _call_static(lib, comm, d_tok, ntokens, hidden, d_w, nexperts, ffn, topk, d_splits, d_si, d_scale, out, in_dt, tuning=None):
+    from flux_b200 import _lib
+
+    stream = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+    rc = lib.fluxb_moe_scatter_gemm_static(
+        comm.handle, d_tok.data_ptr(), ntokens, hidden, d_w.data_ptr(), nexperts, ffn, topk, d_splits.data_ptr(),
+        d_si.data_ptr(), d_scale.data_ptr(), out.data_ptr(), in_dt, _lib.BF16,
+        C.byref(_lib.make_tuning(tuning)) if tuning else None, stream)
+    assert rc == _lib.FLUXB_OK, _lib.last_error()
+
+
+def test_static_entry_point_allocates_no_device_memory():
+    """The property the entry point exists for, observed rather than read: the device's free memory
+    (cudaMemGetInfo) is the same before and after the calls. The first call on a device does the one-time
+    set-up (address look-up, kernel attributes), so the window opens after a warm call."""
+    import flux_b200 as flux
+    from flux_b200 import _lib
+
+    lib = _lib.load()
+    flux.init_flux_shm(None)
+    comm = flux.get_comm(None)
+    comm.set_timeout_ms(5000)
+    nexperts, hidden, ffn, topk, ntokens = 8, 256, 384, 2, 512
+    tok, w, splits, si, scale = _case(ntokens, topk, nexperts, hidden, ffn, 21, False)
+    d = [t.cuda() for t in (tok, w, splits, si, scale)]
+    out = torch.empty((ntokens * topk, ffn), dtype=torch.bfloat16, device="cuda")
+    _call_static(lib, comm, d[0], ntokens, hidden, d[1], nexperts, ffn, topk, d[2], d[3], d[4], out, _lib.BF16)
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    for _ in range(3):
+        _call_static(lib, comm, d[0], ntokens, hidden, d[1], nexperts, ffn, topk, d[2], d[3], d[4], out, _lib.BF16)
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    comm.check_status()
+    assert free_after == free_before, f"free device memory changed by {free_before - free_after} bytes across the calls"
+    oracle, _ = golden.moe_ag_scatter_single([tok], w, splits, si, scale)
+    assert golden.max_rel_err(out, oracle) <= TOL
+
+
+def test_static_entry_point_fp8_and_cta_pairs():
+    """e4m3 inputs, and the CTA-pair tile shape (256-row tiles whose second half may hold no rows)."""
+    import flux_b200 as flux
+    from flux_b200 import _lib
+
+    lib = _lib.load()
+    flux.init_flux_shm(None)
+    comm = flux.get_comm(None)
+    comm.set_timeout_ms(5000)
+    nexperts, hidden, ffn, topk, ntokens = 4, 256, 256, 2, 160  # 320 routed rows over 4 experts: <= 128 rows for some
+    tok, w, splits, si, scale = _case(ntokens, topk, nexperts, hidden, ffn, 31, False)
+    out = torch.empty((ntokens * topk, ffn), dtype=torch.bfloat16, device="cuda")
+    d = [t.cuda() for t in (tok, w, splits, si, scale)]
+    oracle, _ = golden.moe_ag_scatter_single([tok], w, splits, si, scale)
+    for cg in (1, 2):
+        out.fill_(float("nan"))
+        _call_static(lib, comm, d[0], ntokens, hidden, d[1], nexperts, ffn, topk, d[2], d[3], d[4], out, _lib.BF16,
+                     tuning={"cta_group": cg})
+        torch.cuda.synchronize()
+        comm.check_status()
+        assert not torch.isnan(out.float()).any(), f"cta_group {cg}: rows were left unwritten"
+        assert golden.max_rel_err(out, oracle) <= TOL, f"cta_group {cg}"
+    f8 = torch.float8_e4m3fn
+    tok8, w8 = tok.to(f8), (w.float() * 16).to(f8)  # weights scaled into e4m3's normal range
+    oracle8, _ = golden.moe_ag_scatter_single([tok8.to(torch.bfloat16)], w8.to(torch.bfloat16), splits, si, scale)
+    out.fill_(float("nan"))
+    _call_static(lib, comm, tok8.cuda(), ntokens, hidden, w8.cuda(), nexperts, ffn, topk, d[2], d[3], d[4], out, _lib.E4M3)
+    torch.cuda.synchronize()
+    comm.check_status()
+    assert golden.max_rel_err(out, oracle8) <= 3e-2
+
+
 def test_static_entry_point_rejects_oversized_problems():
     import flux_b200 as flux
     from flux_b200 import _lib
