@@ -21,10 +21,11 @@ STATIC_MAX_ROWS = 65536
 STATIC_MAX_EXPERTS = 256
 IPC_HANDLE_BYTES = 64
 
-BF16, F16, F32, E4M3, E5M2 = 0, 1, 2, 3, 4
+BF16, F16, F32, E4M3, E5M2, S8 = 0, 1, 2, 3, 4, 5
 BIAS_NONE, BIAS_MN, BIAS_1N = 0, 1, 2
 WEIGHT_KN = 1
 RS_FP32_WIRE = 2
+RS_RING_ORDER = 4
 
 STATUS_NAMES = {
     0: "ok",
@@ -105,6 +106,7 @@ SIGNATURES = {
     "fluxb_moe_ag_scatter_create": (_i, [_vp, _i, _i, _i, _i, _i, _i, _i, _pp, _pp, _vp, _pp]),
     "fluxb_moe_ag_scatter_destroy": (_i, [_vp]),
     "fluxb_moe_ag_scatter_reset": (_i, [_vp, _vp]),
+    "fluxb_moe_ag_scatter_set_ep": (_i, [_vp, _i, _i]),
     "fluxb_moe_ag_scatter_forward": (_i, [_vp, _vp, _i, _vp, _vp, _vp, _vp, _vp, _vp, _tun, _vp]),
     "fluxb_moe_scatter_gemm_static": (_i, [_vp, _vp, _i, _i, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _i, _i, _tun, _vp]),
     "fluxb_moe_gather_rs_workspace_bytes": (_sz, [_i, _i, _i, _i]),
@@ -114,6 +116,8 @@ SIGNATURES = {
     "fluxb_moe_gather_rs_destroy": (_i, [_vp]),
     "fluxb_moe_gather_rs_reset": (_i, [_vp, _vp]),
     "fluxb_moe_gather_rs_forward": (_i, [_vp, _vp, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _tun, _vp]),
+    "fluxb_moe_gather_rs_set_ep": (_i, [_vp, _i, _i]),
+    "fluxb_moe_gather_rs_forward_ep": (_i, [_vp, _vp, _i, _i, _i, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _tun, _vp]),
 }
 
 _LIB = None

@@ -72,12 +72,14 @@ struct GemmParams {
   CUtensorMap tmap_a_own;  // all-gather: this rank's own shard, read in place (valid if a_own_valid)
   int a_own_valid;
   int b_mn_major;  // 1: B is stored [K, N] (N contiguous), loaded as 64-column boxes (16-bit inputs only)
+  int acc_int;     // 1: 8-bit operands are signed integers and the accumulator is int32 (w8a8 with dequantisation)
   int M, N, K;
   // M segmentation: nseg segments of seg_rows rows; tiles never straddle a
   // segment; segments are visited (seg_first + i) % nseg.
   int nseg, seg_rows, seg_first;
   int group_m;  // rasterisation band height in M tiles (uniform bands, used when n_bands == 0)
   int rs_wire16;  // reduce-scatter partials cross NVLink in the 16-bit output format instead of fp32
+  int rs_ring;    // with rs_wire16: every addition of the reduction is rounded to the 16-bit type, own partial last
   int n_bands;  // > 0: explicit bands, band b covers M tiles [band_end[b-1], band_end[b])
   int band_end[8];
   // epilogue
@@ -134,6 +136,8 @@ struct GemmParams {
   uint8_t* g_sorted;              // [rows, K] sorted activations, null = gather4 form
   int* g_perm_done;               // [world] finished permute items per source rank (local, zeroed per call)
   const int* g_scatter_index;     // [tokens, topk]
+  const int* g_row_range;         // device [2]: rows [lo, hi) of the sorted order that this rank computes (expert
+                                  // parallelism: the rows of its experts); null = all rows. Row lo is row 0 of g_sorted.
   const uint8_t* g_tokens;        // gathered tokens [tokens, K] (this rank's gather buffer, or the input at world 1)
   int g_topk;
   // MoE layer 1: the comm warps combine every token's top-k rows of D column slab by column slab (a slab =
@@ -142,7 +146,9 @@ struct GemmParams {
   // in one launch. Tiles are walked slab by slab (one rasterisation band over all M tiles).
   int* gr_slab_done;             // [n_tiles] one arrival per epilogue warp per tile (local, zeroed per call); null = off
   int gr_slab_expected;          // arrivals of a complete slab
-  const int* gr_scatter_index;   // [tokens * topk]: row of D that holds (token, k)
+  const int* gr_scatter_index;   // [tokens * topk]: row of the expert-sorted order that holds (token, k)
+  int gr_row_lo, gr_rows;        // D holds rows [gr_row_lo, gr_row_lo + gr_rows) of that order (expert parallelism:
+                                 // this rank's experts; the other rows are other ranks' and contribute nothing here)
   int gr_topk;
   int gr_tokens_per_rank;
   void* gr_stage[kMaxWorld];     // owner o's staging slot of THIS rank: [tokens_per_rank][N], 16-bit
@@ -483,9 +489,11 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           // grouped, permute form: every source rank the tile reads must be fully permuted
           const int expected = ((p.g_rows_per_rank + kBM - 1) / kBM) * kAgUnitsPerSlice *
                                static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+          const uint64_t w0 = tr != nullptr ? globaltimer_ns() : 0;
           for (int r = 0; ok && r < p.world; ++r)
             if ((tc.need_mask >> r) & 1)
               ok = flag_wait_eq(p.g_perm_done + r, expected, ab, kStatusTimeoutFlag, budget);
+          if (tr != nullptr) tr[5] += globaltimer_ns() - w0;
           if (!ok) break;
           fence_proxy_async();
         }
@@ -595,9 +603,11 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             const uint32_t accum = (kb > kb0 || k > 0) ? 1u : 0u;
             if (CTA2) {
               if (KIND == 0) umma_f16_2cta(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
+              else if (p.acc_int) umma_i8_2cta(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
               else umma_f8_2cta(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
             } else {
               if (KIND == 0) umma_f16(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
+              else if (p.acc_int) umma_i8(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
               else umma_f8(d_tmem, a_desc + 2u * k, b_desc + b_step * k, idesc, accum);
             }
           }
@@ -719,6 +729,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
         sum_row = p.rs_local_stage + static_cast<long long>(p.rank) * p.seg_rows * p.N + lrow * p.N;
         if (p.bias_mode == kBiasFull)
           bias_row = static_cast<const uint8_t*>(p.bias) + static_cast<long long>(grow) * p.ldbias * 2;
+        else if (p.bias_mode == kBiasRow)
+          bias_row = static_cast<const uint8_t*>(p.bias);
       } else if (p.epi_mode == kEpiStore) {
         long long orow = grow;
         if (p.g_scatter_rows != nullptr && row_ok) orow = p.g_scatter_rows[grow];
@@ -734,6 +746,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
         dst_row = reinterpret_cast<uint8_t*>(p.rs_stage[tc.seg] + lrow * p.N);
         if (p.bias_mode == kBiasFull)
           bias_row = static_cast<const uint8_t*>(p.bias) + static_cast<long long>(grow) * p.ldbias * 2;
+        else if (p.bias_mode == kBiasRow)
+          bias_row = static_cast<const uint8_t*>(p.bias);
       }
 
 #pragma unroll 1
@@ -770,12 +784,27 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           }
         }
         float v[32];
+        if (KIND == 1 && p.acc_int) {
+          // int8 operands, int32 accumulator. Dequantisation in the reference's order, so that the result is
+          // bit-identical to its golden path (test/python/ag_gemm/test_ag_kernel.py:143-150, threshold 0):
+          // (input_scale[row] * weight_scale[col]) * float(acc), rounded to the 16-bit output; a bias is then
+          // added in 16-bit arithmetic (`output += bias` on the rounded tensor).
 #pragma unroll
-        for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_scale;
-        if (active && p.scale_b != nullptr) {
+          for (int j = 0; j < 32; ++j) {
+            const float sb = (active && p.scale_b != nullptr && col0 + j < p.N) ? p.scale_b[col0 + j] : 1.0f;
+            v[j] = (row_scale * sb) * __int2float_rn(static_cast<int>(r[j]));
+            if (bias_row != nullptr)
+              v[j] = ((p.epi_mode == kEpiRsPush ? p.rs_out_type : p.out_type) == kOutF16)
+                         ? __half2float(__float2half_rn(v[j])) : __bfloat162float(__float2bfloat16_rn(v[j]));
+          }
+        } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            if (col0 + j < p.N) v[j] *= p.scale_b[col0 + j];
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_scale;
+          if (active && p.scale_b != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (col0 + j < p.N) v[j] *= p.scale_b[col0 + j];
+          }
         }
         if (active && bias_row != nullptr) {
           // bias has the output dtype in store mode, bf16 in reduce-scatter mode
@@ -793,6 +822,13 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
               v[j] += b;
             }
           }
+        }
+        if (own && active && (p.rs_ring || (KIND == 1 && p.acc_int))) {
+          // ring order: the own partial joins last, as a 16-bit value like the peers'; w8a8: every rank's
+          // dequantised partial is a 16-bit tensor in the reference (test/python/gemm_rs/test_gemm_rs.py:127-135)
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            v[j] = (p.rs_out_type == kOutF16) ? __half2float(__float2half_rn(v[j])) : __bfloat162float(__float2bfloat16_rn(v[j]));
         }
         if (own && active) {
 #pragma unroll
@@ -1010,6 +1046,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           int src_rank = p.rank + d;
           if (src_rank >= p.world) src_rank -= p.world;
           const long long tok0 = static_cast<long long>(src_rank) * p.g_rows_per_rank;
+          const int perm_lo = p.g_row_range != nullptr ? p.g_row_range[0] : 0;
+          const int perm_rows = p.g_row_range != nullptr ? p.g_row_range[1] - perm_lo : p.M;
           for (int u = cta_id; comm_ok && u < units_per_src; u += num_ctas) {
             const int ks = u / (perm_chunks * kAgUnitsPerSlice);
             const int rem = u - ks * (perm_chunks * kAgUnitsPerSlice);
@@ -1047,8 +1085,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
                 for (int j = 0; j < 8; ++j)
                   if (rr + j < nrows)
                     for (int k = 0; k < p.g_topk; ++k) {
-                      const long long drow = si[(rr + j) * p.g_topk + k];
-                      if (drow >= 0 && drow < p.M)  // a corrupt routing entry must not become a wild store
+                      const long long drow = static_cast<long long>(si[(rr + j) * p.g_topk + k]) - perm_lo;
+                      if (drow >= 0 && drow < perm_rows)  // rows of other ranks' experts; a corrupt entry must not become a wild store
                         *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
                     }
               }
@@ -1109,8 +1147,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
                 for (int j = 0; j < 4; ++j) {
                   raw[j] = make_uint4(0u, 0u, 0u, 0u);
                   if (tl[j] < tpr && lane_on) {
-                    const int row = p.gr_scatter_index[(static_cast<long long>(owner) * tpr + tl[j]) * p.gr_topk + k];
-                    if (row >= 0 && row < p.M)  // a corrupt routing entry must not become a wild load
+                    const int row = p.gr_scatter_index[(static_cast<long long>(owner) * tpr + tl[j]) * p.gr_topk + k] - p.gr_row_lo;
+                    if (row >= 0 && row < p.gr_rows)  // rows of other ranks' experts; a corrupt entry must not become a wild load
                       raw[j] = ld_relaxed_gpu_v4(static_cast<const uint16_t*>(p.out) + static_cast<long long>(row) * p.ldo + col0 + lane * 8);
                   }
                 }
@@ -1263,14 +1301,20 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
               const int col = n0 + (i - r * kVec16PerRow) * 8;
               off[u] = (i < kVec16PerItem && r < rows && col < p.N) ? static_cast<long long>(row_base + r) * p.N + col : -1;
             }
+            // peers in ring order (rank+1, rank+2, ...): the order of the reference's ring_reduce
+            // (src/gemm_rs/ring_reduce.cu:54-80); with rs_ring the running sum is also rounded to the
+            // 16-bit element type after every addition, as that kernel does
             uint4 v[kMaxWorld][2];
 #pragma unroll
-            for (int sr = 0; sr < kMaxWorld; ++sr)
+            for (int i = 0; i < kMaxWorld - 1; ++i)
 #pragma unroll
               for (int u = 0; u < 2; ++u)
-                if (sr < p.world && sr != p.rank && off[u] >= 0)
-                  v[sr][u] = *reinterpret_cast<const uint4*>(
+                if (i + 1 < p.world && off[u] >= 0) {
+                  int sr = p.rank + 1 + i;
+                  if (sr >= p.world) sr -= p.world;
+                  v[i][u] = *reinterpret_cast<const uint4*>(
                       reinterpret_cast<const uint16_t*>(p.rs_local_stage + sr * slot) + off[u]);
+                }
 #pragma unroll
             for (int u = 0; u < 2; ++u) {
               if (off[u] < 0) continue;
@@ -1278,18 +1322,26 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
 #pragma unroll
               for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
-              for (int sr = 0; sr < kMaxWorld; ++sr)
-                if (sr < p.world && sr != p.rank) {
-                  const uint32_t w[4] = {v[sr][u].x, v[sr][u].y, v[sr][u].z, v[sr][u].w};
+              for (int i = 0; i < kMaxWorld - 1; ++i)
+                if (i + 1 < p.world) {
+                  const uint32_t w[4] = {v[i][u].x, v[i][u].y, v[i][u].z, v[i][u].w};
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {
                     if (p.rs_out_type == kOutBf16) {
                       acc[2 * j] += __uint_as_float(w[j] << 16);
                       acc[2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+                      if (p.rs_ring) {
+                        acc[2 * j] = __bfloat162float(__float2bfloat16_rn(acc[2 * j]));
+                        acc[2 * j + 1] = __bfloat162float(__float2bfloat16_rn(acc[2 * j + 1]));
+                      }
                     } else {
                       const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
                       acc[2 * j] += f.x;
                       acc[2 * j + 1] += f.y;
+                      if (p.rs_ring) {
+                        acc[2 * j] = __half2float(__float2half_rn(acc[2 * j]));
+                        acc[2 * j + 1] = __half2float(__float2half_rn(acc[2 * j + 1]));
+                      }
                     }
                   }
                 }

@@ -209,16 +209,23 @@ int launch_fused_gemm(fluxb_comm* comm, GemmParams& p, int in_dtype,
   p.splitk_cnt = comm->splitk_cnt;
   p.rank = comm->rank;
   p.world = comm->world;
-  const int kind = is_fp8(in_dtype) ? 1 : 0;
+  const int kind = is_8bit(in_dtype) ? 1 : 0;
   uint32_t fmt;
   switch (in_dtype) {
     case FLUXB_BF16: fmt = 1; break;
     case FLUXB_F16: fmt = 0; break;
     case FLUXB_E4M3: fmt = 0; break;
     case FLUXB_E5M2: fmt = 1; break;
-    default: FLUXB_FAIL(FLUXB_ERR_INVALID, "input dtype %d is not bf16/f16/e4m3/e5m2", in_dtype);
+    case FLUXB_S8: fmt = 1; break;
+    default: FLUXB_FAIL(FLUXB_ERR_INVALID, "input dtype %d is not bf16/f16/e4m3/e5m2/s8", in_dtype);
   }
-  const uint32_t idesc = make_idesc(fmt, cg == 2 ? 2 * kBM : kBM, static_cast<uint32_t>(bn), p.b_mn_major ? 1u : 0u);
+  p.acc_int = is_int8(in_dtype) ? 1 : 0;
+  if (p.acc_int) {
+    FLUXB_REQUIRE(p.out_type != kOutF32 || p.epi_mode == kEpiRsPush, "int8 inputs produce a 16-bit output");
+    p.splitk_scratch = nullptr;  // the split-K tail adds parked accumulators as fp32: not for int32 accumulators
+  }
+  const uint32_t idesc = make_idesc(fmt, cg == 2 ? 2 * kBM : kBM, static_cast<uint32_t>(bn), p.b_mn_major ? 1u : 0u,
+                                    p.acc_int ? 2u : 1u);
   if (comm->ranks_on_gpu > 1) {
     DeferredItem it;
     it.fused = true;
@@ -256,7 +263,7 @@ static int out_type_of(int out_dtype, int* ot) {
 
 static int check_gemm_shapes(const char* who, int m, int n, int k, int in_dtype, int out_dtype) {
   const int eb = dtype_bytes(in_dtype);
-  FLUXB_REQUIRE(is_16bit(in_dtype) || is_fp8(in_dtype), "%s: input dtype %d unsupported", who, in_dtype);
+  FLUXB_REQUIRE(is_16bit(in_dtype) || is_8bit(in_dtype), "%s: input dtype %d unsupported", who, in_dtype);
   FLUXB_REQUIRE(m >= 1 && n >= 1 && k >= 1, "%s: empty problem m=%d n=%d k=%d", who, m, n, k);
   FLUXB_REQUIRE((static_cast<long long>(k) * eb) % 16 == 0,
                 "%s: k=%d gives a row pitch of %lld bytes; it must be a multiple of 16", who, k,
@@ -566,7 +573,7 @@ int fluxb_gemm_rs_create(fluxb_comm_t comm, int max_m, int n_dim, int in_dtype, 
   FLUXB_REQUIRE(stage_bufs != nullptr && cnt_bufs != nullptr, "gemm_rs_create: NULL buffer table");
   FLUXB_REQUIRE(max_m >= comm->world && n_dim >= 8 && n_dim % 8 == 0,
                 "gemm_rs_create: max_m=%d n_dim=%d invalid (n_dim must be a multiple of 8)", max_m, n_dim);
-  FLUXB_REQUIRE(is_16bit(in_dtype) || is_fp8(in_dtype), "gemm_rs_create: input dtype %d unsupported", in_dtype);
+  FLUXB_REQUIRE(is_16bit(in_dtype) || is_8bit(in_dtype), "gemm_rs_create: input dtype %d unsupported", in_dtype);
   int ot;
   int rc = out_type_of(out_dtype, &ot);
   if (rc != FLUXB_OK) return rc;
@@ -618,12 +625,13 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   int rc = check_gemm_shapes("gemm_rs_forward", m, n, k_local, op->in_dtype, op->out_dtype);
   if (rc != FLUXB_OK) return rc;
   FLUXB_REQUIRE(bias_mode == FLUXB_BIAS_NONE || bias != nullptr, "gemm_rs_forward: bias is NULL");
-  FLUXB_REQUIRE(bias_mode != FLUXB_BIAS_1N, "gemm_rs_forward: only [M,N] bias is supported");
   if (world == 1)
     return fluxb_gemm(comm, a, b, out, m, n, k_local, op->in_dtype, op->out_dtype, bias, bias_mode,
                       scale_a, scale_b, alpha, flags, tuning, stream_);
   FLUXB_REQUIRE(bias_mode == FLUXB_BIAS_NONE || op->out_dtype == FLUXB_BF16,
                 "gemm_rs_forward: bias needs a bf16 output");
+  // w8a8: the bias is applied by rank 0 only (src/gemm_rs/ths_op/gemm_reduce_scatter.cc:596-599)
+  if (is_int8(op->in_dtype) && comm->rank != 0) bias_mode = FLUXB_BIAS_NONE;
 
   const int eb = dtype_bytes(op->in_dtype);
   const int mpr = m / world;
@@ -656,6 +664,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   // fp32 and rounds once more at the end). Slots keep their fp32-sized stride; 16-bit data fills the
   // first half of a peer's slot, the owner's own slot holds the fp32 sum of the peers' partials.
   p.rs_wire16 = (ot == kOutBf16 || ot == kOutF16) && !(flags & FLUXB_RS_FP32_WIRE) ? 1 : 0;
+  p.rs_ring = (p.rs_wire16 && (flags & FLUXB_RS_RING_ORDER)) ? 1 : 0;
   const size_t half_stage = static_cast<size_t>(op->max_m) * op->n_dim;
   for (int r = 0; r < world; ++r) {
     p.rs_stage[r] = op->stage[r] + parity * half_stage + static_cast<size_t>(comm->rank) * mpr * n;

@@ -45,12 +45,15 @@ inline int dtype_bytes(int dt) {
       return 4;
     case FLUXB_E4M3:
     case FLUXB_E5M2:
+    case FLUXB_S8:
       return 1;
     default:
       return 0;
   }
 }
 inline bool is_fp8(int dt) { return dt == FLUXB_E4M3 || dt == FLUXB_E5M2; }
+inline bool is_int8(int dt) { return dt == FLUXB_S8; }
+inline bool is_8bit(int dt) { return is_fp8(dt) || is_int8(dt); }
 inline bool is_16bit(int dt) { return dt == FLUXB_BF16 || dt == FLUXB_F16; }
 
 }  // namespace fluxb

@@ -14,21 +14,27 @@ namespace fluxb {
 constexpr int kIdxThreads = 1024;
 constexpr int kMaxExperts = 1024;
 
-// Single block: per-thread contiguous slices keep (token,k) order, a block
-// scan per expert turns per-slice counts into stable positions.
+constexpr int kExpertChunk = 32;  // experts handled per sweep: one row of per-thread counts per warp
+
+// Single block. Every thread owns a contiguous slice of the (token, k) pairs, so positions inside an expert
+// follow (token, k) order. Experts are handled 32 at a time: the threads count their slice's pairs per expert
+// into a [32][1024] table in shared memory (one column per thread), each of the 32 warps turns one expert's
+// row into exclusive prefixes over the threads, and a second walk over the slice hands out the positions.
+// Three barriers per 32 experts, whatever the number of experts.
 __global__ void __launch_bounds__(kIdxThreads)
 scatter_index_kernel(const int* __restrict__ chosen, int total, int nexperts, int* splits,
                      int* scatter_index) {
-  extern __shared__ int sh[];  // [nexperts] running base + [kIdxThreads] scan scratch
+  extern __shared__ int sh[];  // [nexperts] first row of every expert + [kExpertChunk][kIdxThreads] counts
   int* base = sh;
-  int* scan = sh + nexperts;
+  int* cnt = sh + nexperts;
   const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
   const int per = (total + kIdxThreads - 1) / kIdxThreads;
   const int lo = imin(tid * per, total);
   const int hi = imin(lo + per, total);
   for (int e = tid; e < nexperts; e += kIdxThreads) base[e] = 0;
   __syncthreads();
-  // pass 1: histogram
+  // histogram -> splits and the first row of every expert
   for (int i = lo; i < hi; ++i) {
     const int e = chosen[i];
     if (e >= 0 && e < nexperts) atomicAdd(&base[e], 1);
@@ -43,23 +49,36 @@ scatter_index_kernel(const int* __restrict__ chosen, int total, int nexperts, in
       run += c;
     }
   }
-  __syncthreads();
-  // pass 2: one expert at a time, exclusive scan of per-slice counts
-  for (int e = 0; e < nexperts; ++e) {
-    int cnt = 0;
-    for (int i = lo; i < hi; ++i) cnt += (chosen[i] == e) ? 1 : 0;
-    scan[tid] = cnt;
-    __syncthreads();
-    for (int off = 1; off < kIdxThreads; off <<= 1) {
-      int v = (tid >= off) ? scan[tid - off] : 0;
-      __syncthreads();
-      scan[tid] += v;
-      __syncthreads();
+  for (int e0 = 0; e0 < nexperts; e0 += kExpertChunk) {
+    for (int j = 0; j < kExpertChunk; ++j) cnt[j * kIdxThreads + tid] = 0;
+    for (int i = lo; i < hi; ++i) {
+      const int j = chosen[i] - e0;
+      if (j >= 0 && j < kExpertChunk && j + e0 < nexperts) cnt[j * kIdxThreads + tid] += 1;
     }
-    int pos = base[e] + scan[tid] - cnt;
-    for (int i = lo; i < hi; ++i)
-      if (chosen[i] == e) scatter_index[i] = pos++;
-    __syncthreads();
+    __syncthreads();  // counts complete (and `base` written, first time round)
+    {
+      // warp w scans the row of expert e0 + w: lane l owns threads 32l .. 32l+31
+      int* row = cnt + warp * kIdxThreads + lane * 32;
+      int sum = 0;
+      for (int q = 0; q < 32; ++q) sum += row[q];
+      int incl = sum;
+      for (int off = 1; off < 32; off <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, off);
+        if (lane >= off) incl += v;
+      }
+      int run = incl - sum;
+      for (int q = 0; q < 32; ++q) {
+        const int c = row[q];
+        row[q] = run;
+        run += c;
+      }
+    }
+    __syncthreads();  // prefixes complete
+    for (int i = lo; i < hi; ++i) {
+      const int j = chosen[i] - e0;
+      if (j >= 0 && j < kExpertChunk && j + e0 < nexperts) scatter_index[i] = base[j + e0] + cnt[j * kIdxThreads + tid]++;
+    }
+    __syncthreads();  // the table is reused by the next 32 experts
   }
 }
 
@@ -88,7 +107,15 @@ int fluxb_moe_scatter_index(const int* chosen_experts, int ntokens, int topk, in
                 nexperts, kMaxExperts);
   const long long total = static_cast<long long>(ntokens) * topk;
   FLUXB_REQUIRE(total < (1ll << 30), "moe_scatter_index: too many routed rows");
-  const size_t sh = (nexperts + kIdxThreads) * sizeof(int);
+  const size_t sh = (static_cast<size_t>(nexperts) + static_cast<size_t>(kExpertChunk) * kIdxThreads) * sizeof(int);
+  static bool configured[64] = {};
+  int dev = 0;
+  FLUXB_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !configured[dev]) {  // 132 KB of dynamic shared memory: above the default limit
+    FLUXB_CUDA(cudaFuncSetAttribute(scatter_index_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>((kMaxExperts + kExpertChunk * kIdxThreads) * sizeof(int))));
+    configured[dev] = true;
+  }
   scatter_index_kernel<<<1, kIdxThreads, sh, static_cast<cudaStream_t>(stream)>>>(
       chosen_experts, static_cast<int>(total), nexperts, splits_out, scatter_index_out);
   FLUXB_CUDA(cudaGetLastError());

@@ -69,8 +69,10 @@ static MoeTables carve_tables(void* ws, long long max_rows, int nexperts) {
 
 // One block. Prefix sums over the experts, then each expert writes its tiles.
 __global__ void __launch_bounds__(1024)
-moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_rows, int max_tiles,
-                       int tile_m, MoeTables t, int* status) {
+moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int e_first, int e_count, int total_rows,
+                       int max_tiles, int tile_m, MoeTables t, int* status) {
+  // Experts [e_first, e_first + e_count) live on this rank (expert parallelism; all of them without it): only
+  // they get tiles, and rows are numbered from the first row of that range (t.num_tiles[1], [2] = the range).
   __shared__ int ok;
   if (threadIdx.x == 0) {
     int off = 0, tb = 0;
@@ -79,10 +81,12 @@ moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_r
       t.tile_base[e] = tb;
       const int n = splits[e] < 0 ? 0 : splits[e];
       off += n;
-      tb += (n + tile_m - 1) / tile_m;
+      if (e >= e_first && e < e_first + e_count) tb += (n + tile_m - 1) / tile_m;
     }
     t.expert_off[nexperts] = off;
     t.tile_base[nexperts] = tb;
+    t.num_tiles[1] = t.expert_off[e_first];
+    t.num_tiles[2] = t.expert_off[e_first + e_count];
     ok = (off == total_rows && tb <= max_tiles) ? 1 : 0;
     *t.num_tiles = ok ? tb : 0;
     if (!ok) {
@@ -92,15 +96,16 @@ moe_build_tiles_kernel(const int* __restrict__ splits, int nexperts, int total_r
   }
   __syncthreads();
   if (!ok) return;
-  for (int e = threadIdx.x; e < nexperts; e += blockDim.x) {
+  const int row_lo = t.num_tiles[1];
+  for (int e = e_first + threadIdx.x; e < e_first + e_count; e += blockDim.x) {
     const int off = t.expert_off[e];
     const int n = t.expert_off[e + 1] - off;
     const int tb = t.tile_base[e];
     for (int c = 0; c * tile_m < n; ++c) {
       GroupTile g;
-      g.a_row0 = off + c * tile_m;
+      g.a_row0 = off - row_lo + c * tile_m;
       g.rows = imin(tile_m, n - c * tile_m);
-      g.expert = e;
+      g.expert = e - e_first;
       g.need_mask = 0;
       t.tiles[tb + c] = g;
     }
@@ -113,9 +118,9 @@ __global__ void moe_route_rows_kernel(const int* __restrict__ scatter_index, int
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= total || *t.num_tiles == 0) return;
   const int row = scatter_index[i];
-  if (row < 0 || row >= total) return;
+  if (row < t.num_tiles[1] || row >= t.num_tiles[2]) return;  // not a row of this rank's experts (or corrupt)
   const int token = i / topk;
-  t.gather[row] = token;
+  t.gather[row - t.num_tiles[1]] = token;
   int lo = 0, hi = nexperts;  // largest e with expert_off[e] <= row
   while (hi - lo > 1) {
     const int mid = (lo + hi) >> 1;
@@ -168,6 +173,7 @@ struct fluxb_moe_ag_scatter {
   unsigned long long calls;
   int last_parity;      // parity of the buffers the last push filled
   int last_ntokens;     // tokens gathered by the last push
+  int ep_rank = 0, ep_size = 1;  // expert parallelism: this rank holds experts [ep_rank, ep_rank + 1) * nexperts / ep_size
   AgDma dma;
 };
 
@@ -179,6 +185,7 @@ struct fluxb_moe_gather_rs {
   void* workspace;
   long long cnt_cap;
   unsigned long long calls;
+  int ep_rank = 0, ep_size = 1;
 };
 
 static int flag_stride_of(int full_m, int world) {
@@ -249,6 +256,17 @@ int fluxb_moe_ag_scatter_destroy(fluxb_moe_ag_scatter_t op) {
   return FLUXB_OK;
 }
 
+int fluxb_moe_ag_scatter_set_ep(fluxb_moe_ag_scatter_t op, int ep_rank, int ep_size) {
+  FLUXB_REQUIRE(op != nullptr, "moe_ag_scatter_set_ep: op is NULL");
+  FLUXB_REQUIRE(ep_size >= 1 && ep_rank >= 0 && ep_rank < ep_size && op->nexperts % ep_size == 0 &&
+                    op->comm->world % ep_size == 0,
+                "moe_ag_scatter_set_ep: ep_rank=%d ep_size=%d must divide nexperts=%d and world=%d", ep_rank, ep_size,
+                op->nexperts, op->comm->world);
+  op->ep_rank = ep_rank;
+  op->ep_size = ep_size;
+  return FLUXB_OK;
+}
+
 int fluxb_moe_ag_scatter_reset(fluxb_moe_ag_scatter_t op, fluxb_stream_t stream) {
   FLUXB_REQUIRE(op != nullptr, "moe_ag_scatter_reset: op is NULL");
   FLUXB_CUDA(cudaMemsetAsync(op->flags[op->comm->rank], 0, fluxb_ag_gemm_flag_bytes(op->max_ntokens, op->comm->world),
@@ -288,8 +306,9 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   p.g_tiles = tb.tiles;
   const int cg = grouped_cta_group(tuning, rows, op->nexperts);
   const int tile_m = cg == 2 ? 2 * kBM : kBM;
-  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, op->nexperts, static_cast<int>(rows), max_tiles, tile_m,
-                                                tb, comm->status_dev);
+  const int e_count = op->nexperts / op->ep_size, e_first = op->ep_rank * e_count;
+  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, op->nexperts, e_first, e_count, static_cast<int>(rows),
+                                                max_tiles, tile_m, tb, comm->status_dev);
   FLUXB_CUDA(cudaGetLastError());
   moe_route_rows_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, stream>>>(
       scatter_index_dev, static_cast<int>(rows), op->topk, ntokens_local, op->nexperts, tile_m, tb);
@@ -332,6 +351,7 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   p.g_ntokens = static_cast<int>(ntokens);
   p.g_topk = op->topk;
   p.g_scatter_index = scatter_index_dev;
+  p.g_row_range = tb.num_tiles + 1;  // rows of this rank's experts (all rows without expert parallelism)
   p.ag_row_bytes = row_bytes;
   uint8_t* ws = static_cast<uint8_t*>(op->workspace);
   int* perm_done = reinterpret_cast<int*>(ws + tables_bytes(max_rows, op->nexperts));
@@ -367,7 +387,7 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   const int bn = resolve_block_n(comm, p, tuning, max_tiles);
   int rc = encode_tmap_2d(&p.tmap_a, p.g_sorted, op->in_dtype, rows, op->hidden, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * op->ffn_local,
+  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(e_count) * op->ffn_local,
                       op->hidden, row_bytes, cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
@@ -427,7 +447,7 @@ int fluxb_moe_gather_rs_create(fluxb_comm_t comm, int nexperts, int max_m, int n
                 "moe_gather_rs_create: max_m=%d must be a positive multiple of topk*world=%d", max_m, topk * comm->world);
   FLUXB_REQUIRE(n_dim >= 8 && n_dim % 8 == 0, "moe_gather_rs_create: n_dim=%d must be a multiple of 8", n_dim);
   fluxb_moe_gather_rs* op = new fluxb_moe_gather_rs();
-  memset(op, 0, sizeof(*op));
+  op->calls = 0;
   op->comm = comm;
   op->nexperts = nexperts;
   op->max_m = max_m;
@@ -454,6 +474,17 @@ int fluxb_moe_gather_rs_destroy(fluxb_moe_gather_rs_t op) {
   return FLUXB_OK;
 }
 
+int fluxb_moe_gather_rs_set_ep(fluxb_moe_gather_rs_t op, int ep_rank, int ep_size) {
+  FLUXB_REQUIRE(op != nullptr, "moe_gather_rs_set_ep: op is NULL");
+  FLUXB_REQUIRE(ep_size >= 1 && ep_rank >= 0 && ep_rank < ep_size && op->nexperts % ep_size == 0 &&
+                    op->comm->world % ep_size == 0,
+                "moe_gather_rs_set_ep: ep_rank=%d ep_size=%d must divide nexperts=%d and world=%d", ep_rank, ep_size,
+                op->nexperts, op->comm->world);
+  op->ep_rank = ep_rank;
+  op->ep_size = ep_size;
+  return FLUXB_OK;
+}
+
 int fluxb_moe_gather_rs_reset(fluxb_moe_gather_rs_t op, fluxb_stream_t stream) {
   FLUXB_REQUIRE(op != nullptr, "moe_gather_rs_reset: op is NULL");
   FLUXB_CUDA(cudaMemsetAsync(op->cnt[op->comm->rank], 0, fluxb_moe_gather_rs_cnt_bytes(op->max_m, op->n_dim, op->topk, op->comm->world),
@@ -467,6 +498,17 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
                                 const int* routing_idx_dev, const float* in_scale,
                                 const float* w_scale, const float* vec_scale, void* out,
                                 const fluxb_tuning* tuning, fluxb_stream_t stream_) {
+  FLUXB_REQUIRE(op != nullptr, "moe_gather_rs_forward: NULL argument");
+  FLUXB_REQUIRE(op->ep_size == 1, "moe_gather_rs_forward: with expert parallelism call fluxb_moe_gather_rs_forward_ep");
+  return fluxb_moe_gather_rs_forward_ep(op, x, m, m / op->topk, k_local, weights, splits_host, routing_idx_dev, in_scale,
+                                        w_scale, vec_scale, out, tuning, stream_);
+}
+
+int fluxb_moe_gather_rs_forward_ep(fluxb_moe_gather_rs_t op, const void* x, int m, int ntokens, int k_local,
+                                   const void* weights, const int* splits_host,
+                                   const int* routing_idx_dev, const float* in_scale,
+                                   const float* w_scale, const float* vec_scale, void* out,
+                                   const fluxb_tuning* tuning, fluxb_stream_t stream_) {
   FLUXB_REQUIRE(op != nullptr && x != nullptr && weights != nullptr && splits_host != nullptr &&
                     routing_idx_dev != nullptr && out != nullptr, "moe_gather_rs_forward: NULL argument");
   fluxb_comm* comm = op->comm;
@@ -474,36 +516,47 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   const int world = comm->world;
   const int topk = op->topk;
   const int n = op->n_dim;
-  FLUXB_REQUIRE(m >= topk * world && m <= op->max_m && m % (topk * world) == 0,
-                "moe_gather_rs_forward: m=%d must be a multiple of topk*world=%d within max_m=%d", m, topk * world, op->max_m);
+  const long long rows_all = static_cast<long long>(ntokens) * topk;
+  FLUXB_REQUIRE(ntokens >= world && rows_all <= op->max_m && ntokens % world == 0,
+                "moe_gather_rs_forward: ntokens=%d must be a multiple of world=%d with ntokens*topk within max_m=%d",
+                ntokens, world, op->max_m);
+  FLUXB_REQUIRE(m >= 0 && m <= rows_all && (op->ep_size > 1 || m == rows_all),
+                "moe_gather_rs_forward: m=%d rows for %d tokens x top-%d", m, ntokens, topk);
   const int eb = dtype_bytes(op->in_dtype);
   FLUXB_REQUIRE(k_local >= 8 && (static_cast<long long>(k_local) * eb) % 16 == 0,
                 "moe_gather_rs_forward: k_local=%d gives a row pitch that is not a multiple of 16 bytes", k_local);
-  const int ntokens = m / topk;
   const int tpr = ntokens / world;
+  // expert parallelism: this rank computes the rows of experts [e_first, e_first + e_count), which are rows
+  // [row_lo, row_lo + m) of the expert-sorted order; `x`, the row scales and the tiles count from row_lo
+  const int e_count = op->nexperts / op->ep_size, e_first = op->ep_rank * e_count;
 
   // tile table from the host-side splits (the reference also packs its problem list on the host
   // and uploads it, gemm_grouped_v3_gather_rs.cc:245-416)
   GemmParams p;
   memset(&p, 0, sizeof(p));
-  const int cg = grouped_cta_group(tuning, m, op->nexperts);
+  const int cg = grouped_cta_group(tuning, m, e_count);
   const int tile_m = cg == 2 ? 2 * kBM : kBM;
   std::vector<GroupTile> tiles;
-  long long off = 0;
+  long long off = 0, row_lo = 0;
   for (int e = 0; e < op->nexperts; ++e) {
     const int cnt = splits_host[e];
     FLUXB_REQUIRE(cnt >= 0, "moe_gather_rs_forward: splits[%d]=%d is negative", e, cnt);
-    for (int c = 0; c * tile_m < cnt; ++c) {
-      GroupTile g;
-      g.a_row0 = static_cast<int>(off) + c * tile_m;
-      g.rows = cnt - c * tile_m < tile_m ? cnt - c * tile_m : tile_m;
-      g.expert = e;
-      g.need_mask = 0;
-      tiles.push_back(g);
-    }
+    if (e == e_first) row_lo = off;
+    if (e >= e_first && e < e_first + e_count)
+      for (int c = 0; c * tile_m < cnt; ++c) {
+        GroupTile g;
+        g.a_row0 = static_cast<int>(off - row_lo) + c * tile_m;
+        g.rows = cnt - c * tile_m < tile_m ? cnt - c * tile_m : tile_m;
+        g.expert = e - e_first;
+        g.need_mask = 0;
+        tiles.push_back(g);
+      }
     off += cnt;
+    if (e == e_first + e_count - 1)
+      FLUXB_REQUIRE(off - row_lo == m, "moe_gather_rs_forward: the splits of this rank's experts sum to %lld, expected m=%d",
+                    off - row_lo, m);
   }
-  FLUXB_REQUIRE(off == m, "moe_gather_rs_forward: splits sum to %lld, expected m=%d", off, m);
+  FLUXB_REQUIRE(off == rows_all, "moe_gather_rs_forward: splits sum to %lld, expected ntokens*topk=%lld", off, rows_all);
   uint8_t* ws = static_cast<uint8_t*>(op->workspace);
   void* inter = ws;
   MoeTables tb = carve_tables(ws + align_up(static_cast<size_t>(op->max_m) * n * 2, 256), op->max_m, op->nexperts);
@@ -512,11 +565,11 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   FLUXB_CUDA(cudaMemcpyAsync(tb.num_tiles, &num_tiles, sizeof(int), cudaMemcpyHostToDevice, stream));
 
   p.out_type = op->out_dtype == FLUXB_BF16 ? kOutBf16 : kOutF16;
-  p.M = m;
+  p.M = m > 0 ? m : 1;
   p.N = n;
   p.K = k_local;
   p.nseg = 1;
-  p.seg_rows = m;
+  p.seg_rows = p.M;
   p.epi_mode = kEpiStore;
   p.out = inter;
   p.ldo = n;
@@ -532,9 +585,9 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   p.g_rows_per_expert_b = n;
   const long long row_bytes = static_cast<long long>(k_local) * eb;
   const int bn = resolve_block_n(comm, p, tuning, num_tiles > 0 ? num_tiles : 1);
-  int rc = encode_tmap_2d(&p.tmap_a, x, op->in_dtype, m, k_local, row_bytes, kBM);
+  int rc = encode_tmap_2d(&p.tmap_a, x, op->in_dtype, p.M, k_local, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
-  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(op->nexperts) * n, k_local, row_bytes,
+  rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(e_count) * n, k_local, row_bytes,
                       cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
   // combine + reduce-scatter run inside the same launch (comm warps), column slab by column slab
@@ -552,6 +605,8 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   p.gr_slab_done = slab_done;
   p.gr_slab_expected = num_tiles * (cg == 2 ? 2 : 1) * 4;
   p.gr_scatter_index = routing_idx_dev;
+  p.gr_row_lo = static_cast<int>(row_lo);
+  p.gr_rows = m;
   p.gr_topk = topk;
   p.gr_tokens_per_rank = tpr;
   for (int r = 0; r < world; ++r) {
@@ -566,7 +621,7 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
   // the output is produced slab by slab and the combine + reduce-scatter of slab s overlaps the GEMM of slab
   // s+1 (A is re-read once per slab, from L2). Otherwise the usual bands of 8 M tiles (A streams from HBM
   // once); the slabs then complete together at the end and the combine follows the GEMM inside the launch.
-  const bool slab_order = static_cast<double>(m) * k_local * eb <= 64.0 * 1024 * 1024;
+  const bool slab_order = static_cast<double>(p.M) * k_local * eb <= 64.0 * 1024 * 1024;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   t.cta_group = cg;
@@ -658,8 +713,8 @@ extern "C" int fluxb_moe_scatter_gemm_static(fluxb_comm_t comm, const void* toke
   const int tile_m = cg == 2 ? 2 * kBM : kBM;
   // every table entry a later stage reads is written here first: tile list, tile count, offsets and
   // the source-rank masks by the first kernel, the gather index of all `rows` rows by the second
-  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, nexperts, static_cast<int>(rows), max_tiles, tile_m, tb,
-                                                comm->status_dev);
+  moe_build_tiles_kernel<<<1, 1024, 0, stream>>>(splits_dev, nexperts, 0, nexperts, static_cast<int>(rows), max_tiles,
+                                                tile_m, tb, comm->status_dev);
   FLUXB_CUDA(cudaGetLastError());
   moe_route_rows_kernel<<<static_cast<int>((rows + 255) / 256), 256, 0, stream>>>(
       scatter_index_dev, static_cast<int>(rows), topk, ntokens, nexperts, tile_m, tb);

@@ -258,6 +258,18 @@ __device__ __forceinline__ void umma_f8(uint32_t d_tmem, uint64_t a_desc, uint64
       : "memory");
 }
 
+// same for signed 8-bit integer inputs, int32 accumulate
+__device__ __forceinline__ void umma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                        uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread `lane` receives row
 // (taddr.lane + lane), columns taddr.col .. +31.
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
@@ -336,6 +348,16 @@ __device__ __forceinline__ void umma_f8_2cta(uint32_t d_tmem, uint64_t a_desc, u
       "{\n\t.reg .pred p;\n\t"
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+      :
+      : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void umma_i8_2cta(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
+                                             uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::i8 [%0], %1, %2, %3, p;\n\t}"
       :
       : "r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
       : "memory");
@@ -429,14 +451,14 @@ __device__ __forceinline__ uint64_t make_mnmajor_sw128_desc(uint32_t smem_addr, 
   return d;
 }
 
-// Instruction descriptor (dense, fp32 accumulate, both operands K-major).
-//   [4,6) D format (1 = f32)   [7,10) A format   [10,13) B format
+// Instruction descriptor (dense, both operands K-major unless b_mn_major).
+//   [4,6) D format (1 = f32, 2 = s32)   [7,10) A format   [10,13) B format
 //   [15] A major (0 = K)       [16] B major (0 = K)
 //   [17,23) N >> 3             [24,29) M >> 4
-// A/B format: kind::f16 -> 0 = f16, 1 = bf16; kind::f8f6f4 -> 0 = e4m3, 1 = e5m2
+// A/B format: kind::f16 -> 0 = f16, 1 = bf16; kind::f8f6f4 -> 0 = e4m3, 1 = e5m2; kind::i8 -> 0 = u8, 1 = s8
 __host__ __device__ constexpr uint32_t make_idesc(uint32_t ab_format, uint32_t m, uint32_t n,
-                                                  uint32_t b_mn_major = 0) {
-  return (1u << 4) | (ab_format << 7) | (ab_format << 10) | (b_mn_major << 16) | ((n >> 3) << 17) |
+                                                  uint32_t b_mn_major = 0, uint32_t d_format = 1) {
+  return (d_format << 4) | (ab_format << 7) | (ab_format << 10) | (b_mn_major << 16) | ((n >> 3) << 17) |
          ((m >> 4) << 24);
 }
 

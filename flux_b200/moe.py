@@ -5,7 +5,8 @@
   GemmGroupedV3GatherRS  - src/pybind/gemm_grouped_v3_gather_rs.cc:35-126
                            (src/moe_gather_rs/ths_op/gemm_grouped_v3_gather_rs.cc)
   calc_scatter_index     - src/pybind/ths_op.cc:59-76 (stable order here)
-Tensor parallelism over the ffn dimension with all experts on every rank (EP = 1).
+Tensor parallelism over the ffn dimension; with an `ep_group` the experts are additionally split over
+`ep_size` groups of `world / ep_size` ranks (DistEnvTPWithEP, src/ths_op/ths_op.cc:334-346).
 """
 from __future__ import annotations
 
@@ -61,12 +62,16 @@ class GemmGroupedV3AGScatter:
     out[scatter_index[t, k], :] = token_t . W[expert(t,k)]^T * output_scale[expert]."""
 
     def __init__(self, tp_env: DistEnvTPWithEP, moe_args: MoeArguments):
-        _check(tp_env.ep_size == 1, "GemmGroupedV3AGScatter: expert parallelism (EP > 1) is not supported")
         self.comm = get_comm(tp_env.tp_group)
         self.args = moe_args
         w = self.comm.world
-        _check(moe_args.ffn_hidden % w == 0, "GemmGroupedV3AGScatter: ffn_hidden must divide by the TP size")
-        self.ffn_local = moe_args.ffn_hidden // w
+        self.ep_rank, self.ep_size = int(tp_env.ep_rank), int(tp_env.ep_size)
+        _check(w % self.ep_size == 0 and moe_args.nexperts % self.ep_size == 0,
+               "GemmGroupedV3AGScatter: the EP size must divide the world size and the number of experts")
+        ffn_tp = w // self.ep_size
+        _check(moe_args.ffn_hidden % ffn_tp == 0, "GemmGroupedV3AGScatter: ffn_hidden must divide by the ffn TP size")
+        self.ffn_local = moe_args.ffn_hidden // ffn_tp
+        self.nexperts_local = moe_args.nexperts // self.ep_size
         self.input_dtype = moe_args.input_dtype
         self.output_dtype = torch.bfloat16 if is_fp8_dtype(moe_args.input_dtype) and moe_args.output_dtype == moe_args.input_dtype \
             else moe_args.output_dtype
@@ -83,6 +88,8 @@ class GemmGroupedV3AGScatter:
             in_dt, fluxb_dtype(self.output_dtype), self._gather.table(), self._flags.table(), self._ws.data_ptr(),
             C.byref(h)))
         self._h = h
+        if self.ep_size > 1:
+            _lib.check(lib.fluxb_moe_ag_scatter_set_ep(h, self.ep_rank, self.ep_size))
         self.comm.host_barrier()
 
     def __del__(self):
@@ -98,8 +105,8 @@ class GemmGroupedV3AGScatter:
         # shape rules of src/moe_ag_scatter/ths_op/gemm_grouped_v3_ag_scatter.cc:239-265
         _check(weights.is_cuda and weights.dim() == 3 and weights.is_contiguous(), "weights must be a contiguous CUDA [E, ffn/TP, hidden] tensor")
         _check(weights.dtype == self.input_dtype, "weights dtype mismatch")
-        _check(tuple(weights.shape) == (a.nexperts, self.ffn_local, a.hidden),
-               f"weights shape {tuple(weights.shape)} != {(a.nexperts, self.ffn_local, a.hidden)}")
+        _check(tuple(weights.shape) == (self.nexperts_local, self.ffn_local, a.hidden),
+               f"weights shape {tuple(weights.shape)} != {(self.nexperts_local, self.ffn_local, a.hidden)}")
         _check(splits_gpu.is_cuda and splits_gpu.dtype == torch.int32 and splits_gpu.numel() >= a.nexperts,
                "splits_gpu must be a CUDA int32 tensor with at least nexperts entries")
         _check(scatter_index.is_cuda and scatter_index.dtype == torch.int32 and scatter_index.dim() == 2
@@ -113,14 +120,24 @@ class GemmGroupedV3AGScatter:
                    and tuple(inputs_shard.shape) == (nlocal, a.hidden),
                    f"inputs_shard must be a contiguous [{nlocal}, {a.hidden}] tensor")
         if output_scale is not None:
-            _check(output_scale.dtype == torch.float32 and output_scale.numel() == a.nexperts and output_scale.is_contiguous(),
-                   "output_scale must be a float32 [nexperts] tensor")
+            _check(output_scale.dtype == torch.float32 and output_scale.numel() == self.nexperts_local
+                   and output_scale.is_contiguous(), "output_scale must be a float32 tensor with one entry per local expert")
         rows = ntokens * a.topk
+        if self.ep_size > 1:
+            # only the rows of this rank's experts are produced; their number is a device value (the reference
+            # reads the splits back on every call, gemm_grouped_v3_ag_scatter.cc:323-363): callers who know it
+            # pass an `outputs_buf` of that many rows and no read-back happens
+            if outputs_buf is not None:
+                rows = min(rows, outputs_buf.shape[0])
+            else:
+                e0 = self.ep_rank * self.nexperts_local
+                rows = int(splits_gpu[e0:e0 + self.nexperts_local].sum().item())
         if outputs_buf is None:
             outputs_buf = torch.empty((rows, self.ffn_local), dtype=self.output_dtype, device=weights.device)
         else:
             _check(outputs_buf.dtype == self.output_dtype and outputs_buf.is_contiguous() and outputs_buf.shape[0] >= rows
-                   and outputs_buf.shape[1] == self.ffn_local, "outputs_buf has the wrong shape, dtype or layout")
+                   and outputs_buf.dim() == 2 and outputs_buf.shape[1] == self.ffn_local,
+                   "outputs_buf has the wrong shape, dtype or layout")
         if allgather_output is not None:
             _check(tuple(allgather_output.shape) == (ntokens, a.hidden) and allgather_output.dtype == self.input_dtype
                    and allgather_output.is_contiguous(), "allgather_output has the wrong shape, dtype or layout")
@@ -183,8 +200,10 @@ class GemmGroupedV3GatherRS:
 
     def __init__(self, total_num_experts, max_m, n_dim, topk, rank, world_size, tp_world_size, ep_world_size,
                  max_input_groups=1, ep_in_dp=False, input_dtype=torch.bfloat16, output_dtype=None):
-        _check(int(ep_world_size) == 1 and int(tp_world_size) == int(world_size),
-               "GemmGroupedV3GatherRS: expert parallelism (EP > 1) is not supported")
+        _check(int(tp_world_size) * int(ep_world_size) == int(world_size),
+               "GemmGroupedV3GatherRS: tp_world_size * ep_world_size must equal world_size")
+        self.ep_size = int(ep_world_size)
+        self.ep_rank = int(rank) // int(tp_world_size)  # ranks of one ffn-TP group are consecutive
         self.comm = default_comm()
         _check(self.comm.rank == int(rank) and self.comm.world == int(world_size),
                f"GemmGroupedV3GatherRS: rank/world_size ({rank}/{world_size}) do not match the communicator of "
@@ -204,6 +223,9 @@ class GemmGroupedV3GatherRS:
             self.comm.handle, self.nexperts, self.max_m, self.n_dim, self.topk, fluxb_dtype(self.input_dtype),
             fluxb_dtype(self.output_dtype), self._stage.table(), self._cnt.table(), self._ws.data_ptr(), C.byref(h)))
         self._h = h
+        if self.ep_size > 1:
+            _check(self.nexperts % self.ep_size == 0, "GemmGroupedV3GatherRS: the EP size must divide the number of experts")
+            _lib.check(lib.fluxb_moe_gather_rs_set_ep(h, self.ep_rank, self.ep_size))
         self.comm.host_barrier()
 
     def __del__(self):
@@ -224,26 +246,29 @@ class GemmGroupedV3GatherRS:
         _check(weight.is_cuda and weight.dim() == 3 and weight.is_contiguous() and weight.dtype == self.input_dtype,
                "weight must be a contiguous CUDA [E, N, K] tensor of the op's dtype")
         m, k = input.shape
-        _check(tuple(weight.shape) == (self.nexperts, self.n_dim, k), f"weight shape {tuple(weight.shape)} != {(self.nexperts, self.n_dim, k)}")
+        e_local = self.nexperts // self.ep_size
+        _check(tuple(weight.shape) == (e_local, self.n_dim, k), f"weight shape {tuple(weight.shape)} != {(e_local, self.n_dim, k)}")
         _check(not splits_cpu.is_cuda and splits_cpu.dtype == torch.int32 and splits_cpu.numel() >= self.nexperts,
                "splits_cpu must be a CPU int32 tensor with at least nexperts entries")
-        _check(routing_idx.is_cuda and routing_idx.dtype == torch.int32 and routing_idx.numel() == m,
-               "routing_idx must be a CUDA int32 tensor with M entries")
-        _check(m % self.topk == 0 and m <= self.max_m, f"M={m} must divide by topk and be <= max_m={self.max_m}")
+        _check(routing_idx.is_cuda and routing_idx.dtype == torch.int32, "routing_idx must be a CUDA int32 tensor")
+        rows_all = routing_idx.numel()  # ntokens * topk; with expert parallelism `input` holds this rank's experts' rows
+        _check(rows_all % self.topk == 0 and rows_all <= self.max_m and (self.ep_size > 1 or rows_all == m),
+               f"routing_idx has {rows_all} entries for M={m} rows (max_m={self.max_m}, topk={self.topk})")
         w = self.comm.world
-        for name, s, numel in (("input_scale", input_scale, 1), ("weight_scale", weight_scale, self.nexperts),
+        for name, s, numel in (("input_scale", input_scale, 1), ("weight_scale", weight_scale, e_local),
                                ("output_vec_scale", output_vec_scale, m)):
             if s is not None:
                 _check(s.is_cuda and s.dtype == torch.float32 and s.numel() == numel and s.is_contiguous(),
                        f"{name} must be a contiguous CUDA float32 tensor with {numel} element(s)")
-        out = torch.empty((m // self.topk // w, self.n_dim), dtype=self.output_dtype, device=input.device)
+        ntokens = rows_all // self.topk
+        out = torch.empty((ntokens // w, self.n_dim), dtype=self.output_dtype, device=input.device)
         splits = splits_cpu.contiguous()
         if tuning is None and _tune.TABLE.records:
             tuning = _tune.TABLE.get(_tune.record_key("moe_gather_rs", m, self.n_dim, k, self.input_dtype, w))
-        _lib.check(_lib.load().fluxb_moe_gather_rs_forward(
-            self._h, input.data_ptr(), m, k, weight.data_ptr(), splits.data_ptr(), routing_idx.contiguous().data_ptr(),
-            _ptr(input_scale), _ptr(weight_scale), _ptr(output_vec_scale), out.data_ptr(), _tuning(tuning),
-            _cur_stream()))
+        _lib.check(_lib.load().fluxb_moe_gather_rs_forward_ep(
+            self._h, input.data_ptr(), m, ntokens, k, weight.data_ptr(), splits.data_ptr(),
+            routing_idx.contiguous().data_ptr(), _ptr(input_scale), _ptr(weight_scale), _ptr(output_vec_scale),
+            out.data_ptr(), _tuning(tuning), _cur_stream()))
         if with_stream_sync:
             torch.cuda.current_stream().synchronize()
         return out

@@ -29,6 +29,14 @@ def is_fp8_dtype(dt: torch.dtype) -> bool:
     return dt in (getattr(torch, "float8_e4m3fn", None), getattr(torch, "float8_e5m2", None))
 
 
+def is_s8_dtype(dt: torch.dtype) -> bool:
+    return dt == torch.int8
+
+
+def _is_8bit(dt: torch.dtype) -> bool:
+    return is_fp8_dtype(dt) or is_s8_dtype(dt)
+
+
 def _cur_stream() -> C.c_void_p:
     return C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
@@ -125,6 +133,7 @@ class DistEnvTPWithEP(DistEnvTP):
             import torch.distributed as dist
 
             self.ep_rank, self.ep_size = dist.get_rank(ep_group), dist.get_world_size(ep_group)
+        _check(self.world_size % self.ep_size == 0, "DistEnvTPWithEP: the EP size must divide the world size")
         self.ffn_tp_size = self.world_size // self.ep_size
         self.ffn_tp_rank = self.rank % self.ffn_tp_size
 
@@ -218,7 +227,7 @@ def _out_dtype(input_dtype: torch.dtype, output_dtype: Optional[torch.dtype]) ->
     # fp8 / int8 inputs produce bf16 (src/ag_gemm/ths_op/gemm_with_barrier.cc:184-185)
     if output_dtype is not None:
         return output_dtype
-    return torch.bfloat16 if is_fp8_dtype(input_dtype) else input_dtype
+    return torch.bfloat16 if _is_8bit(input_dtype) else input_dtype
 
 
 def _expand_scale(s: Optional[torch.Tensor], n: int, what: str) -> Optional[torch.Tensor]:
@@ -280,7 +289,7 @@ class AGKernel:
         if transpose_weight:
             # weight arrives as [K, N] ("RRR"); fp8 forbids it (src/ag_gemm/ths_op/gemm_with_barrier.cc:188,196-197).
             # The kernel reads it in place as an MN-major operand: no transposing copy.
-            _check(not is_fp8_dtype(self.input_dtype), "AGKernel: fp8 does not support transpose_weight")
+            _check(not _is_8bit(self.input_dtype), "AGKernel: 8-bit inputs do not support transpose_weight")
             flags |= _lib.WEIGHT_KN
         _check(input.is_contiguous(), "AGKernel: input must be contiguous")
         if not weight.is_contiguous():
@@ -371,8 +380,16 @@ class AGKernel:
 class GemmRS:
     """`flux.GemmRS(tp_group, nnodes, max_m, n_dim, input_dtype, output_dtype=None,
     transpose_weight=False, fuse_reduction=False, ring_reduction=False)` - reduce-scatter fused into
-    the GEMM epilogue (src/pybind/gemm_rs.cc:30-60). Partials are exchanged and summed in fp32, so
-    `fuse_reduction` / `ring_reduction` (bf16 summation orders of the reference) have nothing to select."""
+    the GEMM epilogue (src/pybind/gemm_rs.cc:30-60).
+
+    Partial products travel to the rank that owns their rows in the 16-bit output format (one rounding per
+    partial, as in the reference, whose reduce buffer has the output dtype) and are summed there in the order
+    rank+1, rank+2, ..., own partial last. By default the sum is kept in fp32 and rounded once;
+    `ring_reduction=True` rounds it to the element type after every addition, which is what the reference's
+    `ring_reduce` kernel computes (src/gemm_rs/ring_reduce.cu:54-80). `fuse_reduction` asks the reference for
+    an in-kernel reduction; here the reduction is always inside the kernel, so the flag changes nothing.
+    `fp32_wire = True` sends the partials as fp32 instead (no rounding before the sum, twice the NVLink bytes).
+    Rounding points against the 1e-2 tolerance: one per partial + one at the end (default)."""
 
     def __init__(self, tp_group, nnodes, max_m, n_dim, input_dtype, output_dtype=None, transpose_weight=False,
                  fuse_reduction=False, ring_reduction=False):
@@ -382,8 +399,8 @@ class GemmRS:
         self.input_dtype = input_dtype
         self.output_dtype = _out_dtype(input_dtype, output_dtype)
         self.transpose_weight = bool(transpose_weight)
-        # Partial sums travel to their owner in the 16-bit output format (as in the reference, which reduces
-        # in the output dtype); set to True to send them as fp32 at twice the NVLink bytes.
+        self.ring_reduction = bool(ring_reduction)
+        self.fuse_reduction = bool(fuse_reduction)
         self.fp32_wire = False
         lib = _lib.load()
         w = self.comm.world
@@ -413,10 +430,12 @@ class GemmRS:
         _check(output_scale is None, "GemmRS: output_scale is not supported")
         flags = 0
         if self.transpose_weight:
-            _check(not is_fp8_dtype(self.input_dtype), "GemmRS: fp8 does not support transpose_weight")
+            _check(not _is_8bit(self.input_dtype), "GemmRS: 8-bit inputs do not support transpose_weight")
             flags |= _lib.WEIGHT_KN  # [K, N] weight read in place as an MN-major operand
         if self.fp32_wire:
             flags |= _lib.RS_FP32_WIRE
+        if self.ring_reduction:
+            flags |= _lib.RS_RING_ORDER
         if not weight.is_contiguous():
             weight = weight.contiguous()
         _check(input.is_contiguous(), "GemmRS: input must be contiguous")
@@ -433,9 +452,14 @@ class GemmRS:
         if bias is not None:
             # fp8 rejects bias (gemm_reduce_scatter.cc:601-603)
             _check(not is_fp8_dtype(self.input_dtype), "GemmRS: fp8 does not support bias")
-            _check(tuple(bias.shape) == (m, n) and bias.dtype == self.output_dtype and bias.is_contiguous(),
-                   "GemmRS: bias must be a contiguous [M,N] tensor of the output dtype")
-            bias_mode = _lib.BIAS_MN
+            _check(bias.dtype == self.output_dtype and bias.is_contiguous(), "GemmRS: bias dtype/layout")
+            if tuple(bias.shape) == (m, n):
+                bias_mode = _lib.BIAS_MN
+            elif tuple(bias.shape) in ((1, n), (n,)):
+                # the int8 form: [1,N], applied by rank 0 only (gemm_reduce_scatter.cc:596-599)
+                bias_mode = _lib.BIAS_1N
+            else:
+                raise RuntimeError(f"GemmRS: bias shape {tuple(bias.shape)} is neither [M,N] nor [1,N]")
         sa = _expand_scale(input_scale, m, "input_scale")
         sb = _expand_scale(weight_scale, n, "weight_scale")
         out = torch.empty((m // w, n), dtype=self.output_dtype, device=input.device)
@@ -487,13 +511,13 @@ class GemmOnly:
     """`flux.GemmOnly(input_dtype, output_dtype=None, transpose_weight=False, use_fp8_gemm=False)`: the plain
     GEMM the reference uses as its unfused building block (src/pybind/gemm_only.cc; shapes and formulas in
     python/flux/cpp_mod.pyi:215-253): output = input[M,K] @ weight[N,K].T (weight [K,N] if transpose_weight),
-    fp8 with scalar or per-row / per-channel scales, bias [M,N] (16-bit) or [1,N]. Same kernel as the fused
-    ops, without communication. The int8 modes are not supported."""
+    fp8 with scalar or per-row / per-channel scales, int8 (w8a8) with per-row x per-channel dequantisation, bias [M,N]
+    (16-bit) or [1,N]. Same kernel as the fused ops, without communication."""
 
     def __init__(self, input_dtype, output_dtype=None, transpose_weight=False, use_fp8_gemm=False):
-        _check(input_dtype in (torch.bfloat16, torch.float16) or is_fp8_dtype(input_dtype),
-               f"GemmOnly: input dtype {input_dtype} is not supported (bf16, fp16, fp8 only)")
-        _check(not (transpose_weight and is_fp8_dtype(input_dtype)), "GemmOnly: fp8 does not support transpose_weight")
+        _check(input_dtype in (torch.bfloat16, torch.float16) or _is_8bit(input_dtype),
+               f"GemmOnly: input dtype {input_dtype} is not supported (bf16, fp16, fp8, int8)")
+        _check(not (transpose_weight and _is_8bit(input_dtype)), "GemmOnly: 8-bit inputs do not support transpose_weight")
         self.input_dtype = input_dtype
         self.output_dtype = _out_dtype(input_dtype, output_dtype)
         self.transpose_weight = bool(transpose_weight)

@@ -23,6 +23,7 @@ _TORCH_TO_FLUXB = {
     torch.bfloat16: _lib.BF16,
     torch.float16: _lib.F16,
     torch.float32: _lib.F32,
+    torch.int8: _lib.S8,
 }
 if hasattr(torch, "float8_e4m3fn"):
     _TORCH_TO_FLUXB[torch.float8_e4m3fn] = _lib.E4M3

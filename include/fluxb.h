@@ -40,6 +40,8 @@ extern "C" {
 #define FLUXB_F32 2
 #define FLUXB_E4M3 3
 #define FLUXB_E5M2 4
+#define FLUXB_S8 5 /* w8a8: int8 operands, int32 accumulation, output = (scale_a[m] * scale_b[n]) * acc in the 16-bit
+                      output type (AGS8KernelArguments, include/flux/args/ag_gemm.h:38-54) */
 
 /* bias layouts (src/ag_gemm/ths_op/gemm_with_barrier.cc:201-205) */
 #define FLUXB_BIAS_NONE 0
@@ -52,6 +54,11 @@ extern "C" {
 #define FLUXB_RS_FP32_WIRE 2 /* fluxb_gemm_rs_forward: send the partial sums to their owner as fp32 instead of
                                 the 16-bit output format (the reference reduces in the output format,
                                 src/gemm_rs/ths_op/gemm_reduce_scatter.cc:335-899); twice the NVLink bytes */
+
+#define FLUXB_RS_RING_ORDER 4 /* fluxb_gemm_rs_forward: reduce in the order and precision of the reference's
+                                `ring_reduction` (src/gemm_rs/ring_reduce.cu:54-80): partials of rank+1, rank+2, ...,
+                                own partial last, the running sum rounded to the 16-bit element type after every
+                                addition. Default: the same order, summed in fp32 and rounded once. */
 
 typedef struct fluxb_comm* fluxb_comm_t;
 typedef struct fluxb_ag_gemm* fluxb_ag_gemm_t;
@@ -209,6 +216,13 @@ int fluxb_moe_ag_scatter_destroy(fluxb_moe_ag_scatter_t op);
 /* GemmGroupedV3AGScatterOp::clear_buffers (src/moe_ag_scatter/ths_op/gemm_grouped_v3_ag_scatter.cc:112-126);
  * see fluxb_ag_gemm_reset. */
 int fluxb_moe_ag_scatter_reset(fluxb_moe_ag_scatter_t op, fluxb_stream_t stream);
+/* Expert parallelism (DistEnvTPWithEP with an ep_group, src/ths_op/ths_op.cc:334-346): the `world` ranks form
+ * ep_size groups of world / ep_size ranks; group ep_rank holds experts [ep_rank, ep_rank + 1) * nexperts / ep_size
+ * with the ffn dimension sharded over the ranks of the group (`ffn_local` = ffn / (world / ep_size)). Tokens are
+ * still gathered from all `world` ranks. After this call `weights` is [nexperts / ep_size, ffn_local, hidden] and
+ * `out` receives only the rows of this rank's experts, numbered from the first of them
+ * (python/flux/testing/moe_ag_scatter_utils.py:228-262). */
+int fluxb_moe_ag_scatter_set_ep(fluxb_moe_ag_scatter_t op, int ep_rank, int ep_size);
 int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_shard,
                                  int ntokens_local, const void* weights, const int* splits_dev,
                                  const int* scatter_index_dev, const float* out_scale, void* out,
@@ -262,6 +276,16 @@ int fluxb_moe_gather_rs_forward(fluxb_moe_gather_rs_t op, const void* x, int m, 
                                 const int* routing_idx_dev, const float* in_scale,
                                 const float* w_scale, const float* vec_scale, void* out,
                                 const fluxb_tuning* tuning, fluxb_stream_t stream);
+/* Expert parallelism (see fluxb_moe_ag_scatter_set_ep): `x` [m, k_local] and `vec_scale` [m] hold only the rows
+ * of this rank's experts (m = sum of their splits), `weights` is [nexperts / ep_size, n, k_local], `splits_host`
+ * and `routing_idx_dev` stay global ([nexperts] and [ntokens * topk]); every rank pushes its share of every
+ * token's top-k sum to the token's owner (python/flux/testing/moe_gather_rs_utils.py:26-125). */
+int fluxb_moe_gather_rs_set_ep(fluxb_moe_gather_rs_t op, int ep_rank, int ep_size);
+int fluxb_moe_gather_rs_forward_ep(fluxb_moe_gather_rs_t op, const void* x, int m, int ntokens, int k_local,
+                                   const void* weights, const int* splits_host,
+                                   const int* routing_idx_dev, const float* in_scale,
+                                   const float* w_scale, const float* vec_scale, void* out,
+                                   const fluxb_tuning* tuning, fluxb_stream_t stream);
 
 #ifdef __cplusplus
 }

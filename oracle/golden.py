@@ -73,7 +73,13 @@ def _ag_gemm_math(full_input, weight, bias, full_input_scale, weight_scale, out_
     """test/python/ag_gemm/test_ag_kernel.py:139-153: matmul with weight.t(), scales, cast, `+= bias`.
     fp8: operands are cast to bf16 and the product is multiplied by the scales (:119-124,:147);
     per-row x per-channel scales follow the int8 rule `full_input_scale * weight_scale * accum` (:143-145)."""
-    if is_fp8(full_input.dtype):
+    if full_input.dtype == torch.int8:
+        # w8a8 (:143-150): `accum = matmul_int8(full_input, weight.t()).to(float32)`,
+        # `output = full_input_scale * weight_scale * accum`, cast to bf16; the tests ask for a bitwise match
+        accum = torch.matmul(full_input.to(torch.int32), weight.to(torch.int32).t()).to(torch.float32)
+        out = full_input_scale.reshape(-1, 1).float() * weight_scale.reshape(1, -1).float() * accum
+        out = out.to(torch.bfloat16)
+    elif is_fp8(full_input.dtype):
         a = full_input.to(torch.bfloat16)
         w = weight.to(torch.bfloat16)
         out = torch.matmul(a, w.t()).float()
@@ -127,7 +133,11 @@ def ag_gemm_single(inputs: Sequence[torch.Tensor], weight, bias=None, input_scal
 # --------------------------------------------------------------------------- dense GEMM-RS
 def _rs_partial(input, weight, bias, input_scale, weight_scale):
     """test/python/gemm_rs/test_gemm_rs.py:113-135: matmul (fp8: scaled, bf16 out), `+= bias` on every rank."""
-    if is_fp8(input.dtype):
+    if input.dtype == torch.int8:
+        # :127-135: dequantised int8 product in the output dtype; the caller passes the bias on rank 0 only
+        accum = torch.matmul(input.to(torch.int32), weight.to(torch.int32).t()).to(torch.float32)
+        out = (input_scale.reshape(-1, 1).float() * weight_scale.reshape(1, -1).float() * accum).to(torch.bfloat16)
+    elif is_fp8(input.dtype):
         out = torch.matmul(input.to(torch.bfloat16), weight.to(torch.bfloat16).t()).float()
         if input_scale is not None:
             out = out * (input_scale.reshape(-1, 1).float() if input_scale.numel() > 1 else input_scale.float())
@@ -176,6 +186,18 @@ def gemm_rs_single(inputs, weights, biases=None, input_scales=None, weight_scale
     return [total[r * mpr:(r + 1) * mpr].contiguous() for r in range(world)]
 
 
+def ring_reduce_single(parts: Sequence[torch.Tensor], rank: int) -> torch.Tensor:
+    """src/gemm_rs/ring_reduce.cu:54-80 (`packed_ring_reduction`) for the rows of `rank`: a running sum in the
+    element dtype that starts at zero and adds the partials of rank+1, rank+2, ..., rank (own last), rounding
+    after every addition."""
+    world = len(parts)
+    mpr = parts[0].shape[0] // world
+    acc = torch.zeros_like(parts[0][:mpr])
+    for i in range(rank + 1, rank + 1 + world):
+        acc = acc + parts[i % world][rank * mpr:(rank + 1) * mpr]
+    return acc
+
+
 # --------------------------------------------------------------------------- MoE routing (integer, bit-exact)
 def calc_scatter_index_stable(chosen_experts: torch.Tensor) -> torch.Tensor:
     """python/flux/testing/moe_utils.py:141-144."""
@@ -209,20 +231,28 @@ def topk_routing(logits: torch.Tensor, topk: int) -> Tuple[torch.Tensor, torch.T
 
 
 # --------------------------------------------------------------------------- MoE layer 0
-def moe_ag_scatter_single(token_shards, weights, splits, scatter_index, output_scale=None, out_dtype=None):
-    """python/flux/testing/moe_ag_scatter_utils.py:195-262 (`comm_impl`, `scatter_impl`, `gemm_impl`), EP=1:
+def moe_ag_scatter_single(token_shards, weights, splits, scatter_index, output_scale=None, out_dtype=None,
+                          ep_rank: int = 0, ep_size: int = 1):
+    """python/flux/testing/moe_ag_scatter_utils.py:195-262 (`comm_impl`, `scatter_impl`, `gemm_impl`):
     all_gather tokens -> index_select(gather_index) -> per-expert matmul with W[e].t() -> `mul_(output_scale[e])`.
-    `weights` is this rank's [E, ffn_local, hidden]. Returns (out [T*topk, ffn_local], gathered tokens)."""
+    `weights` is this rank's [E / ep_size, ffn_local, hidden]; with expert parallelism only the experts
+    [ep_rank, ep_rank + 1) * E / ep_size are computed, from the rows `input_offset = sum(splits[:first expert])`
+    onwards (:228-236), and the output holds just those rows. Returns (out, gathered tokens)."""
     full = torch.cat(list(token_shards), dim=0)
     gather_index, _ = calc_gather_index(scatter_index.cpu())
     scat = torch.index_select(full, 0, gather_index.long().to(full.device))
     od = out_dtype or full.dtype
-    out = torch.zeros((scat.shape[0], weights.shape[1]), dtype=od, device=full.device)
+    e_local = weights.shape[0]
+    e_first = e_local * ep_rank
+    assert e_local * ep_size == len(splits)
+    input_offset = int(sum(int(x) for x in splits[:e_first]))
+    nrows = int(sum(int(x) for x in splits[e_first:e_first + e_local]))
+    out = torch.zeros((nrows, weights.shape[1]), dtype=od, device=full.device)
     off = 0
-    for e in range(weights.shape[0]):
-        nxt = off + int(splits[e])
+    for e in range(e_local):
+        nxt = off + int(splits[e + e_first])
         if nxt > off:
-            o = torch.matmul(scat[off:nxt], weights[e].t())
+            o = torch.matmul(scat[off + input_offset:nxt + input_offset], weights[e].t())
             if output_scale is not None:
                 o = o * output_scale[e]
             out[off:nxt] = o.to(od)
@@ -232,15 +262,21 @@ def moe_ag_scatter_single(token_shards, weights, splits, scatter_index, output_s
 
 # --------------------------------------------------------------------------- MoE layer 1
 def moe_gather_rs_partial(x, weights, splits, scatter_index, topk, input_scale=None, weight_scale=None,
-                          output_vec_scale=None):
+                          output_vec_scale=None, ep_rank: int = 0, ep_size: int = 1):
     """One rank's contribution before the reduce-scatter
     (python/flux/testing/moe_gather_rs_utils.py:26-101): per-expert matmul * (weight_scale[e] * input_scale),
-    `* output_vec_scale`, cast, rows placed at `topk * token + k`, `.view(T, topk, N).sum(1)`."""
+    `* output_vec_scale`, cast, rows placed at `topk * token + k`, `.view(T, topk, N).sum(1)`. With expert
+    parallelism `x` / `weights` hold this rank's experts only (`eid_start`, `ep_rank_m_start:ep_rank_m_end`,
+    :70,:102-105) and the rows of other ranks' experts stay zero."""
     n = weights.shape[1]
+    e_first = weights.shape[0] * ep_rank
+    assert weights.shape[0] * ep_size == len(splits)
+    m_start = int(sum(int(v) for v in splits[:e_first]))
+    total_rows = int(sum(int(v) for v in splits))
     out_list = []
     acc = 0
     for e in range(weights.shape[0]):
-        mi = int(splits[e])
+        mi = int(splits[e + e_first])
         xe = x[acc:acc + mi]
         acc += mi
         sv = 1.0
@@ -252,16 +288,17 @@ def moe_gather_rs_partial(x, weights, splits, scatter_index, topk, input_scale=N
         output = output * output_vec_scale.unsqueeze(1)
     output = output.to(x.dtype)
     gather_index, topk_index = calc_gather_index(scatter_index.cpu())
-    new_index = (topk * gather_index.long() + topk_index.long()).to(x.device)
-    full = torch.zeros((x.shape[0], n), dtype=x.dtype, device=x.device)
+    new_index = (topk * gather_index.long() + topk_index.long())[m_start:m_start + x.shape[0]].to(x.device)
+    full = torch.zeros((total_rows, n), dtype=x.dtype, device=x.device)
     full[new_index] = output
     return full.view(full.shape[0] // topk, topk, n).sum(1)
 
 
 def moe_gather_rs_single(xs, weights_per_rank, splits, scatter_index, topk, input_scales=None, weight_scales=None,
-                         output_vec_scales=None) -> List[torch.Tensor]:
+                         output_vec_scales=None, ep_size: int = 1) -> List[torch.Tensor]:
     """All ranks in one process; reduce_scatter_tensor (moe_gather_rs_utils.py:111-119) = fp32 sum of the
-    per-rank partials in rank order, one rounding, row slice."""
+    per-rank partials in rank order, one rounding, row slice. With expert parallelism rank r belongs to expert
+    group r // (world / ep_size)."""
     world = len(xs)
     parts = [
         moe_gather_rs_partial(
@@ -269,6 +306,7 @@ def moe_gather_rs_single(xs, weights_per_rank, splits, scatter_index, topk, inpu
             None if input_scales is None else input_scales[r],
             None if weight_scales is None else weight_scales[r],
             None if output_vec_scales is None else output_vec_scales[r],
+            ep_rank=r // (world // ep_size), ep_size=ep_size,
         )
         for r in range(world)
     ]

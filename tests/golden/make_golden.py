@@ -117,6 +117,81 @@ def gen_moe_l0(ag, moe_utils):
     print("moe_l0.pt:", len(cases), "cases")
 
 
+def gen_moe_l0_ep(ag, moe_utils):
+    """Layer 0 with expert parallelism: the reference's gemm_impl for every ep_rank of ep_size = 2 (each rank holds
+    half of the experts and produces only their rows)."""
+    cases = []
+    ntokens, topk, nexperts, hidden, ffn, dtype, ep_size = 48, 2, 8, 64, 40, torch.bfloat16, 2
+    g = torch.Generator().manual_seed(230)
+    scores = torch.rand(ntokens, nexperts, generator=g)
+    chosen = torch.topk(scores, topk, dim=-1).indices.to(torch.int32)
+    scatter = moe_utils.calc_scatter_index_stable(chosen)
+    splits = torch.bincount(chosen.view(-1), minlength=nexperts).to(torch.int32)
+    inv = torch.empty(ntokens * topk, dtype=torch.int64)
+    inv[scatter.view(-1).long()] = torch.arange(ntokens * topk) // topk
+    tokens = torch.randn(ntokens, hidden, generator=g).to(dtype)
+    e_local = nexperts // ep_size
+    for ep_rank in range(ep_size):
+        weights = (torch.randn(e_local, ffn, hidden, generator=g) * 0.05).to(dtype)
+        out_scale = torch.rand(e_local, generator=g) + 0.5
+        nrows = int(splits[ep_rank * e_local:(ep_rank + 1) * e_local].sum())
+        ctx = types.SimpleNamespace(
+            inputs=tokens, scatter_inputs=torch.zeros(ntokens * topk, hidden, dtype=dtype), gather_index=inv,
+            is_s8=False, input_scale=None, weight_groups=1, nexperts_ep=e_local, ep_rank=ep_rank,
+            splits_cpu=splits, outputs=[torch.zeros(nrows, ffn, dtype=dtype)], weights=[weights],
+            fast_accum=False, bias=None, output_scale=[out_scale],
+        )
+        ag.MoeAgScatterWithTorch.scatter_impl(ctx)
+        ag.MoeAgScatterWithTorch.gemm_impl(ctx, None)
+        cases.append({"tokens": tokens, "weights": weights, "splits": splits, "scatter_index": scatter,
+                      "output_scale": out_scale, "ep_rank": ep_rank, "ep_size": ep_size, "out": ctx.outputs[0].clone()})
+    torch.save(cases, HERE / "moe_l0_ep.pt")
+    print("moe_l0_ep.pt:", len(cases), "cases")
+
+
+def _l1_ep_worker(rank, world, port, ref_root, out_path):
+    """Layer 1 with expert parallelism on 2 gloo ranks: ffn TP size 1, EP size 2 (rank = ep_rank)."""
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    _, moe_utils, _, rs = load_reference_helpers(Path(ref_root))
+    ntokens, topk, nexperts, kloc, n, dtype = 32, 2, 8, 48, 40, torch.bfloat16
+    g = torch.Generator().manual_seed(330)
+    chosen = torch.topk(torch.rand(ntokens, nexperts, generator=g), topk, dim=-1).indices.to(torch.int32)
+    scatter = moe_utils.calc_scatter_index_stable(chosen)
+    splits = torch.bincount(chosen.view(-1), minlength=nexperts).to(torch.int32)
+    order = chosen.flatten().sort(stable=True).indices
+    token_index = (order // topk).to(torch.int32)
+    topk_index = torch.arange(topk, dtype=torch.int32).repeat(ntokens)[order]
+    e_local = nexperts // world
+    eid_start = rank * e_local
+    m_start = int(splits[:eid_start].sum())
+    m_end = m_start + int(splits[eid_start:eid_start + e_local].sum())
+    gr = torch.Generator().manual_seed(340 + rank)
+    x = torch.randn(m_end - m_start, kloc, generator=gr).to(dtype)
+    w = (torch.randn(e_local, n, kloc, generator=gr) * 0.05).to(dtype)
+    vec = torch.rand(m_end - m_start, generator=gr) + 0.25
+    full = rs.moe_gather_rs_forward_torch(
+        dist.group.WORLD, ntokens * topk, eid_start, m_start, m_end, x, w, splits, token_index, topk_index, topk,
+        torch.ones(1), torch.ones(e_local), vec, do_all_reduce=True,
+    )
+    tpr = ntokens // world
+    mine = {"x": x, "w": w, "vec": vec, "out": full[rank * tpr:(rank + 1) * tpr].clone()}
+    gathered = [None] * world
+    dist.all_gather_object(gathered, mine)
+    if rank == 0:
+        torch.save({"topk": topk, "scatter_index": scatter, "splits": splits, "ep_size": world, "ranks": gathered}, out_path)
+    dist.destroy_process_group()
+
+
+def gen_moe_l1_ep(ref_root):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    mp.spawn(_l1_ep_worker, args=(2, port, str(ref_root), str(HERE / "moe_l1_ep.pt")), nprocs=2, join=True)
+    print("moe_l1_ep.pt: 1 case")
+
+
 # ----------------------------------------------------------------------------- MoE layer 1 (2 gloo ranks)
 def _l1_inputs(rank, case):
     ntokens, topk, nexperts, kloc, n, dtype = case
@@ -281,9 +356,14 @@ def gen_dense(ref_root):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of a checkout of the reference")
+    ap.add_argument("--only-ep", action="store_true", help="only the expert-parallel MoE vectors")
     args = ap.parse_args()
     ref_root = Path(args.reference)
     _, moe_utils, ag, _ = load_reference_helpers(ref_root)
+    gen_moe_l0_ep(ag, moe_utils)
+    gen_moe_l1_ep(ref_root)
+    if args.only_ep:
+        return
     gen_routing(moe_utils)
     gen_moe_l0(ag, moe_utils)
     gen_moe_l1(ref_root)

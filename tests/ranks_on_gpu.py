@@ -104,7 +104,9 @@ class Ranks:
                 _p(scales_a[r]) if scales_a else None, _p(scales_b[r]) if scales_b else None, 1.0, flags, tun, _stream()))
         self.run()
 
-    def moe_ops(self, max_ntokens, hidden, ffn_local, nexperts, topk, dtype):
+    def moe_ops(self, max_ntokens, hidden, ffn_local, nexperts, topk, dtype, ep_size=1):
+        """Layer-0 and layer-1 op handles of every rank; with ep_size > 1 rank r belongs to expert group
+        r // (n / ep_size) and `ffn_local` is the ffn share inside a group."""
         lib = self.lib
         dt = fluxb_dtype(dtype)
         _, gt = self.symm(lib.fluxb_ag_gemm_gather_bytes(max_ntokens, hidden, dt))
@@ -124,6 +126,9 @@ class Ranks:
                                                        gt, ft, _p(ws0), C.byref(h0)))
             _lib.check(lib.fluxb_moe_gather_rs_create(self.comms[r], nexperts, max_m, hidden, topk, dt, dt, st, ct, _p(ws1),
                                                       C.byref(h1)))
+            if ep_size > 1:
+                _lib.check(lib.fluxb_moe_ag_scatter_set_ep(h0, r // (self.n // ep_size), ep_size))
+                _lib.check(lib.fluxb_moe_gather_rs_set_ep(h1, r // (self.n // ep_size), ep_size))
             l0.append(h0)
             l1.append(h1)
         return l0, l1
@@ -138,10 +143,15 @@ class Ranks:
                 _p(out_scales[r]) if out_scales else None, _p(outs[r]), _p(gathered[r]) if gathered else None, tun, _stream()))
         self.run()
 
-    def moe_l1_forward(self, ops, xs, weights, splits_cpu, routing_idx, outs, vec_scale=None):
-        m, k_local = xs[0].shape
+    def moe_l1_forward(self, ops, xs, weights, splits_cpu, routing_idx, outs, vec_scale=None, vec_scales=None):
+        """`vec_scale`: one row-scale vector for every rank; `vec_scales`: one per rank (expert parallelism: every
+        rank holds different rows)."""
+        topk = routing_idx.numel() // (outs[0].shape[0] * self.n)
+        ntokens = routing_idx.numel() // topk
         for r in range(self.n):
-            _lib.check(self.lib.fluxb_moe_gather_rs_forward(
-                ops[r], _p(xs[r]), m, k_local, _p(weights[r]), C.c_void_p(splits_cpu.data_ptr()), _p(routing_idx), None, None,
-                _p(vec_scale), _p(outs[r]), None, _stream()))
+            m, k_local = xs[r].shape
+            vs = vec_scales[r] if vec_scales is not None else vec_scale
+            _lib.check(self.lib.fluxb_moe_gather_rs_forward_ep(
+                ops[r], _p(xs[r]), m, ntokens, k_local, _p(weights[r]), C.c_void_p(splits_cpu.data_ptr()), _p(routing_idx),
+                None, None, _p(vs), _p(outs[r]), None, _stream()))
         self.run()

@@ -52,6 +52,29 @@ def test_gemm_only_matches_oracle(flux, m, n, k, dtype):
     assert golden.max_rel_err(out, ref) <= BF16_TOL
 
 
+@pytest.mark.parametrize("m,n,k,cta_group", [(256, 264, 512, 1), (512, 520, 1024, 2), (200, 72, 136 * 2, 1), (1024, 1536, 4096, 2)])
+def test_int8_gemm_is_bit_identical_to_the_golden_path(flux, m, n, k, cta_group):
+    """w8a8: int8 x int8 -> int32 on the tensor cores (tcgen05 kind::i8), dequantised as
+    (input_scale[m] * weight_scale[n]) * acc, rounded to bf16, then `+= bias` in bf16; the reference's test asks for
+    a bitwise match (threshold 0, test/python/ag_gemm/test_ag_kernel.py:143-150,615)."""
+    g = torch.Generator().manual_seed(m + n)
+    a = torch.randint(-127, 128, (m, k), generator=g, dtype=torch.int32).to(torch.int8)
+    b = torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int32).to(torch.int8)
+    sa = torch.rand(m, 1, generator=g) * 0.01 + 0.001
+    sb = torch.rand(1, n, generator=g) * 0.01 + 0.001
+    bias = (torch.randn(1, n, generator=g) * 0.5).to(torch.bfloat16)
+    op = flux.GemmOnly(torch.int8)
+    for with_bias in (False, True):
+        out = op.forward(a.cuda(), b.cuda(), bias=bias.cuda() if with_bias else None, input_scale=sa.cuda(),
+                         weight_scale=sb.cuda(), tuning={"cta_group": cta_group})
+        torch.cuda.synchronize()
+        op.comm.check_status()
+        ref, _ = golden.ag_gemm_single([a], b, bias=bias if with_bias else None, input_scales=[sa], weight_scale=sb)
+        assert out.dtype == torch.bfloat16
+        assert torch.equal(out.cpu().view(torch.int16), ref.view(torch.int16)), \
+            f"not bit-identical (bias {with_bias}): max rel err {golden.max_rel_err(out, ref)}"
+
+
 @pytest.mark.parametrize("block_n", [64, 128, 192, 256])
 @pytest.mark.parametrize("group_m", [1, 3, 16])
 def test_gemm_tile_configs(flux, block_n, group_m):

@@ -62,8 +62,9 @@ def test_dtype_codes():
     from flux_b200.shm import fluxb_dtype
 
     assert fluxb_dtype(torch.bfloat16) == _lib.BF16 and fluxb_dtype(torch.float8_e4m3fn) == _lib.E4M3
+    assert fluxb_dtype(torch.int8) == _lib.S8  # w8a8
     with pytest.raises(RuntimeError):
-        fluxb_dtype(torch.int8)
+        fluxb_dtype(torch.int64)
 
 
 def test_ops_fail_loudly_without_a_gpu():
@@ -87,14 +88,17 @@ def test_build_recipe_lists_every_source():
 
 
 def test_gemm_only_rejects_unsupported_modes():
-    """GemmOnly's int8 modes and fp8 with transposed weights are refused at construction
-    (python/flux/cpp_mod.pyi:215-253 lists the modes; src/ag_gemm/ths_op/gemm_with_barrier.cc:188 the fp8 rule)."""
+    """Input types outside bf16 / fp16 / fp8 / int8 and 8-bit inputs with transposed weights are refused at
+    construction, before any device is touched (python/flux/cpp_mod.pyi:215-253 lists the modes;
+    src/ag_gemm/ths_op/gemm_with_barrier.cc:188 the fp8 rule)."""
     import pytest
     import torch
 
     import flux_b200 as flux
 
-    with pytest.raises(RuntimeError):
-        flux.GemmOnly(torch.int8)
-    with pytest.raises(RuntimeError):
+    with pytest.raises(RuntimeError, match="not supported"):
+        flux.GemmOnly(torch.int32)
+    with pytest.raises(RuntimeError, match="transpose_weight"):
         flux.GemmOnly(torch.float8_e4m3fn, transpose_weight=True)
+    with pytest.raises(RuntimeError, match="transpose_weight"):
+        flux.GemmOnly(torch.int8, transpose_weight=True)

@@ -64,6 +64,26 @@ def test_moe_l1_matches_reference_vectors():
             assert golden.max_rel_err(o, ref) <= tol
 
 
+# ------------------------------------------------------------------ pinned: expert parallelism
+def test_moe_expert_parallel_matches_reference_vectors():
+    """The reference's golden path with ep_size = 2 (tests/golden/make_golden.py --only-ep): layer 0 computes only the
+    rows of the rank's experts; layer 1 scatters them into the full result, the reduce-scatter adds the ranks."""
+    for case in _load("moe_l0_ep.pt"):
+        out, _ = golden.moe_ag_scatter_single(
+            [case["tokens"]], case["weights"], case["splits"], case["scatter_index"], case["output_scale"],
+            ep_rank=case["ep_rank"], ep_size=case["ep_size"])
+        assert out.shape == case["out"].shape and torch.equal(out, case["out"])
+    case = _load("moe_l1_ep.pt")
+    ranks = case["ranks"]
+    e_local = ranks[0]["w"].shape[0]
+    outs = golden.moe_gather_rs_single(
+        [r["x"] for r in ranks], [r["w"] for r in ranks], case["splits"], case["scatter_index"], case["topk"],
+        input_scales=[torch.ones(1)] * len(ranks), weight_scales=[torch.ones(e_local)] * len(ranks),
+        output_vec_scales=[r["vec"] for r in ranks], ep_size=case["ep_size"])
+    for r, o in enumerate(outs):
+        assert golden.max_rel_err(o, ranks[r]["out"]) <= 1e-2
+
+
 # ------------------------------------------------------------------ known answers of the --debug inputs
 def test_ag_gemm_debug_known_answer():
     """test/python/ag_gemm/test_ag_kernel.py:670-678: input zero except column 0 = rank+1, weight = 1

@@ -14,7 +14,7 @@ import pytest
 import torch
 
 sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
-from ranks_on_gpu import Ranks  # noqa: E402
+from ranks_on_gpu import Ranks, _stream  # noqa: E402
 
 from oracle import golden  # noqa: E402
 
@@ -130,6 +130,100 @@ def test_fp8_all_ranks_on_one_gpu(ag_mode):
         rk.close()
 
 
+def _int8_inputs(world, m_rows, n, k, seed):
+    xs, ws, sxs, sws = [], [], [], []
+    for r in range(world):
+        g = torch.Generator().manual_seed(seed + r)
+        xs.append(torch.randint(-127, 128, (m_rows, k), generator=g, dtype=torch.int32).to(torch.int8))
+        ws.append(torch.randint(-127, 128, (n, k), generator=g, dtype=torch.int32).to(torch.int8))
+        sxs.append(torch.rand(m_rows, 1, generator=g) * 0.01 + 0.001)
+        sws.append(torch.rand(1, n, generator=g) * 0.01 + 0.001)
+    return xs, ws, sxs, sws
+
+
+@pytest.mark.parametrize("ag_mode", [1, 2])
+def test_int8_ag_gemm_bitwise_all_ranks_on_one_gpu(ag_mode):
+    """w8a8 AG-GEMM: int8 operands, int32 accumulation, per-row x per-channel dequantisation, bias [1,N]. The
+    reference's test demands a bitwise match with its golden path (test/python/ag_gemm/test_ag_kernel.py:615)."""
+    world, m_local, n, k = 4, 256, 392, 1024
+    rk = Ranks(world)
+    try:
+        xs, ws, sxs, sws = _int8_inputs(world, m_local, n, k, 31)
+        g = torch.Generator().manual_seed(9)
+        biases = [(torch.randn(1, n, generator=g) * 0.5).to(BF16) for _ in range(world)]
+        ops = rk.ag_gemm_ops(m_local * world, n, k, torch.int8, BF16, with_scales=True)
+        outs = [torch.empty((m_local * world, n), dtype=BF16, device="cuda") for _ in range(world)]
+        for with_bias in (False, True):
+            rk.ag_gemm_forward(ops, [x.cuda() for x in xs], [w.cuda() for w in ws], outs,
+                               biases=[b.cuda() for b in biases] if with_bias else None, bias_mode=2 if with_bias else 0,
+                               scales_a=[s.reshape(-1).cuda() for s in sxs], scales_b=[s.reshape(-1).cuda() for s in sws],
+                               tuning={"ag_mode": ag_mode})
+            for r in range(world):
+                ref, _ = golden.ag_gemm_single(xs, ws[r], bias=biases[r] if with_bias else None, input_scales=sxs,
+                                               weight_scale=sws[r])
+                assert torch.equal(outs[r].cpu().view(torch.int16), ref.view(torch.int16)), \
+                    f"int8 AG-GEMM rank {r} bias {with_bias}: not bit-identical to the golden path " \
+                    f"(max rel err {golden.max_rel_err(outs[r], ref)})"
+    finally:
+        rk.close()
+
+
+def test_int8_gemm_rs_all_ranks_on_one_gpu():
+    """w8a8 GEMM-RS: every rank's dequantised partial in bf16, bias [1,N] on rank 0 only
+    (src/gemm_rs/ths_op/gemm_reduce_scatter.cc:596-599), reduce-scatter."""
+    world, m, n, k_local = 4, 512, 264, 512
+    rk = Ranks(world)
+    try:
+        xs, ws, sxs, sws = _int8_inputs(world, m, n, k_local, 77)
+        g = torch.Generator().manual_seed(10)
+        bias = (torch.randn(1, n, generator=g) * 0.5).to(BF16)
+        ops = rk.gemm_rs_ops(m, n, torch.int8, BF16)
+        outs = [torch.empty((m // world, n), dtype=BF16, device="cuda") for _ in range(world)]
+        from flux_b200 import _lib
+
+        d_x, d_w = [x.cuda() for x in xs], [w.cuda() for w in ws]
+        d_sx, d_sw = [s.reshape(-1).cuda() for s in sxs], [s.reshape(-1).cuda() for s in sws]
+        d_bias = bias.cuda()
+        for r in range(world):  # every rank passes the bias; only rank 0 applies it
+            _lib.check(rk.lib.fluxb_gemm_rs_forward(
+                ops[r], d_x[r].data_ptr(), d_w[r].data_ptr(), m, n, k_local, outs[r].data_ptr(), d_bias.data_ptr(),
+                _lib.BIAS_1N, d_sx[r].data_ptr(), d_sw[r].data_ptr(), 1.0, 0, None, _stream()))
+        rk.run()
+        refs = golden.gemm_rs_single(xs, ws, [bias if r == 0 else None for r in range(world)], sxs, sws)
+        for r in range(world):
+            # the reference's own bar for w8a8 GEMM-RS is 2e-1 elementwise (test/python/gemm_rs/test_gemm_rs.py:593);
+            # the rounding points are the golden path's, so nearly every element is bit-identical as well
+            _close(outs[r], refs[r], 1e-2, 2e-1, f"int8 GEMM-RS rank {r}")
+            same = (outs[r].cpu().view(torch.int16) == refs[r].view(torch.int16)).float().mean().item()
+            assert same >= 0.99, f"rank {r}: only {same:.4f} of the elements are bit-identical to the golden path"
+    finally:
+        rk.close()
+
+
+def test_gemm_rs_ring_reduction_all_ranks_on_one_gpu():
+    """`ring_reduction`: partials summed in the order rank+1, ..., own last, rounded to bf16 after every addition
+    (src/gemm_rs/ring_reduce.cu:54-80)."""
+    from flux_b200 import _lib
+
+    world, m, n, k_local = 4, 1024, 520, 256
+    rk = Ranks(world)
+    try:
+        ab = [_cpu_inputs(r, m, n, k_local, BF16, 2468) for r in range(world)]
+        ops = rk.gemm_rs_ops(m, n, BF16, BF16)
+        outs = [torch.empty((m // world, n), dtype=BF16, device="cuda") for _ in range(world)]
+        rk.gemm_rs_forward(ops, [a.cuda() for a, _ in ab], [b.cuda() for _, b in ab], outs, flags=_lib.RS_RING_ORDER)
+        parts = [golden._rs_partial(a, b, None, None, None) for a, b in ab]
+        for r in range(world):
+            ref = golden.ring_reduce_single(parts, r)
+            _close(outs[r], ref, 1e-2, 2e-2, f"ring-order GEMM-RS rank {r}")
+            # the roundings are the reference's: nearly every element is bit-identical (the partials themselves may
+            # differ in their last bit, because the GPU accumulates K in another order than the CPU matmul)
+            same = (outs[r].cpu().view(torch.int16) == ref.view(torch.int16)).float().mean().item()
+            assert same >= 0.95, f"rank {r}: only {same:.3f} of the elements match the ring reduction bit for bit"
+    finally:
+        rk.close()
+
+
 @pytest.mark.parametrize("ag_mode", [1, 2])
 @pytest.mark.parametrize("world", [2, 4])
 def test_moe_all_ranks_on_one_gpu(world, ag_mode):
@@ -172,6 +266,56 @@ def test_moe_all_ranks_on_one_gpu(world, ag_mode):
             refs1 = golden.moe_gather_rs_single(ref0, w1s, splits, si, topk, output_vec_scales=[vec] * world)
             for r in range(world):
                 _close(out1[r], refs1[r], 2e-2, 2e-2, f"MoE layer 1 world {world} call {it} rank {r}")
+    finally:
+        rk.close()
+
+
+@pytest.mark.parametrize("world,ep_size", [(4, 2), (4, 4), (2, 2)])
+def test_moe_expert_parallel_all_ranks_on_one_gpu(world, ep_size):
+    """TP x EP (DistEnvTPWithEP with an ep_group, src/ths_op/ths_op.cc:334-346): `ep_size` groups of world / ep_size
+    ranks; a group holds nexperts / ep_size experts with the ffn dimension sharded inside the group. Tokens are gathered
+    from all ranks; layer 0 produces only the rows of the rank's experts, layer 1 combines every rank's share."""
+    ntokens, topk, nexperts, hidden = 128 * world, 2, 8, 256
+    ffn_tp = world // ep_size
+    ffn_local, e_local = 128, nexperts // ep_size
+    rk = Ranks(world)
+    try:
+        l0, l1 = rk.moe_ops(ntokens, hidden, ffn_local, nexperts, topk, BF16, ep_size=ep_size)
+        for it in range(2):
+            g = torch.Generator().manual_seed(4321 + it)
+            logits = torch.randn(ntokens, nexperts, generator=g)
+            if it == 1:
+                logits[:, 5] = -1e9  # an expert that receives no tokens
+            chosen, rw = golden.topk_routing(logits, topk)
+            si = golden.calc_scatter_index_stable(chosen)
+            splits = golden.calc_splits(chosen, nexperts)
+            gi, ti = golden.calc_gather_index(si)
+            vec_all = rw.reshape(-1)[(gi.long() * topk + ti.long())].contiguous()
+            toks, w0s, w1s, ref0, vecs = [], [], [], [], []
+            for r in range(world):
+                gr = torch.Generator().manual_seed(555 + r + 9 * it)
+                toks.append(torch.randn(ntokens // world, hidden, generator=gr).to(BF16))
+                w0s.append((torch.randn(e_local, ffn_local, hidden, generator=gr) * 0.02).to(BF16))
+                w1s.append((torch.randn(e_local, hidden, ffn_local, generator=gr) * 0.02).to(BF16))
+            out0 = []
+            for r in range(world):
+                ep_rank = r // ffn_tp
+                ref, _ = golden.moe_ag_scatter_single(toks, w0s[r], splits, si, None, ep_rank=ep_rank, ep_size=ep_size)
+                ref0.append(ref)
+                m_start = int(splits[:ep_rank * e_local].sum())
+                vecs.append(vec_all[m_start:m_start + ref.shape[0]].contiguous())
+                out0.append(torch.full((max(ref.shape[0], 1), ffn_local), float("nan"), dtype=BF16, device="cuda"))
+            rk.moe_l0_forward(l0, [t.cuda() for t in toks], [w.cuda() for w in w0s], splits.cuda(), si.cuda(), out0)
+            for r in range(world):
+                if ref0[r].shape[0] > 0:
+                    _close(out0[r][:ref0[r].shape[0]], ref0[r], 1e-2, 1e-2, f"EP layer 0 world {world} ep {ep_size} call {it} rank {r}")
+            out1 = [torch.empty((ntokens // world, hidden), dtype=BF16, device="cuda") for _ in range(world)]
+            d_x = [x.cuda() if x.shape[0] > 0 else torch.zeros((1, ffn_local), dtype=BF16, device="cuda")[:0] for x in ref0]
+            rk.moe_l1_forward(l1, d_x, [w.cuda() for w in w1s], splits, si.reshape(-1).cuda(), out1,
+                              vec_scales=[v.cuda() for v in vecs])
+            refs1 = golden.moe_gather_rs_single(ref0, w1s, splits, si, topk, output_vec_scales=vecs, ep_size=ep_size)
+            for r in range(world):
+                _close(out1[r], refs1[r], 2e-2, 2e-2, f"EP layer 1 world {world} ep {ep_size} call {it} rank {r}")
     finally:
         rk.close()
 
