@@ -573,6 +573,7 @@ def run_ours(args):
 
     flux.init_flux_shm(group)
     comm = flux.get_comm(group)
+    comm.set_timeout_ms(3000)  # a device wait that runs out ends its call after 3 s (default 10 s)
     a, b0, b1 = _make_inputs(rank, world)
     ag = flux.AGKernel(group, 1, M, N0 // world, K0, torch.bfloat16)
     rs = flux.GemmRS(group, 1, M, N1, torch.bfloat16)
@@ -691,12 +692,13 @@ def run_ours(args):
     try:
         if world > 1:
             meas["nvlink"] = {
-                "ag_gemm": _nvlink_from_trace(comm, lambda: ag.forward(a, b0, output=c0), 4,
+                "ag_gemm": _nvlink_from_trace(comm, lambda: ag.forward(a, b0, output=c0, tuning={"ag_mode": 1}), 4,
                                               (world - 1) * (M // world) * K0 * 2, world, barrier),
                 "gemm_rs": _nvlink_from_trace(comm, lambda: rs.forward(c0, b1), 3,
                                               (world - 1) * (M // world) * N1 * 2, world, barrier),
-                "what": "bytes this GPU sends (AG: its shard to every peer; RS: bf16 partials to every owner) / time "
-                        "from the first CTA's start to the last push (per-CTA %globaltimer stamps), max over ranks"}
+                "what": "bytes this GPU sends (AG: its shard to every peer, pushed by the kernel's comm warps; RS: bf16 "
+                        "partials to every owner, spread over the whole kernel by design) / time from the first CTA's "
+                        "start to the last push (per-CTA %globaltimer stamps), max over ranks"}
         else:
             meas["nvlink"] = {"note": "TP=1: nothing crosses NVLink"}
     except Exception as exc:
@@ -888,6 +890,7 @@ def run_secondary(args):
 
     flux.init_flux_shm(group)
     comm = flux.get_comm(group)
+    comm.set_timeout_ms(3000)
     if args.workload == "moe":
         res = moe_leg(flux, comm, group, rank, world, args.steps, args.warmup)
         metric = "MoE MLP (AG+scatter grouped GEMM, grouped GEMM+gather-RS) aggregate TFLOP/s"

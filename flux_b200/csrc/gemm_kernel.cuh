@@ -70,6 +70,9 @@ struct GemmParams {
   CUtensorMap tmap_a;
   CUtensorMap tmap_b;
   CUtensorMap tmap_a_own;  // all-gather: this rank's own shard, read in place (valid if a_own_valid)
+  CUtensorMap tmap_out;    // 16-bit output [rows, N] as 32-row x 64-column boxes (valid if tmap_out_valid): full
+                           // 32-row groups of a tile leave through shared memory and one tiled store per box
+  int tmap_out_valid;
   int a_own_valid;
   int b_mn_major;  // 1: B is stored [K, N] (N contiguous), loaded as 64-column boxes (16-bit inputs only)
   int acc_int;     // 1: 8-bit operands are signed integers and the accumulator is int32 (w8a8 with dequantisation)
@@ -78,6 +81,7 @@ struct GemmParams {
   // segment; segments are visited (seg_first + i) % nseg.
   int nseg, seg_rows, seg_first;
   int group_m;  // rasterisation band height in M tiles (uniform bands, used when n_bands == 0)
+  int n_group;  // > 0: tile columns are visited in groups of this many (all M tiles of a group before the next group)
   int rs_wire16;  // reduce-scatter partials cross NVLink in the 16-bit output format instead of fp32
   int rs_ring;    // with rs_wire16: every addition of the reduction is rounded to the 16-bit type, own partial last
   int n_bands;  // > 0: explicit bands, band b covers M tiles [band_end[b-1], band_end[b])
@@ -139,6 +143,7 @@ struct GemmParams {
   const int* g_row_range;         // device [2]: rows [lo, hi) of the sorted order that this rank computes (expert
                                   // parallelism: the rows of its experts); null = all rows. Row lo is row 0 of g_sorted.
   const uint8_t* g_tokens;        // gathered tokens [tokens, K] (this rank's gather buffer, or the input at world 1)
+  const uint8_t* g_tokens_own;    // this rank's own token shard, read in place (no copy to itself, no wait); null = in g_tokens
   int g_topk;
   // MoE layer 1: the comm warps combine every token's top-k rows of D column slab by column slab (a slab =
   // one tile column, BN wide) as soon as all tiles of the slab are stored, push the combined rows (16-bit) to
@@ -234,6 +239,16 @@ __host__ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t,
   // band's M tiles first, then move to the next column block (A band stays in L2, B streams once per band).
   int m_idx, n_idx;
   tc.band = 0;
+  // Column groups (n_group > 0): all tiles of the first n_group tile columns come first, then the next group ...;
+  // inside a group the bands below apply. The output is then complete group by group.
+  int n_base = 0;
+  if (p.n_group > 0 && p.n_group < n_tiles) {
+    const int per_group = m_tiles * p.n_group;
+    const int g = t / per_group;
+    t -= g * per_group;
+    n_base = g * p.n_group;
+    n_tiles = imin(p.n_group, n_tiles - n_base);
+  }
   if (p.n_bands > 0) {
     int b = 0;
     while (b + 1 < p.n_bands && t >= p.band_end[b] * n_tiles) ++b;
@@ -251,6 +266,7 @@ __host__ __device__ __forceinline__ void decode_tile(const GemmParams& p, int t,
     m_idx = band * p.group_m + r % gm_eff;
     n_idx = r / gm_eff;
   }
+  n_idx += n_base;
   tc.n_idx = n_idx;
   tc.n0 = n_idx * BN;
   if (p.g_tiles == nullptr) {
@@ -750,6 +766,10 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           bias_row = static_cast<const uint8_t*>(p.bias);
       }
 
+      // Plain output whose 32 rows of this warp are all valid: staged in shared memory and written with tiled
+      // stores (full 128-byte rows, one instruction per 32 x 64 box) instead of 16 bytes per lane per row.
+      const bool tma_out = p.tmap_out_valid && p.epi_mode == kEpiStore && otype != kOutF32 &&
+                           p.g_scatter_rows == nullptr && quad * 32 + 32 <= tc.rows;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
         uint32_t r[32];
@@ -801,9 +821,20 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
 #pragma unroll
           for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * row_scale;
           if (active && p.scale_b != nullptr) {
+            if (col0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(p.scale_b) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (col0 + j < p.N) v[j] *= p.scale_b[col0 + j];
+              for (int q = 0; q < 8; ++q) {  // 8 x 16-byte loads instead of 32 scalar ones
+                const float4 s4 = __ldg(reinterpret_cast<const float4*>(p.scale_b + col0) + q);
+                v[q * 4] *= s4.x;
+                v[q * 4 + 1] *= s4.y;
+                v[q * 4 + 2] *= s4.z;
+                v[q * 4 + 3] *= s4.w;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (col0 + j < p.N) v[j] *= p.scale_b[col0 + j];
+            }
           }
         }
         if (active && bias_row != nullptr) {
@@ -878,6 +909,36 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
               bulk_commit();
             }
           }
+        } else if (tma_out) {
+          // same staging as the 16-bit reduce-scatter push, into the output tensor itself
+          const int box = c >> 1, h = c & 1;
+          const uint32_t stage_blk = stage_blk0 + (L::kEpiBufs == 2 ? (box & 1) * L::kEpiBlockBytes : 0);
+          const uint32_t stage_row = stage_blk + lane * L::kEpiPitch;
+          if (h == 0) {
+            if (lane == 0) {  // the previous store out of this block has been read
+              if (L::kEpiBufs == 2) bulk_wait_read_keep1(); else bulk_wait_read();
+            }
+            __syncwarp();
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint32_t w[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              w[j] = (otype == kOutBf16) ? pack_bf16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1])
+                                         : pack_f16(v[q * 8 + 2 * j], v[q * 8 + 2 * j + 1]);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(stage_row + (((h * 4 + q) ^ (lane & 7)) << 4)),
+                         "r"(w[0]), "r"(w[1]), "r"(w[2]), "r"(w[3])
+                         : "memory");
+          }
+          if (h == 1) {
+            fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+              if (col0 - 32 < p.N) tma_store_2d(&p.tmap_out, stage_blk, col0 - 32, tc.row0 + quad * 32);
+              bulk_commit();
+            }
+          }
         } else if (p.epi_mode == kEpiRsPush && !own) {
           // fp32 wire format. Park the warp's 32 x 32 fp32 block in shared memory (lane = row, 16-byte pieces XOR-swizzled
           // by row so that the writes spread over all banks and match the tensor map's 128-byte swizzle),
@@ -942,8 +1003,15 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       if (lane == 0) {
         if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
         else mbar_arrive(bar_tempty(acc));
-        // MoE layer 1: this warp's rows of the tile are stored (release covers the whole warp's stores)
-        if (p.gr_slab_done != nullptr) red_add_release_gpu(p.gr_slab_done + tc.n_idx, 1);
+        // MoE layer 1: this warp's rows of the tile are stored (tiled stores complete, and the release covers
+        // the whole warp's plain stores)
+        if (p.gr_slab_done != nullptr) {
+          if (tma_out) {
+            bulk_wait_all();
+            fence_proxy_async();
+          }
+          red_add_release_gpu(p.gr_slab_done + tc.n_idx, 1);
+        }
       }
       if (p.epi_mode == kEpiRsPush) {
         // Publish the PREVIOUS pushed tile of this warp: its stores were issued a whole tile ago, so
@@ -975,6 +1043,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       }
     }
     if (tr != nullptr && warp == 2 && lane == 0) tr[3] = globaltimer_ns();
+    if (p.epi_mode == kEpiStore && p.tmap_out_valid && lane == 0) bulk_wait_all();  // tiled stores must not outlive the CTA
     if (p.epi_mode == kEpiRsPush && lane == 0) {
       // also on the way out after a failed wait: the stores must not outlive the CTA
       bulk_wait_all();
@@ -996,7 +1065,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
     // The push is skipped when the copy engines carry the all-gather (p.ag_src == nullptr).
     if (p.ag_src != nullptr || p.g_sorted != nullptr) {
       const int ctid = threadIdx.x - 6 * 32;  // 0..127
-      const int d_first = (p.ag_src != nullptr && p.a_own_valid) ? 1 : 0;  // own tiles read the caller's tensor
+      // own rows are read from the caller's tensor (dense: by the own tiles; MoE: by the permute): no copy to itself
+      const int d_first = (p.ag_src != nullptr && (p.a_own_valid || p.g_tokens_own != nullptr)) ? 1 : 0;
       const int push_chunks = (p.seg_rows + kBM - 1) / kBM;
       const int units_per_dest = ag_nslices * push_chunks * kAgUnitsPerSlice;
       const int perm_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
@@ -1054,7 +1124,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             const int chunk = rem / kAgUnitsPerSlice;
             const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.g_rows_per_rank);
             const int nrows = imin(kAgUnitRows, p.g_rows_per_rank - r0);
-            if (p.ag_flags != nullptr) {
+            const bool own_src = p.g_tokens_own != nullptr && src_rank == p.rank;
+            if (p.ag_flags != nullptr && !own_src) {
               if (ctid == 0) {
                 const int grp = ks / p.ag_spf;
                 const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
@@ -1072,7 +1143,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
             const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
             if (ctid * 16 < slice_bytes) {
-              const uint8_t* s0 = p.g_tokens + (tok0 + r0) * p.ag_row_bytes + b0 + ctid * 16;
+              const uint8_t* s0 = (own_src ? p.g_tokens_own + static_cast<long long>(r0) * p.ag_row_bytes
+                                           : p.g_tokens + (tok0 + r0) * p.ag_row_bytes) + b0 + ctid * 16;
               uint8_t* d0 = p.g_sorted + b0 + ctid * 16;
               const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
 #pragma unroll 1

@@ -86,7 +86,7 @@ int ag_slices_per_flag(long long row_bytes) {
 int resolve_ag_mode(const fluxb_tuning* tuning) {
   if (tuning != nullptr && (tuning->ag_mode == kAgModeKernelPush || tuning->ag_mode == kAgModeCopyEngine))
     return tuning->ag_mode;
-  return kAgModeCopyEngine;
+  return kAgModeKernelPush;
 }
 
 int ag_dma_create(AgDma* d, int flag_stride) {
@@ -274,6 +274,17 @@ static int check_gemm_shapes(const char* who, int m, int n, int k, int in_dtype,
 }
 
 static void zero_params(GemmParams& p) { memset(&p, 0, sizeof(p)); }
+}  // namespace fluxb
+
+namespace fluxb {
+// Tiled-store map over a plain 16-bit output [rows, n] (row pitch n); left invalid where the map's alignment
+// rules do not hold, in which case the epilogue uses per-lane stores.
+void encode_out_map(GemmParams& p, void* out, long long rows, long long n, int out_type) {
+  p.tmap_out_valid = 0;
+  if (out_type == kOutF32 || out == nullptr || rows <= 0) return;
+  if ((reinterpret_cast<uintptr_t>(out) & 15) != 0 || (n * 2) % 16 != 0) return;
+  if (encode_tmap_b16_store(&p.tmap_out, out, rows, n) == FLUXB_OK) p.tmap_out_valid = 1;
+}
 
 // B operand: [n, k] (k contiguous) as one box of `box_rows` rows, or, with the FLUXB_WEIGHT_KN flag,
 // [k, n] (n contiguous) as 64-column boxes feeding an MN-major UMMA operand.
@@ -351,6 +362,7 @@ int fluxb_gemm(fluxb_comm_t comm, const void* a, const void* b, void* c, int m, 
   const int bn = resolve_block_n(comm, p, tuning, 0);
   rc = encode_tmap_2d(&p.tmap_a, a, in_dtype, m, k, static_cast<long long>(k) * eb, kBM);
   if (rc != FLUXB_OK) return rc;
+  encode_out_map(p, c, m, n, p.out_type);
   rc = encode_b(p, b, in_dtype, n, k, resolve_cta_group(p, tuning) == 2 ? bn / 2 : bn, flags);
   if (rc != FLUXB_OK) return rc;
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
@@ -528,6 +540,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   if (rc != FLUXB_OK) return rc;
   rc = encode_tmap_2d(&p.tmap_a_own, a_shard, op->in_dtype, m_local, k, row_bytes, kBM);
   if (rc != FLUXB_OK) return rc;
+  encode_out_map(p, c, m, n, p.out_type);
   // kernel push: per-row scales travel through the scale buffer under the same flags as the data, so the
   // own shard takes the flagged path too in that case (the copy-engine form has put the own scales in place)
   p.a_own_valid = (scale_a_shard == nullptr || dma) ? 1 : 0;

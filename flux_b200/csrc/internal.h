@@ -110,6 +110,9 @@ int encode_tmap_b16_store(CUtensorMap* out, const void* base, long long rows, lo
 int resolve_block_n(const fluxb_comm* comm, const GemmParams& p, const fluxb_tuning* tuning,
                     long long m_tiles_hint);
 
+// Tiled-store map over a plain 16-bit output (see GemmParams::tmap_out); never fails, it only leaves the map invalid.
+void encode_out_map(GemmParams& p, void* out, long long rows, long long n, int out_type);
+
 // 2 KB slices of a row that share one arrival counter (1 unless the row has more than kAgMaxGroups slices)
 int ag_slices_per_flag(long long row_bytes);
 

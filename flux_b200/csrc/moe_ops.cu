@@ -363,6 +363,8 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
     p.g_tokens = static_cast<const uint8_t*>(tokens_shard);  // nothing to gather: permute straight from the caller's tokens
   } else {
     p.g_tokens = local_gather;
+    // this rank's own tokens are permuted straight from the caller's tensor: no copy to itself on the critical path
+    if (!reuse) p.g_tokens_own = static_cast<const uint8_t*>(tokens_shard);
   }
   if (world > 1 && !reuse) {
     p.ag_flags = op->flags[comm->rank] + parity * half_flags;
@@ -375,11 +377,10 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
       p.ag_dst_flags[r] = op->flags[r] + parity * half_flags;
     }
     if (resolve_ag_mode(tuning) == kAgModeCopyEngine) {
-      // the copy engines carry the tokens (this rank's own ones included: the permute reads every source
-      // from the gather buffer); the comm warps only permute what arrives
+      // the copy engines carry the tokens to the peers; the comm warps only permute what arrives
       dma = true;
       int rc2 = ag_dma_push(comm, &op->dma, tokens_shard, ntokens_local, row_bytes, p.ag_dst, p.ag_dst_flags, nullptr, nullptr,
-                            true, stream);
+                            false, stream);
       if (rc2 != FLUXB_OK) return rc2;
       p.ag_src = nullptr;
     }
@@ -390,6 +391,9 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(e_count) * op->ffn_local,
                       op->hidden, row_bytes, cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
+  // (with expert parallelism the caller's buffer may hold fewer rows than `rows`: no tiled stores then, since
+  // the map's row bound is what clips a store)
+  if (op->ep_size == 1) encode_out_map(p, out, rows, op->ffn_local, p.out_type);
   fluxb_tuning t = tuning != nullptr ? *tuning : fluxb_tuning{0, 0, 0, 0, 0};
   t.block_n = bn;
   t.cta_group = cg;
@@ -397,11 +401,15 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
   if (rc != FLUXB_OK) return rc;
   if (dma) FLUXB_CUDA(cudaStreamWaitEvent(stream, op->dma.ev_done, 0));
   if (!reuse) {
-    if (world == 1) {
-      // keep a copy so that further weight groups and `gathered_out` see the same tokens
-      FLUXB_CUDA(cudaMemcpyAsync(op->gather[0] + parity * half_gather, tokens_shard, ntokens * row_bytes,
-                                 cudaMemcpyDeviceToDevice, stream));
-    }
+    // keep a copy of the own tokens in the gather buffer (after the launch, off its critical path) so that
+    // further weight groups and `gathered_out` find every rank's tokens there
+    uint8_t* own_dst = op->gather[comm->rank] + parity * half_gather + static_cast<size_t>(comm->rank) * ntokens_local * row_bytes;
+    const size_t own_bytes = static_cast<size_t>(ntokens_local) * row_bytes;
+    rc = enqueue_or_defer(comm, stream, [=](cudaStream_t st) -> int {
+      FLUXB_CUDA(cudaMemcpyAsync(own_dst, tokens_shard, own_bytes, cudaMemcpyDeviceToDevice, st));
+      return FLUXB_OK;
+    });
+    if (rc != FLUXB_OK) return rc;
     op->last_parity = parity;
     op->last_ntokens = ntokens_local;
     op->calls += 1;
@@ -590,6 +598,7 @@ int fluxb_moe_gather_rs_forward_ep(fluxb_moe_gather_rs_t op, const void* x, int 
   rc = encode_tmap_2d(&p.tmap_b, weights, op->in_dtype, static_cast<long long>(e_count) * n, k_local, row_bytes,
                       cg == 2 ? bn / 2 : bn);
   if (rc != FLUXB_OK) return rc;
+  encode_out_map(p, inter, p.M, n, p.out_type);
   // combine + reduce-scatter run inside the same launch (comm warps), column slab by column slab
   const int parity = static_cast<int>(op->calls & 1ull);
   const size_t half_stage_elems = (static_cast<size_t>(op->max_m) / topk) * n;
@@ -628,6 +637,10 @@ int fluxb_moe_gather_rs_forward_ep(fluxb_moe_gather_rs_t op, const void* x, int 
   if (slab_order) {
     p.group_m = 1 << 20;
     t.group_m = p.group_m;
+  } else {
+    // four column groups: A streams from HBM four times (there is bandwidth to spare next to a tensor-bound GEMM),
+    // and the combine of a group overlaps the GEMM of the next one
+    p.n_group = (n_tiles + 3) / 4;
   }
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;

@@ -16,6 +16,7 @@ from __future__ import annotations
 
 import argparse
 import os
+import time
 
 import torch
 import torch.distributed as dist
@@ -59,6 +60,7 @@ def main() -> None:
     group = dist.group.WORLD if world > 1 else None
     flux.init_flux_shm(group)
     comm = flux.get_comm(group)
+    comm.set_timeout_ms(2000)  # a wait that runs out ends the call after 2 s instead of the default 10
     m, k0, n0, n1, k1 = args.m, args.hidden, args.ffn, args.hidden, args.ffn
     gen = torch.Generator(device="cuda").manual_seed(rank)
     a = torch.randn(m // world, k0, generator=gen, device="cuda").bfloat16()
@@ -77,6 +79,11 @@ def main() -> None:
             dist.barrier()
 
     def run(name, fn):
+        # every measurement starts from the same idle state: without the pause the later ones inherit the
+        # power-cap state of the earlier ones and look slower than they are
+        barrier()
+        time.sleep(0.5)
+        barrier()
         for _ in range(3):
             fn()
         barrier()
