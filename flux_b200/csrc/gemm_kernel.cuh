@@ -63,7 +63,7 @@ struct GroupTile {
   int a_row0;      // first sorted row of the tile
   int rows;        // valid rows (1..128)
   int expert;      // which weight slab
-  int need_mask;   // bit r set = tile reads tokens that live on source rank r
+  int need_mask;   // bit (r * g_nvr + j) set = tile reads tokens of block j of source rank r
 };
 
 struct GemmParams {
@@ -138,7 +138,8 @@ struct GemmParams {
   // grouped mode, permute form: the comm warps copy every gathered token row to its top-k places in
   // an expert-sorted buffer (which tmap_a then describes) and count finished work items per source rank
   uint8_t* g_sorted;              // [rows, K] sorted activations, null = gather4 form
-  int* g_perm_done;               // [world] finished permute items per source rank (local, zeroed per call)
+  int* g_perm_done;               // [world * g_nvr] finished permute units per source block (local, zeroed per call)
+  int g_vblk, g_nvr;              // tokens per source block (a multiple of 128) and blocks per rank (world * g_nvr <= 32)
   const int* g_scatter_index;     // [tokens, topk]
   const int* g_row_range;         // device [2]: rows [lo, hi) of the sorted order that this rank computes (expert
                                   // parallelism: the rows of its experts); null = all rows. Row lo is row 0 of g_sorted.
@@ -502,13 +503,17 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
         if (p.ag_flags != nullptr && p.g_tiles == nullptr && tc.rows > 0 && !(p.a_own_valid && tc.seg == p.rank))
           tile_flags = p.ag_flags + tc.seg * p.ag_flag_stride + tc.chunk * p.ag_groups;
         if (p.g_perm_done != nullptr) {
-          // grouped, permute form: every source rank the tile reads must be fully permuted
-          const int expected = ((p.g_rows_per_rank + kBM - 1) / kBM) * kAgUnitsPerSlice *
-                               static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
+          // grouped, permute form: every source block the tile reads must be fully permuted
+          const int nvr = p.g_nvr > 0 ? p.g_nvr : 1;
+          const int cpv = (p.g_vblk > 0 ? p.g_vblk : p.g_rows_per_rank + kBM - 1) / kBM;  // chunks per block
+          const int all_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
           const uint64_t w0 = tr != nullptr ? globaltimer_ns() : 0;
-          for (int r = 0; ok && r < p.world; ++r)
-            if ((tc.need_mask >> r) & 1)
-              ok = flag_wait_eq(p.g_perm_done + r, expected, ab, kStatusTimeoutFlag, budget);
+          for (int b = 0; ok && b < p.world * nvr; ++b)
+            if ((tc.need_mask >> b) & 1) {
+              const int j = b % nvr;
+              const int expected = imin(cpv, all_chunks - j * cpv) * kAgUnitsPerSlice * ag_nslices;
+              ok = flag_wait_eq(p.g_perm_done + b, expected, ab, kStatusTimeoutFlag, budget);
+            }
           if (tr != nullptr) tr[5] += globaltimer_ns() - w0;
           if (!ok) break;
           fence_proxy_async();
@@ -1070,7 +1075,6 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       const int push_chunks = (p.seg_rows + kBM - 1) / kBM;
       const int units_per_dest = ag_nslices * push_chunks * kAgUnitsPerSlice;
       const int perm_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
-      const int units_per_src = ag_nslices * perm_chunks * kAgUnitsPerSlice;
       volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
       bool comm_ok = true;
       for (int d = 0; comm_ok && d < p.world; ++d) {
@@ -1118,11 +1122,19 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           const long long tok0 = static_cast<long long>(src_rank) * p.g_rows_per_rank;
           const int perm_lo = p.g_row_range != nullptr ? p.g_row_range[0] : 0;
           const int perm_rows = p.g_row_range != nullptr ? p.g_row_range[1] - perm_lo : p.M;
-          for (int u = cta_id; comm_ok && u < units_per_src; u += num_ctas) {
-            const int ks = u / (perm_chunks * kAgUnitsPerSlice);
-            const int rem = u - ks * (perm_chunks * kAgUnitsPerSlice);
-            const int chunk = rem / kAgUnitsPerSlice;
-            const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.g_rows_per_rank);
+          // units of a source in block-major order (block j: its slices, chunks, 32-row quarters), so that the
+          // source's blocks complete one after the other
+          const int nvr = p.g_nvr > 0 ? p.g_nvr : 1;
+          const int cpv = (p.g_vblk > 0 ? p.g_vblk : p.g_rows_per_rank + kBM - 1) / kBM;
+          const int slots_per_blk = ag_nslices * cpv * kAgUnitsPerSlice;
+          for (int u = cta_id; comm_ok && u < nvr * slots_per_blk; u += num_ctas) {
+            const int vb = u / slots_per_blk;
+            const int ub = u - vb * slots_per_blk;
+            const int ks = ub / (cpv * kAgUnitsPerSlice);
+            const int rem = ub - ks * (cpv * kAgUnitsPerSlice);
+            const int chunk = vb * cpv + rem / kAgUnitsPerSlice;
+            if (chunk >= perm_chunks) continue;  // the last block of a rank may hold fewer chunks
+            const int r0 = imin(chunk * kBM + (rem % kAgUnitsPerSlice) * kAgUnitRows, p.g_rows_per_rank);
             const int nrows = imin(kAgUnitRows, p.g_rows_per_rank - r0);
             const bool own_src = p.g_tokens_own != nullptr && src_rank == p.rank;
             if (p.ag_flags != nullptr && !own_src) {
@@ -1165,7 +1177,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             }
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (ctid == 0) red_add_release_sys(p.g_perm_done + src_rank, 1);
+            if (ctid == 0) red_add_release_sys(p.g_perm_done + src_rank * nvr + vb, 1);
           }
         }
       }
