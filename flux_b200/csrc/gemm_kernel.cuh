@@ -1063,10 +1063,10 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
     // one 16-byte column per thread, 8 rows in flight, then ONE system-scope release per unit (measured on 8
     // GPUs: the release waits for the unit's stores to be acknowledged over NVLink, so a release per 8 rows
     // per warp halved the push rate; per 32 rows per CTA it is affordable).
-    // Steps d = 0 .. world-1 interleave the two jobs: push this rank's shard to the rank that needs it
-    // d-th soonest (rank-1, rank-2, ...; one destination at a time, so every link carries one stream at
-    // full rate and shards land in the order they are consumed), then permute the tokens of source
-    // rank+d (own tokens first), which that source pushed during its own step d-1.
+    // Steps d = 0 .. world-1 interleave the two jobs: permute the tokens of source rank+d (own tokens first,
+    // read in place; the others were pushed by their source during its step d-1), then push this rank's shard
+    // to the rank that needs it d-th soonest (rank-1, rank-2, ...; one destination at a time, so every link
+    // carries one stream at full rate and shards land in the order they are consumed).
     // The push is skipped when the copy engines carry the all-gather (p.ag_src == nullptr).
     if (p.ag_src != nullptr || p.g_sorted != nullptr) {
       const int ctid = threadIdx.x - 6 * 32;  // 0..127
@@ -1078,41 +1078,6 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
       bool comm_ok = true;
       for (int d = 0; comm_ok && d < p.world; ++d) {
-        if (p.ag_src != nullptr && d + d_first < p.world) {
-          int dest = p.rank - (d + d_first);
-          if (dest < 0) dest += p.world;
-          // units of one destination in slice-major order: the first 2 KB of every row go out first, so
-          // that the consumer's walk along K can begin after a fraction of the shard has crossed
-          for (int u = cta_id; u < units_per_dest; u += num_ctas) {
-            const int ks = u / (push_chunks * kAgUnitsPerSlice);
-            const int rem = u - ks * (push_chunks * kAgUnitsPerSlice);
-            const int chunk = rem / kAgUnitsPerSlice;
-            const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.seg_rows);
-            const int nrows = imin(kAgUnitRows, p.seg_rows - r0);  // 0 for a unit past the shard's last row: it still signals
-            const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
-            const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
-            if (ctid * 16 < slice_bytes) {
-              const uint8_t* src = p.ag_src + static_cast<long long>(r0) * p.ag_row_bytes + b0 + ctid * 16;
-              uint8_t* dst = p.ag_dst[dest] + (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0 + ctid * 16;
-#pragma unroll 1
-              for (int rr = 0; rr < nrows; rr += 8) {
-                uint4 val[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (rr + j < nrows) val[j] = __ldg(reinterpret_cast<const uint4*>(src + (rr + j) * p.ag_row_bytes));
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (rr + j < nrows) *reinterpret_cast<uint4*>(dst + (rr + j) * p.ag_row_bytes) = val[j];
-              }
-            }
-            if (ks == 0 && p.ag_src_scale != nullptr && ctid < nrows)
-              p.ag_dst_scale[dest][static_cast<long long>(p.rank) * p.seg_rows + r0 + ctid] = p.ag_src_scale[r0 + ctid];
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            // the release covers every thread's stores (ordered before it by the barrier)
-            if (ctid == 0)
-              red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk * p.ag_groups + ks / p.ag_spf, 1);
-          }
-        }
         if (p.g_sorted != nullptr) {
           // MoE layer 0, permute form: copy every token row of source rank+d to its top-k rows of the
           // expert-sorted buffer (one load, top-k stores per 16-byte piece) and count the unit as done
@@ -1178,6 +1143,41 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             __threadfence();
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (ctid == 0) red_add_release_sys(p.g_perm_done + src_rank * nvr + vb, 1);
+          }
+        }
+        if (p.ag_src != nullptr && d + d_first < p.world) {
+          int dest = p.rank - (d + d_first);
+          if (dest < 0) dest += p.world;
+          // units of one destination in slice-major order: the first 2 KB of every row go out first, so
+          // that the consumer's walk along K can begin after a fraction of the shard has crossed
+          for (int u = cta_id; u < units_per_dest; u += num_ctas) {
+            const int ks = u / (push_chunks * kAgUnitsPerSlice);
+            const int rem = u - ks * (push_chunks * kAgUnitsPerSlice);
+            const int chunk = rem / kAgUnitsPerSlice;
+            const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.seg_rows);
+            const int nrows = imin(kAgUnitRows, p.seg_rows - r0);  // 0 for a unit past the shard's last row: it still signals
+            const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
+            const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
+            if (ctid * 16 < slice_bytes) {
+              const uint8_t* src = p.ag_src + static_cast<long long>(r0) * p.ag_row_bytes + b0 + ctid * 16;
+              uint8_t* dst = p.ag_dst[dest] + (static_cast<long long>(p.rank) * p.seg_rows + r0) * p.ag_row_bytes + b0 + ctid * 16;
+#pragma unroll 1
+              for (int rr = 0; rr < nrows; rr += 8) {
+                uint4 val[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (rr + j < nrows) val[j] = __ldg(reinterpret_cast<const uint4*>(src + (rr + j) * p.ag_row_bytes));
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  if (rr + j < nrows) *reinterpret_cast<uint4*>(dst + (rr + j) * p.ag_row_bytes) = val[j];
+              }
+            }
+            if (ks == 0 && p.ag_src_scale != nullptr && ctid < nrows)
+              p.ag_dst_scale[dest][static_cast<long long>(p.rank) * p.seg_rows + r0 + ctid] = p.ag_src_scale[r0 + ctid];
+            asm volatile("bar.sync 1, 128;" ::: "memory");
+            // the release covers every thread's stores (ordered before it by the barrier)
+            if (ctid == 0)
+              red_add_release_sys(p.ag_dst_flags[dest] + p.rank * p.ag_flag_stride + chunk * p.ag_groups + ks / p.ag_spf, 1);
           }
         }
       }

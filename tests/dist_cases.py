@@ -211,3 +211,114 @@ def tp_mlp_case(rank, world):
     assert rel(x_shard.grad, x.grad[rows]) <= 2e-2
     assert rel(mlp.fc1.weight.grad, w1.grad[cols]) <= 2e-2
     assert rel(mlp.fc2.weight.grad, w2.grad[:, cols]) <= 2e-2
+
+
+def baseline_shapes_case(rank, world):
+    """The dense BASELINE configurations at this world size, one process per GPU: D0 (AG-GEMM M=4096, N=49152/TP,
+    K=12288) feeding D1 (GEMM-RS M=4096, N=12288, K=49152/TP), both all-gather transports, and F (fp8 AG-GEMM
+    M=8192, N=28672/TP, K=8192 with per-row x per-channel scales); checked by fp64 dot products on sampled entries,
+    rows of every source rank included (the CPU oracle would take minutes at these sizes)."""
+    import flux_b200 as flux
+
+    group = dist.group.WORLD
+    flux.init_flux_shm(group)
+    comm = flux.get_comm(group)
+    comm.set_timeout_ms(5000)
+    M, N0, K0, N1 = 4096, 49152, 12288, 12288
+    m_local, n_local = M // world, N0 // world
+    g = torch.Generator(device="cuda").manual_seed(1234 + rank)
+    a = torch.randn(m_local, K0, generator=g, device="cuda").bfloat16()
+    b0 = (torch.randn(n_local, K0, generator=g, device="cuda") * 0.02).bfloat16()
+    b1 = (torch.randn(N1, n_local, generator=g, device="cuda") * 0.02).bfloat16()
+
+    def spread(n, count):
+        return torch.tensor([round(i * (n - 1) / (count - 1)) for i in range(count)], device="cuda")
+
+    def all_gather_cuda(x):
+        # the spawn helper runs over gloo: gather through the host
+        host = [torch.empty_like(x.cpu()) for _ in range(world)]
+        dist.all_gather(host, x.cpu().contiguous(), group=group)
+        return torch.cat(host).cuda()
+
+    def all_reduce_cuda(x):
+        h = x.cpu()
+        dist.all_reduce(h, group=group)
+        return h.cuda()
+
+    def check(got, exact, tol_rel, tol_elem, what):
+        got, exact = got.double(), exact.double()
+        rel = float((got - exact).abs().max() / exact.abs().max())
+        assert rel <= tol_rel, f"rank {rank} {what}: max rel err {rel}"
+        assert bool(((got - exact).abs() <= tol_elem + tol_elem * exact.abs()).all()), f"rank {rank} {what}: elementwise {tol_elem}"
+
+    ag = flux.AGKernel(group, 1, M, n_local, K0, torch.bfloat16)
+    rs = flux.GemmRS(group, 1, M, N1, torch.bfloat16)
+    rows_l, cols0, cols1 = spread(m_local, 8), spread(n_local, 16), spread(N1, 16)
+    grows = (torch.arange(world, device="cuda")[:, None] * m_local + rows_l[None, :]).reshape(-1)
+    a_rows = all_gather_cuda(a[rows_l]).double()
+    exact0 = a_rows @ b0[cols0].double().t()
+    for ag_mode in (1, 2):
+        c0 = ag.forward(a, b0, tuning={"ag_mode": ag_mode})
+        torch.cuda.synchronize()
+        comm.check_status()
+        check(c0[grows][:, cols0], exact0, 1e-2, 1e-2, f"D0 (all-gather transport {ag_mode})")
+    out = rs.forward(c0, b1)
+    torch.cuda.synchronize()
+    comm.check_status()
+    part = c0[grows].double() @ b1[cols1].double().t()
+    exact1 = all_reduce_cuda(part)
+    gold1 = all_reduce_cuda(part.bfloat16().double()).bfloat16()  # the golden path rounds every rank's partial to bf16
+    lo = rank * rows_l.numel()
+    got1 = out[rows_l][:, cols1]
+    rel = float((got1.double() - exact1[lo:lo + rows_l.numel()]).abs().max() / exact1.abs().max())
+    assert rel <= 1e-2, f"rank {rank} D1: max rel err vs fp64 {rel}"
+    check(got1, gold1[lo:lo + rows_l.numel()], 1e-2, 2e-2, "D1 vs the golden path")
+    del ag, rs, b0, b1, c0
+    # ---- F: fp8 with per-row / per-channel scales
+    f8 = torch.float8_e4m3fn
+    FM, FN, FK = 8192, 28672, 8192
+    fm, fn = FM // world, FN // world
+    x = torch.randn(fm, FK, generator=g, device="cuda")
+    w = torch.randn(fn, FK, generator=g, device="cuda") * 0.02
+    sx = (x.abs().amax(1).clamp_min(1e-12) / 448.0).float()
+    sw = (w.abs().amax(1).clamp_min(1e-12) / 448.0).float()
+    qx, qw = (x / sx[:, None]).to(f8), (w / sw[:, None]).to(f8)
+    op = flux.AGKernel(group, 1, FM, fn, FK, f8)
+    o8 = op.forward(qx, qw, input_scale=sx, weight_scale=sw)
+    torch.cuda.synchronize()
+    comm.check_status()
+    r8, c8 = spread(fm, 8), spread(fn, 16)
+    g8 = (torch.arange(world, device="cuda")[:, None] * fm + r8[None, :]).reshape(-1)
+    xr = all_gather_cuda(qx[r8].double() * sx[r8].double()[:, None])
+    check(o8[g8][:, c8], xr @ (qw[c8].double() * sw[c8].double()[:, None]).t(), 3e-2, 3e-2, "F")
+
+
+def runtime_case(rank, world):
+    """Symmetric tensor list and the stream barrier across processes (reference test:
+    test/python/util/test_flux_ring_barrier.py; src/ths_op/flux_shm.cc:434-452,656-733): every rank writes its own
+    block, a barrier on the stream orders the writes, then every rank reads all peers' blocks through the mapped
+    pointers and writes into the next peer's block."""
+    import flux_b200 as flux
+
+    group = dist.group.WORLD
+    flux.init_flux_shm(group)
+    comm = flux.get_comm(group)
+    comm.set_timeout_ms(5000)
+    ts = flux.flux_create_tensor_list((4, 64), torch.float32, group)
+    assert len(ts) == world and all(t.shape == (4, 64) for t in ts)
+    gb = flux.GroupBarrier(group)
+    for it in range(3):
+        ts[rank].fill_(float(10 * it + rank + 1))
+        gb.barrier_all()
+        for r in range(world):
+            # peers' blocks are only ever touched by copies (copy engines), never handed to a library kernel
+            got = ts[r].cpu()
+            assert float(got.sum()) == 4 * 64 * (10 * it + r + 1), f"rank {rank} reads rank {r}'s block (iteration {it})"
+        gb.barrier_all()  # nobody overwrites a block that a peer is still reading
+    nxt = (rank + 1) % world
+    ts[nxt][0].copy_(torch.full((64,), -float(rank + 1), device="cuda"))  # a copy into a peer's memory
+    gb.barrier_all()
+    torch.cuda.synchronize()
+    prev = (rank - 1) % world
+    assert float(ts[rank][0, 0]) == -float(prev + 1) and float(ts[rank][1, 0]) == 20.0 + rank + 1
+    comm.check_status()

@@ -255,3 +255,12 @@ def test_stress_random_m_multi_rank():
     ms = [int(x) for x in torch.randint(1, 513, (10,), generator=g)]
     run_distributed(dist_cases.ag_gemm_case, w, [(m, 512, 512) for m in ms], "bfloat16", False, None)
     run_distributed(dist_cases.gemm_rs_case, w, [(m * w, 512, 256) for m in ms], "bfloat16", False, None)
+
+
+def test_baseline_shapes_multi_rank():
+    """D0, D1 and F of the benchmark at the box's GPU count, one process per GPU (fp64 samples)."""
+    w = min(gpu_count(), 8)
+    if w < 2:
+        pytest.skip("needs >= 2 GPUs")
+    w = 1 << (w.bit_length() - 1)
+    run_distributed(dist_cases.baseline_shapes_case, w)

@@ -52,6 +52,17 @@ def test_create_tensor_list_world1(flux):
     assert tb[0].numel() == 7
 
 
+def test_tensor_list_and_barrier_multi_rank():
+    from conftest import gpu_count
+    import dist_cases
+    from _dist import run_distributed
+
+    w = min(gpu_count(), 8)
+    if w < 2:
+        pytest.skip("needs >= 2 GPUs")
+    run_distributed(dist_cases.runtime_case, 1 << (w.bit_length() - 1))
+
+
 def _status(lib, h):
     s = C.c_int(-1)
     assert lib.fluxb_status_peek(h, C.byref(s)) == 0
