@@ -423,7 +423,9 @@ class GemmRS:
             pass
 
     def forward(self, input, weight, bias=None, input_scale=None, weight_scale=None, output_scale=None,
-                fast_accum=False, reduce_scatter_option=None, tuning=None):
+                fast_accum=False, reduce_scatter_option=None, tuning=None, output=None):
+        """`output` (not in the reference, which returns a tensor derived from its internal buffers): an optional
+        [M/TP, N] tensor to write into, for callers that must not allocate inside a timed or captured region."""
         _check(input.is_cuda and weight.is_cuda, "GemmRS: tensors must be CUDA tensors")
         _check(input.dim() == 2 and weight.dim() == 2, "GemmRS: input and weight must be 2-D")
         _check(input.dtype == self.input_dtype and weight.dtype == self.input_dtype, "GemmRS: dtype mismatch")
@@ -462,7 +464,12 @@ class GemmRS:
                 raise RuntimeError(f"GemmRS: bias shape {tuple(bias.shape)} is neither [M,N] nor [1,N]")
         sa = _expand_scale(input_scale, m, "input_scale")
         sb = _expand_scale(weight_scale, n, "weight_scale")
-        out = torch.empty((m // w, n), dtype=self.output_dtype, device=input.device)
+        if output is None:
+            out = torch.empty((m // w, n), dtype=self.output_dtype, device=input.device)
+        else:
+            _check(tuple(output.shape) == (m // w, n) and output.dtype == self.output_dtype and output.is_contiguous(),
+                   "GemmRS: output has the wrong shape, dtype or layout")
+            out = output
         if tuning is None and _tune.TABLE.records:
             tuning = _tune.TABLE.get(_tune.record_key("gemm_rs", m, n, k, self.input_dtype, w))
         lib = _lib.load()
