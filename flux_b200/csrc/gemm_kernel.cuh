@@ -46,8 +46,8 @@ constexpr int kRowBytes = 128;    // bytes of K per smem row (one swizzle span)
 constexpr int kThreads = 320;
 constexpr int kMaxWorld = 8;
 constexpr int kCommSliceBytes = 2048;  // bytes of one row handled by one comm unit
-constexpr int kAgUnitRows = 32;        // rows of one all-gather push unit (32 rows x 2 KB by the 128 comm threads)
-constexpr int kAgUnitsPerSlice = kBM / kAgUnitRows;  // units that signal one (128-row chunk, 2 KB slice)
+constexpr int kPermUnitRows = 32;      // rows of one permute unit of MoE layer 0 (32 rows x 2 KB by the 128 comm threads)
+constexpr int kPermUnitsPerSlice = kBM / kPermUnitRows;
 constexpr int kGrTokBlock = 32;        // tokens per combine / reduce work item of MoE layer 1
 constexpr int kAgMaxGroups = 64;       // arrival counters per (source rank, chunk): one per group of 2 KB slices
 
@@ -98,13 +98,14 @@ struct GemmParams {
   const float* alpha_ptr;  // optional device scalar multiplied into alpha
   // all-gather: consumer side
   // Arrival counters [source rank][128-row chunk][slice group]: a group is `ag_spf` consecutive 2 KB slices
-  // of the rows (1 unless a row has more than kAgMaxGroups slices); every push unit of 32 rows x 2 KB adds 1,
-  // so a complete group counts kAgUnitsPerSlice x (slices in the group). The GEMM waits group by group as
+  // of the rows (1 unless a row has more than kAgMaxGroups slices); every push unit of ag_unit_rows rows x 2 KB
+  // adds 1, so a complete group counts (128 / ag_unit_rows) x (slices in the group). The GEMM waits group by group as
   // it walks along K, so a tile starts as soon as the first 2 KB of its rows are in.
   const int* ag_flags;  // null = no waits
   int ag_flag_stride;   // counters per source rank (= chunks of the buffer x ag_groups)
   int ag_groups;        // counters per chunk
   int ag_spf;           // 2 KB slices per counter
+  int ag_unit_rows;     // rows of one push unit: 32, 64 or 128 (one release per unit)
   // all-gather: producer side (comm warps)
   const uint8_t* ag_src;          // this rank's shard, row-major, row_bytes per row
   uint8_t* ag_dst[kMaxWorld];     // gather buffer of every rank (own included)
@@ -398,6 +399,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
   // all-gather bookkeeping: a K block is 128 bytes of a row, a push slice 2 KB, a counter covers ag_spf slices
   const int ag_nslices = static_cast<int>((p.ag_row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
   const int kb_per_group = (kCommSliceBytes / kRowBytes) * (p.ag_spf > 0 ? p.ag_spf : 1);
+  const int ag_ups = kBM / (p.ag_unit_rows > 0 ? p.ag_unit_rows : 32);  // push units per (chunk, slice)
 
   // Work schedule, identical in every role: worker w (a CTA, or a CTA pair) takes tiles w, w+P, ...
   // of the full waves; if the last wave is at most half full, each of its tiles is cut along K into
@@ -511,7 +513,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           for (int b = 0; ok && b < p.world * nvr; ++b)
             if ((tc.need_mask >> b) & 1) {
               const int j = b % nvr;
-              const int expected = imin(cpv, all_chunks - j * cpv) * kAgUnitsPerSlice * ag_nslices;
+              const int expected = imin(cpv, all_chunks - j * cpv) * kPermUnitsPerSlice * ag_nslices;
               ok = flag_wait_eq(p.g_perm_done + b, expected, ab, kStatusTimeoutFlag, budget);
             }
           if (tr != nullptr) tr[5] += globaltimer_ns() - w0;
@@ -521,6 +523,36 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
         // K block at which the next slice group of the rows begins (never, if there is nothing to wait for):
         // one compare per K block on the producer's critical path, the arithmetic only when a group begins
         int next_group_kb = tile_flags != nullptr ? kb0 : 0x7fffffff;
+        if (tile_flags != nullptr) {
+          // Look ahead: read the counters of all slice groups of the rows in one sweep (relaxed loads issued
+          // together, 16 counters at a time) and make the leading complete ones visible with ONE acquire fence.
+          // In the steady state every group has arrived and the tile costs one load latency instead of one
+          // acquire per group; the groups still missing are waited for one by one below.
+          const int ngroups = (ag_nslices + p.ag_spf - 1) / p.ag_spf;
+          int lead = 0;
+          bool scanning = true;
+          for (int g0 = 0; scanning && g0 < ngroups; g0 += 16) {
+            uint4 v[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              v[q] = g0 + 4 * q < ngroups ? ld_relaxed_sys_v4(tile_flags + g0 + 4 * q) : make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+            for (int q = 0; q < 16; ++q) {
+              const uint4 w = v[q >> 2];
+              const int val = static_cast<int>((q & 3) == 0 ? w.x : (q & 3) == 1 ? w.y : (q & 3) == 2 ? w.z : w.w);
+              const int gi = g0 + q;
+              if (scanning && gi < ngroups) {
+                if (val == ag_ups * imin(p.ag_spf, ag_nslices - gi * p.ag_spf)) lead = gi + 1;
+                else scanning = false;
+              }
+            }
+          }
+          if (lead > 0) {
+            fence_acq_rel_sys();
+            fence_proxy_async();
+            if (lead * kb_per_group > kb0) next_group_kb = lead >= ngroups ? 0x7fffffff : lead * kb_per_group;
+          }
+        }
         for (int kb = kb0; kb < kb1; ++kb) {
           if (kb == next_group_kb) {
             // entering a new slice group of the rows: wait (bounded) until all of its push units are in
@@ -528,7 +560,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             next_group_kb = (grp + 1) * kb_per_group;
             const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
             const uint64_t w0 = tr != nullptr ? globaltimer_ns() : 0;
-            ok = flag_wait_eq(tile_flags + grp, kAgUnitsPerSlice * in_group, ab, kStatusTimeoutFlag, budget);
+            ok = flag_wait_eq(tile_flags + grp, ag_ups * in_group, ab, kStatusTimeoutFlag, budget);
             if (tr != nullptr) tr[5] += globaltimer_ns() - w0;
             if (!ok) break;
             fence_proxy_async();
@@ -1059,10 +1091,10 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
     }
   } else {
     // ----------------------------------------------------------------- comm
-    // All-gather push and (MoE layer 0) permute by the 128 comm threads of the CTA. A unit is 32 rows x 2 KB:
-    // one 16-byte column per thread, 8 rows in flight, then ONE system-scope release per unit (measured on 8
-    // GPUs: the release waits for the unit's stores to be acknowledged over NVLink, so a release per 8 rows
-    // per warp halved the push rate; per 32 rows per CTA it is affordable).
+    // All-gather push and (MoE layer 0) permute by the 128 comm threads of the CTA. A push unit is
+    // ag_unit_rows (32, 64 or 128) rows x 2 KB: one 16-byte column per thread, 8 rows in flight, then ONE
+    // system-scope release per unit (measured on 8 GPUs: the release waits for the unit's stores to be
+    // acknowledged over NVLink, so a release per 8 rows per warp halved the push rate).
     // Steps d = 0 .. world-1 interleave the two jobs: permute the tokens of source rank+d (own tokens first,
     // read in place; the others were pushed by their source during its step d-1), then push this rank's shard
     // to the rank that needs it d-th soonest (rank-1, rank-2, ...; one destination at a time, so every link
@@ -1073,7 +1105,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       // own rows are read from the caller's tensor (dense: by the own tiles; MoE: by the permute): no copy to itself
       const int d_first = (p.ag_src != nullptr && (p.a_own_valid || p.g_tokens_own != nullptr)) ? 1 : 0;
       const int push_chunks = (p.seg_rows + kBM - 1) / kBM;
-      const int units_per_dest = ag_nslices * push_chunks * kAgUnitsPerSlice;
+      const int units_per_dest = ag_nslices * push_chunks * ag_ups;
+      const int unit_rows = kBM / ag_ups;
       const int perm_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
       volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
       bool comm_ok = true;
@@ -1091,23 +1124,23 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           // source's blocks complete one after the other
           const int nvr = p.g_nvr > 0 ? p.g_nvr : 1;
           const int cpv = (p.g_vblk > 0 ? p.g_vblk : p.g_rows_per_rank + kBM - 1) / kBM;
-          const int slots_per_blk = ag_nslices * cpv * kAgUnitsPerSlice;
+          const int slots_per_blk = ag_nslices * cpv * kPermUnitsPerSlice;
           for (int u = cta_id; comm_ok && u < nvr * slots_per_blk; u += num_ctas) {
             const int vb = u / slots_per_blk;
             const int ub = u - vb * slots_per_blk;
-            const int ks = ub / (cpv * kAgUnitsPerSlice);
-            const int rem = ub - ks * (cpv * kAgUnitsPerSlice);
-            const int chunk = vb * cpv + rem / kAgUnitsPerSlice;
+            const int ks = ub / (cpv * kPermUnitsPerSlice);
+            const int rem = ub - ks * (cpv * kPermUnitsPerSlice);
+            const int chunk = vb * cpv + rem / kPermUnitsPerSlice;
             if (chunk >= perm_chunks) continue;  // the last block of a rank may hold fewer chunks
-            const int r0 = imin(chunk * kBM + (rem % kAgUnitsPerSlice) * kAgUnitRows, p.g_rows_per_rank);
-            const int nrows = imin(kAgUnitRows, p.g_rows_per_rank - r0);
+            const int r0 = imin(chunk * kBM + (rem % kPermUnitsPerSlice) * kPermUnitRows, p.g_rows_per_rank);
+            const int nrows = imin(kPermUnitRows, p.g_rows_per_rank - r0);
             const bool own_src = p.g_tokens_own != nullptr && src_rank == p.rank;
             if (p.ag_flags != nullptr && !own_src) {
               if (ctid == 0) {
                 const int grp = ks / p.ag_spf;
                 const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
                 *s_flag = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk * p.ag_groups + grp,
-                                       kAgUnitsPerSlice * in_group, ab, kStatusTimeoutFlag, budget) ? 1 : 0;
+                                       ag_ups * in_group, ab, kStatusTimeoutFlag, budget) ? 1 : 0;
               }
               asm volatile("bar.sync 1, 128;" ::: "memory");
               const int okp = *s_flag;
@@ -1151,11 +1184,11 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           // units of one destination in slice-major order: the first 2 KB of every row go out first, so
           // that the consumer's walk along K can begin after a fraction of the shard has crossed
           for (int u = cta_id; u < units_per_dest; u += num_ctas) {
-            const int ks = u / (push_chunks * kAgUnitsPerSlice);
-            const int rem = u - ks * (push_chunks * kAgUnitsPerSlice);
-            const int chunk = rem / kAgUnitsPerSlice;
-            const int r0 = imin(chunk * kBM + (rem - chunk * kAgUnitsPerSlice) * kAgUnitRows, p.seg_rows);
-            const int nrows = imin(kAgUnitRows, p.seg_rows - r0);  // 0 for a unit past the shard's last row: it still signals
+            const int ks = u / (push_chunks * ag_ups);
+            const int rem = u - ks * (push_chunks * ag_ups);
+            const int chunk = rem / ag_ups;
+            const int r0 = imin(chunk * kBM + (rem - chunk * ag_ups) * unit_rows, p.seg_rows);
+            const int nrows = imin(unit_rows, p.seg_rows - r0);  // 0 for a unit past the shard's last row: it still signals
             const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
             const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
             if (ctid * 16 < slice_bytes) {

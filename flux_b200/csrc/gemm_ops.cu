@@ -84,9 +84,15 @@ int ag_slices_per_flag(long long row_bytes) {
 }
 
 int resolve_ag_mode(const fluxb_tuning* tuning) {
-  if (tuning != nullptr && (tuning->ag_mode == kAgModeKernelPush || tuning->ag_mode == kAgModeCopyEngine))
-    return tuning->ag_mode;
+  if (tuning != nullptr && tuning->ag_mode == kAgModeCopyEngine) return kAgModeCopyEngine;
   return kAgModeKernelPush;
+}
+
+int resolve_ag_unit_rows(const fluxb_tuning* tuning) {
+  if (tuning != nullptr && tuning->ag_mode == kAgModeCopyEngine) return kBM;  // a copied piece arrives whole
+  if (tuning != nullptr && tuning->ag_mode == 3) return 64;
+  if (tuning != nullptr && tuning->ag_mode == 4) return 128;
+  return 32;
 }
 
 int ag_dma_create(AgDma* d, int flag_stride) {
@@ -113,6 +119,7 @@ int ag_dma_push(const fluxb_comm* comm, AgDma* d, const void* src, int m_local, 
                 uint8_t* const* gather, int* const* flags, const float* src_scale, float* const* dst_scale,
                 bool include_self, cudaStream_t main) {
   const int world = comm->world, rank = comm->rank;
+  constexpr int kUnitsPerSlice = 1;  // counter value of a complete (chunk, slice): the consumer is told 128-row units
   if (d->expected_row_bytes != row_bytes) {
     // counter values of a complete shard: every used slice group of every chunk holds its unit count
     const int nslices = static_cast<int>((row_bytes + kCommSliceBytes - 1) / kCommSliceBytes);
@@ -121,7 +128,7 @@ int ag_dma_push(const fluxb_comm* comm, AgDma* d, const void* src, int m_local, 
     for (int i = 0; i < d->flag_stride; ++i) {
       const int g = i % kAgMaxGroups;
       const int left = nslices - g * spf;
-      if (left > 0) v[i] = kAgUnitsPerSlice * (left < spf ? left : spf);
+      if (left > 0) v[i] = kUnitsPerSlice * (left < spf ? left : spf);
     }
     FLUXB_CUDA(cudaMemcpy(d->expected_dev, v.data(), v.size() * sizeof(int), cudaMemcpyHostToDevice));
     d->expected_row_bytes = row_bytes;
@@ -498,6 +505,7 @@ int fluxb_ag_gemm_forward(fluxb_ag_gemm_t op, const void* a_shard, int m_local, 
   p.ag_flag_stride = op->flag_stride;
   p.ag_groups = kAgMaxGroups;
   p.ag_spf = ag_slices_per_flag(row_bytes);
+  p.ag_unit_rows = resolve_ag_unit_rows(tuning);
   p.ag_src = static_cast<const uint8_t*>(a_shard);
   p.ag_row_bytes = row_bytes;
   p.ag_src_scale = scale_a_shard;

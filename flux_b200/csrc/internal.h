@@ -141,6 +141,7 @@ int ag_dma_push(const fluxb_comm* comm, AgDma* d, const void* src, int m_local, 
 
 enum : int { kAgModeDefault = 0, kAgModeKernelPush = 1, kAgModeCopyEngine = 2 };
 int resolve_ag_mode(const fluxb_tuning* tuning);
+int resolve_ag_unit_rows(const fluxb_tuning* tuning);  // rows of a push unit for the chosen mode
 
 // 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile (the caller's choice or a heuristic).
 int resolve_cta_group(const GemmParams& p, const fluxb_tuning* tuning);

@@ -387,6 +387,7 @@ int fluxb_moe_ag_scatter_forward(fluxb_moe_ag_scatter_t op, const void* tokens_s
     p.ag_flag_stride = op->flag_stride;
     p.ag_groups = kAgMaxGroups;
     p.ag_spf = ag_slices_per_flag(row_bytes);
+    p.ag_unit_rows = resolve_ag_unit_rows(tuning);
     p.ag_src = static_cast<const uint8_t*>(tokens_shard);
     for (int r = 0; r < world; ++r) {
       p.ag_dst[r] = op->gather[r] + parity * half_gather;

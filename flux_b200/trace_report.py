@@ -49,6 +49,7 @@ def main() -> None:
     ap.add_argument("--hidden", type=int, default=12288)
     ap.add_argument("--ffn", type=int, default=49152)
     ap.add_argument("--reps", type=int, default=2)
+    ap.add_argument("--push-units", action="store_true", help="also the kernel push in units of 64 and 128 rows")
     ap.add_argument("--moe", action="store_true", help="also the MoE layers at 8192 tokens, hidden 4096, 8 experts, top-2")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", 0)), int(os.environ.get("WORLD_SIZE", 1))
@@ -114,6 +115,9 @@ def main() -> None:
     run("gemm D0", lambda: ag.gemm_only(a_full, b0, output=out))
     if world > 1:
         run("ag-gemm, kernel push", lambda: ag.forward(a, b0, output=out, tuning=kernel_push))
+        if args.push_units:
+            run("ag-gemm, push 64-row units", lambda: ag.forward(a, b0, output=out, tuning={"ag_mode": 3}))
+            run("ag-gemm, push 128-row units", lambda: ag.forward(a, b0, output=out, tuning={"ag_mode": 4}))
         run("ag-gemm, copy engines", lambda: ag.forward(a, b0, output=out, tuning=copy_engines))
     run("gemm D1", lambda: plain1.gemm_only(c0, b1))
     if world > 1:

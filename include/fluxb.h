@@ -73,7 +73,8 @@ typedef struct fluxb_tuning {
   int group_m;  /* rasterisation band height, in 128-row tiles         */
   int num_ctas; /* persistent grid size (<= SM count)                  */
   int cta_group; /* 1 = one CTA per 128-row tile, 2 = CTA pair per 256-row tile */
-  int ag_mode;  /* transport of the all-gather: 1 = pushed by the fused kernel's communication warps, 2 = copy
+  int ag_mode;  /* transport of the all-gather: 1 = pushed by the fused kernel's communication warps (units of 32
+                   rows x 2 KB per system-scope release; 3 = units of 64 rows, 4 = units of 128 rows), 2 = copy
                    engines on a side stream (AllGatherOption.use_cuda_core_ag = true / false in the reference,
                    src/coll/ths_op/all_gather_types.h:35-43); the consuming kernel is the same */
 } fluxb_tuning;

@@ -35,8 +35,9 @@ def _cpu_inputs(rank, rows, n, k, dtype, seed):
     return a, b
 
 
-# transport of the all-gather: 1 = pushed by the kernel's communication warps, 2 = copy engines
-@pytest.mark.parametrize("ag_mode", [1, 2])
+# transport of the all-gather: 1 = pushed by the kernel's communication warps in units of 32 rows (3: 64 rows,
+# 4: 128 rows), 2 = copy engines
+@pytest.mark.parametrize("ag_mode", [1, 2, 3, 4])
 @pytest.mark.parametrize("world", [2, 4, 8])
 def test_ag_gemm_all_ranks_on_one_gpu(world, ag_mode):
     shapes = [(256, 512, 512), (200, 264, 512), (128, 136, 512), (256, 512, 512), (37, 72, 512)]
@@ -224,7 +225,7 @@ def test_gemm_rs_ring_reduction_all_ranks_on_one_gpu():
         rk.close()
 
 
-@pytest.mark.parametrize("ag_mode", [1, 2])
+@pytest.mark.parametrize("ag_mode", [1, 2, 4])
 @pytest.mark.parametrize("world", [2, 4])
 def test_moe_all_ranks_on_one_gpu(world, ag_mode):
     ntokens, topk, nexperts, hidden, ffn = 128 * world, 2, 4, 256, 128 * world
