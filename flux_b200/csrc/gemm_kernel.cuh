@@ -37,6 +37,8 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <type_traits>
+
 #include "ptx.cuh"
 
 namespace fluxb {
@@ -434,6 +436,95 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
     return true;
   };
 
+  // MoE layer 0, permute form. One unit = 32 token rows x one 2 KB slice of source rank `src_rank`: copy every
+  // row to its top-k rows of the expert-sorted buffer (one load, top-k stores per 16-byte piece) and count the
+  // unit as done for its source block; a tile waits until every source block it reads is complete. Units of a
+  // source run block-major (block j: its slices, chunks, 32-row quarters), so that the source's blocks complete
+  // one after the other. Called by 128 threads (`tid` 0..127) that own named barrier BAR.
+  const int perm_nvr = p.g_nvr > 0 ? p.g_nvr : 1;
+  const int perm_cpv = (p.g_vblk > 0 ? p.g_vblk : p.g_rows_per_rank + kBM - 1) / kBM;  // chunks per block
+  const int perm_slots = ag_nslices * perm_cpv * kPermUnitsPerSlice;
+  const int perm_units = perm_nvr * perm_slots;
+  // step 0 (this rank's own tokens, nothing to wait for) gates the first tiles: the epilogue warps, idle until
+  // the first accumulator is complete, permute every second unit of it
+  const bool perm_helped = p.g_sorted != nullptr && (p.ag_flags == nullptr || p.g_tokens_own != nullptr);
+  auto permute_unit = [&](auto bar_tag, int u, int src_rank, int tid, bool may_wait) -> bool {
+    constexpr int BAR = decltype(bar_tag)::value;
+    const long long tok0 = static_cast<long long>(src_rank) * p.g_rows_per_rank;
+    const int perm_lo = p.g_row_range != nullptr ? p.g_row_range[0] : 0;
+    const int perm_rows = p.g_row_range != nullptr ? p.g_row_range[1] - perm_lo : p.M;
+    const int perm_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
+    const int vb = u / perm_slots;
+    const int ub = u - vb * perm_slots;
+    const int ks = ub / (perm_cpv * kPermUnitsPerSlice);
+    const int rem = ub - ks * (perm_cpv * kPermUnitsPerSlice);
+    const int chunk = vb * perm_cpv + rem / kPermUnitsPerSlice;
+    if (chunk >= perm_chunks) return true;  // the last block of a rank may hold fewer chunks
+    const int r0 = imin(chunk * kBM + (rem % kPermUnitsPerSlice) * kPermUnitRows, p.g_rows_per_rank);
+    const int nrows = imin(kPermUnitRows, p.g_rows_per_rank - r0);
+    const bool own_src = p.g_tokens_own != nullptr && src_rank == p.rank;
+    if (may_wait && p.ag_flags != nullptr && !own_src) {
+      volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
+      if (tid == 0) {
+        const int grp = ks / p.ag_spf;
+        const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
+        *s_flag = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk * p.ag_groups + grp,
+                               ag_ups * in_group, ab, kStatusTimeoutFlag, budget) ? 1 : 0;
+      }
+      asm volatile("bar.sync %0, 128;" ::"n"(BAR) : "memory");
+      const int okp = *s_flag;
+      asm volatile("bar.sync %0, 128;" ::"n"(BAR) : "memory");
+      if (!okp) return false;
+    }
+    const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
+    const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
+    {
+      const bool active = tid * 16 < slice_bytes;
+      const uint8_t* s0 = (own_src ? p.g_tokens_own + static_cast<long long>(r0) * p.ag_row_bytes
+                                   : p.g_tokens + (tok0 + r0) * p.ag_row_bytes) + b0 + tid * 16;
+      uint8_t* d0 = p.g_sorted + b0 + tid * 16;
+      const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
+      // The unit's destination rows (rows x top-k entries of the scatter index) are fetched up front, spread
+      // over the lanes of each warp, and handed out by shuffles: a load of the index between two stores cannot
+      // be moved ahead of the store by the compiler, and one dependent load per stored row made a unit
+      // take ~23 us.
+      const int nidx = nrows * p.g_topk;
+      const bool in_regs = nidx <= 128;
+      int sreg[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) sreg[q] = (in_regs && q * 32 + lane < nidx) ? si[q * 32 + lane] : -1;
+#pragma unroll 1
+      for (int rr = 0; rr < nrows; rr += 8) {
+        uint4 val[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (active && rr + j < nrows) val[j] = *reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          if (rr + j < nrows)
+            for (int k = 0; k < p.g_topk; ++k) {
+              const int idx = (rr + j) * p.g_topk + k;
+              int entry;
+              if (in_regs) {
+                const int q = idx >> 5;
+                const int mine = q == 0 ? sreg[0] : q == 1 ? sreg[1] : q == 2 ? sreg[2] : sreg[3];
+                entry = __shfl_sync(0xffffffffu, mine, idx & 31);
+              } else {
+                entry = si[idx];
+              }
+              const long long drow = static_cast<long long>(entry) - perm_lo;
+              if (active && drow >= 0 && drow < perm_rows)  // rows of other ranks' experts; a corrupt entry must not become a wild store
+                *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
+            }
+      }
+    }
+    // the release by one thread covers every thread's stores (ordered before it by the barrier); the counter
+    // and the sorted buffer are local, so device scope is enough
+    asm volatile("bar.sync %0, 128;" ::"n"(BAR) : "memory");
+    if (tid == 0) red_add_release_gpu(p.g_perm_done + src_rank * perm_nvr + vb, 1);
+    return true;
+  };
+
   // Abort path of the producer: every stage it armed still has copies in flight or has been filled; wait
   // (1 ms per stage at most) until each armed phase completes, so that no copy outlives the CTA's shared
   // memory. Stages [0, stage) were last armed in phase `phase`, the others one round earlier. In a CTA pair
@@ -691,6 +782,11 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
     const int row_in_tile = quad * 32 + lane;
     const uint32_t stage_blk0 = smem_base + L::kEpiOffset + (warp - 2) * L::kEpiWarpBytes;
     int* pending_cnt = nullptr;  // reduce-scatter: counter of the previous pushed tile, published one tile late
+    if (perm_helped) {
+      // MoE layer 0: nothing to drain until this rank's own tokens are permuted; take every second unit of them
+      for (int u = cta_id + num_ctas; u < perm_units; u += 2 * num_ctas)
+        permute_unit(std::integral_constant<int, 2>{}, u, p.rank, static_cast<int>(threadIdx.x) - 2 * 32, false);
+    }
     int it = 0;
     int t, kb0, kb1, part;
     for (; get_item(it, t, kb0, kb1, part); ++it) {
@@ -1065,8 +1161,8 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           pending_cnt = (!own && tc.rows > 0) ? p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx : nullptr;
           // Exception: the tiles of the last band of peer-owned rows are the ones their owners are waiting
           // for when they reach their own rows (every rank computes its own rows last), so their publish is
-          // latency-critical: a tile-time of delay there showed up as 50-75 us of waiting in the owners'
-          // last epilogues on 8 GPUs. The accumulator has been released already, so waiting for these
+          // latency-critical: with the late publish, the owners' last epilogues waited about one tile time for
+          // them (seen in the kernel's timeline on 8 GPUs). The accumulator has been released already, so waiting for these
           // stores holds up nothing but this warp. (Without explicit bands: the rows of the previous rank.)
           const int prev_rank = p.rank == 0 ? p.nseg - 1 : p.rank - 1;
           const bool urgent = p.n_bands >= 2 ? tc.band == p.n_bands - 2 : tc.seg == prev_rank;
@@ -1107,8 +1203,6 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       const int push_chunks = (p.seg_rows + kBM - 1) / kBM;
       const int units_per_dest = ag_nslices * push_chunks * ag_ups;
       const int unit_rows = kBM / ag_ups;
-      const int perm_chunks = (p.g_rows_per_rank + kBM - 1) / kBM;
-      volatile int* s_flag = reinterpret_cast<volatile int*>(smem + L::kMiscOffset + 16);
       bool comm_ok = true;
       for (int d = 0; comm_ok && d < p.world; ++d) {
         if (p.g_sorted != nullptr) {
@@ -1117,66 +1211,11 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           // for that source; a tile waits until every source rank it reads is complete.
           int src_rank = p.rank + d;
           if (src_rank >= p.world) src_rank -= p.world;
-          const long long tok0 = static_cast<long long>(src_rank) * p.g_rows_per_rank;
-          const int perm_lo = p.g_row_range != nullptr ? p.g_row_range[0] : 0;
-          const int perm_rows = p.g_row_range != nullptr ? p.g_row_range[1] - perm_lo : p.M;
-          // units of a source in block-major order (block j: its slices, chunks, 32-row quarters), so that the
-          // source's blocks complete one after the other
-          const int nvr = p.g_nvr > 0 ? p.g_nvr : 1;
-          const int cpv = (p.g_vblk > 0 ? p.g_vblk : p.g_rows_per_rank + kBM - 1) / kBM;
-          const int slots_per_blk = ag_nslices * cpv * kPermUnitsPerSlice;
-          for (int u = cta_id; comm_ok && u < nvr * slots_per_blk; u += num_ctas) {
-            const int vb = u / slots_per_blk;
-            const int ub = u - vb * slots_per_blk;
-            const int ks = ub / (cpv * kPermUnitsPerSlice);
-            const int rem = ub - ks * (cpv * kPermUnitsPerSlice);
-            const int chunk = vb * cpv + rem / kPermUnitsPerSlice;
-            if (chunk >= perm_chunks) continue;  // the last block of a rank may hold fewer chunks
-            const int r0 = imin(chunk * kBM + (rem % kPermUnitsPerSlice) * kPermUnitRows, p.g_rows_per_rank);
-            const int nrows = imin(kPermUnitRows, p.g_rows_per_rank - r0);
-            const bool own_src = p.g_tokens_own != nullptr && src_rank == p.rank;
-            if (p.ag_flags != nullptr && !own_src) {
-              if (ctid == 0) {
-                const int grp = ks / p.ag_spf;
-                const int in_group = imin(p.ag_spf, ag_nslices - grp * p.ag_spf);
-                *s_flag = flag_wait_eq(p.ag_flags + src_rank * p.ag_flag_stride + chunk * p.ag_groups + grp,
-                                       ag_ups * in_group, ab, kStatusTimeoutFlag, budget) ? 1 : 0;
-              }
-              asm volatile("bar.sync 1, 128;" ::: "memory");
-              const int okp = *s_flag;
-              asm volatile("bar.sync 1, 128;" ::: "memory");
-              if (!okp) {
-                comm_ok = false;
-                break;
-              }
-            }
-            const long long b0 = static_cast<long long>(ks) * kCommSliceBytes;
-            const int slice_bytes = static_cast<int>((b0 + kCommSliceBytes < p.ag_row_bytes ? b0 + kCommSliceBytes : p.ag_row_bytes) - b0);
-            if (ctid * 16 < slice_bytes) {
-              const uint8_t* s0 = (own_src ? p.g_tokens_own + static_cast<long long>(r0) * p.ag_row_bytes
-                                           : p.g_tokens + (tok0 + r0) * p.ag_row_bytes) + b0 + ctid * 16;
-              uint8_t* d0 = p.g_sorted + b0 + ctid * 16;
-              const int* si = p.g_scatter_index + (tok0 + r0) * p.g_topk;
-#pragma unroll 1
-              for (int rr = 0; rr < nrows; rr += 8) {
-                uint4 val[8];
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (rr + j < nrows) val[j] = *reinterpret_cast<const uint4*>(s0 + (rr + j) * p.ag_row_bytes);
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  if (rr + j < nrows)
-                    for (int k = 0; k < p.g_topk; ++k) {
-                      const long long drow = static_cast<long long>(si[(rr + j) * p.g_topk + k]) - perm_lo;
-                      if (drow >= 0 && drow < perm_rows)  // rows of other ranks' experts; a corrupt entry must not become a wild store
-                        *reinterpret_cast<uint4*>(d0 + drow * p.ag_row_bytes) = val[j];
-                    }
-              }
-            }
-            __threadfence();
-            asm volatile("bar.sync 1, 128;" ::: "memory");
-            if (ctid == 0) red_add_release_sys(p.g_perm_done + src_rank * nvr + vb, 1);
-          }
+          // units of this CTA: u = cta_id, cta_id + num_ctas, ...; while the epilogue warps help (step 0, see
+          // there) they take every second one
+          const int stride = perm_helped && d == 0 ? 2 * num_ctas : num_ctas;
+          for (int u = cta_id; comm_ok && u < perm_units; u += stride)
+            comm_ok = permute_unit(std::integral_constant<int, 1>{}, u, src_rank, ctid, true);
         }
         if (p.ag_src != nullptr && d + d_first < p.world) {
           int dest = p.rank - (d + d_first);

@@ -202,6 +202,7 @@ class GemmGroupedV3GatherRS:
                  max_input_groups=1, ep_in_dp=False, input_dtype=torch.bfloat16, output_dtype=None):
         _check(int(tp_world_size) * int(ep_world_size) == int(world_size),
                "GemmGroupedV3GatherRS: tp_world_size * ep_world_size must equal world_size")
+        _check(not ep_in_dp, "GemmGroupedV3GatherRS: ep_in_dp is not built")
         self.ep_size = int(ep_world_size)
         self.ep_rank = int(rank) // int(tp_world_size)  # ranks of one ffn-TP group are consecutive
         self.comm = default_comm()
@@ -250,6 +251,9 @@ class GemmGroupedV3GatherRS:
         _check(tuple(weight.shape) == (e_local, self.n_dim, k), f"weight shape {tuple(weight.shape)} != {(e_local, self.n_dim, k)}")
         _check(not splits_cpu.is_cuda and splits_cpu.dtype == torch.int32 and splits_cpu.numel() >= self.nexperts,
                "splits_cpu must be a CPU int32 tensor with at least nexperts entries")
+        # the reference's extra splits[E] slot counts dropped tokens (gemm_grouped_v3_gather_rs.cc:668-674)
+        _check(splits_cpu.numel() == self.nexperts or int(splits_cpu[self.nexperts:].sum()) == 0,
+               "forward_gather_rs: token dropping (a non-zero splits[E] slot) is not built")
         _check(routing_idx.is_cuda and routing_idx.dtype == torch.int32, "routing_idx must be a CUDA int32 tensor")
         rows_all = routing_idx.numel()  # ntokens * topk; with expert parallelism `input` holds this rank's experts' rows
         _check(rows_all % self.topk == 0 and rows_all <= self.max_m and (self.ep_size > 1 or rows_all == m),
