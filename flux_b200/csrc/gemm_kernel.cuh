@@ -86,6 +86,12 @@ struct GemmParams {
   int n_group;  // > 0: tile columns are visited in groups of this many (all M tiles of a group before the next group)
   int rs_wire16;  // reduce-scatter partials cross NVLink in the 16-bit output format instead of fp32
   int rs_ring;    // with rs_wire16: every addition of the reduction is rounded to the 16-bit type, own partial last
+  // The peers that compute this rank's rows in their last band of peer rows (rank+1 .. rank+rs_n_late) deliver
+  // just before the own tiles start: their 16-bit partials are added by the own tiles' epilogue itself, straight
+  // from the staging slots (arrivals counted at rs_late_off ints behind the ordinary counters); only the other
+  // peers' partials go through the comm warps' fp32 sum. 0 = every peer goes through the comm warps.
+  int rs_n_late;
+  int rs_late_off;
   int n_bands;  // > 0: explicit bands, band b covers M tiles [band_end[b-1], band_end[b])
   int band_end[8];
   // epilogue
@@ -859,8 +865,12 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
         int okw = 1;
         if (lane == 0) {
           const uint64_t w0 = (tr != nullptr && warp == 2) ? globaltimer_ns() : 0;
-          okw = flag_wait_eq(p.rs_local_ready + tc.chunk * n_tiles + tc.n_idx, 4, ab, kStatusTimeoutReduce,
-                             budget) ? 1 : 0;
+          const int tix = tc.chunk * n_tiles + tc.n_idx;
+          if (p.rs_n_late < p.world - 1)  // the comm warps' sum of the early peers' partials
+            okw = flag_wait_eq(p.rs_local_ready + tix, 4, ab, kStatusTimeoutReduce, budget) ? 1 : 0;
+          if (okw && p.rs_n_late > 0)  // the late peers' partials themselves (4 arrivals each)
+            okw = flag_wait_eq(p.rs_local_cnt + p.rs_late_off + tix, 4 * p.rs_n_late, ab, kStatusTimeoutReduce,
+                               budget) ? 1 : 0;
           if (tr != nullptr && warp == 2) tr[6] += globaltimer_ns() - w0;
         }
         okw = __shfl_sync(0xffffffffu, okw, 0);
@@ -994,7 +1004,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           for (int j = 0; j < 32; ++j)
             v[j] = (p.rs_out_type == kOutF16) ? __half2float(__float2half_rn(v[j])) : __bfloat162float(__float2bfloat16_rn(v[j]));
         }
-        if (own && active) {
+        if (own && active && p.rs_n_late < p.world - 1) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
             if (col0 + q * 4 + 4 <= p.N) {
@@ -1003,6 +1013,35 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
               v[q * 4 + 1] += sv.y;
               v[q * 4 + 2] += sv.z;
               v[q * 4 + 3] += sv.w;
+            }
+          }
+        }
+        if (own && active && p.rs_n_late > 0) {
+          // late peers (rank+1, rank+2, ...): their 16-bit partials straight from the staging slots
+          const long long slot = static_cast<long long>(p.seg_rows) * p.N;
+          const long long eoff = (static_cast<long long>(tc.chunk) * kBM + row_in_tile) * p.N + col0;
+#pragma unroll 1
+          for (int i = 0; i < p.rs_n_late; ++i) {
+            int sr = p.rank + 1 + i;
+            if (sr >= p.world) sr -= p.world;
+            const uint16_t* lp = reinterpret_cast<const uint16_t*>(p.rs_local_stage + sr * slot) + eoff;
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              if (col0 + q * 8 + 8 <= p.N) {
+                const uint4 lv = __ldcg(reinterpret_cast<const uint4*>(lp + q * 8));
+                const uint32_t w[4] = {lv.x, lv.y, lv.z, lv.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  if (p.rs_out_type == kOutBf16) {
+                    v[q * 8 + 2 * j] += __uint_as_float(w[j] << 16);
+                    v[q * 8 + 2 * j + 1] += __uint_as_float(w[j] & 0xFFFF0000u);
+                  } else {
+                    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[j]));
+                    v[q * 8 + 2 * j] += f.x;
+                    v[q * 8 + 2 * j + 1] += f.y;
+                  }
+                }
+              }
             }
           }
         }
@@ -1158,14 +1197,16 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             fence_acq_rel_sys();
             red_add_release_sys(pending_cnt, 1);
           }
-          pending_cnt = (!own && tc.rows > 0) ? p.rs_cnt[tc.seg] + tc.chunk * n_tiles + tc.n_idx : nullptr;
+          const int prev_rank = p.rank == 0 ? p.nseg - 1 : p.rank - 1;
+          const bool urgent = p.n_bands >= 2 ? tc.band == p.n_bands - 2 : tc.seg == prev_rank;
+          pending_cnt = (!own && tc.rows > 0) ? p.rs_cnt[tc.seg] + ((urgent && p.rs_n_late > 0) ? p.rs_late_off : 0) +
+                                                    tc.chunk * n_tiles + tc.n_idx
+                                              : nullptr;
           // Exception: the tiles of the last band of peer-owned rows are the ones their owners are waiting
           // for when they reach their own rows (every rank computes its own rows last), so their publish is
           // latency-critical: with the late publish, the owners' last epilogues waited about one tile time for
           // them (seen in the kernel's timeline on 8 GPUs). The accumulator has been released already, so waiting for these
           // stores holds up nothing but this warp. (Without explicit bands: the rows of the previous rank.)
-          const int prev_rank = p.rank == 0 ? p.nseg - 1 : p.rank - 1;
-          const bool urgent = p.n_bands >= 2 ? tc.band == p.n_bands - 2 : tc.seg == prev_rank;
           if (pending_cnt != nullptr && urgent) {
             bulk_wait_all();
             fence_acq_rel_sys();
@@ -1416,14 +1457,15 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
     }
       if (p.epi_mode == kEpiRsPush) {
       // Owner side of the reduce-scatter. Work item = 32 rows of one 128 x BN tile of this rank's rows:
-      // wait (bounded) until every peer has published the tile (4 arrivals per peer: one per epilogue
-      // warp), sum the peers' partials in fp32 in rank order into this rank's own slot, and add 1 to the
-      // tile's ready count (the epilogue of the own tile waits for 4). Items are spread over all CTAs and
+      // wait (bounded) until every early peer has published the tile (4 arrivals per peer: one per epilogue
+      // warp), sum their partials in fp32 in rank order into this rank's own slot, and add 1 to the
+      // tile's ready count (the epilogue of the own tile waits for 4; the late peers' partials it adds itself). Items are spread over all CTAs and
       // every source's loads are in flight together. The peers compute this rank's rows before their own,
       // so this work is spread over the kernel and finished before the own tiles are.
       const int ctid = threadIdx.x - 6 * 32;  // 0..127
       const int m_chunks = (p.seg_rows + kBM - 1) / kBM;
-      const int total_items = m_chunks * n_tiles * 4;
+      const int n_early = p.world - 1 - p.rs_n_late;            // peers whose partials are summed here
+      const int total_items = n_early > 0 ? m_chunks * n_tiles * 4 : 0;
       constexpr int kVecPerRow = BN / 4;                 // float4 per tile row
       constexpr int kVecPerItem = 32 * kVecPerRow;       // float4 per work item
       const long long slot = static_cast<long long>(p.seg_rows) * p.N;
@@ -1436,7 +1478,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
         const int nt = rt / m_chunks;
         const int tix = c * n_tiles + nt;
         if (ctid == 0)
-          *s_flag = flag_wait_eq(p.rs_local_cnt + tix, 4 * (p.world - 1), ab, kStatusTimeoutReduce, budget) ? 1 : 0;
+          *s_flag = flag_wait_eq(p.rs_local_cnt + tix, 4 * n_early, ab, kStatusTimeoutReduce, budget) ? 1 : 0;
         asm volatile("bar.sync 1, 128;" ::: "memory");
         const int okr = *s_flag;
         asm volatile("bar.sync 1, 128;" ::: "memory");
@@ -1465,7 +1507,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
             for (int i = 0; i < kMaxWorld - 1; ++i)
 #pragma unroll
               for (int u = 0; u < 2; ++u)
-                if (i + 1 < p.world && off[u] >= 0) {
+                if (i >= p.rs_n_late && i + 1 < p.world && off[u] >= 0) {
                   int sr = p.rank + 1 + i;
                   if (sr >= p.world) sr -= p.world;
                   v[i][u] = *reinterpret_cast<const uint4*>(
@@ -1479,7 +1521,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
               for (int j = 0; j < 8; ++j) acc[j] = 0.f;
 #pragma unroll
               for (int i = 0; i < kMaxWorld - 1; ++i)
-                if (i + 1 < p.world) {
+                if (i >= p.rs_n_late && i + 1 < p.world) {
                   const uint32_t w[4] = {v[i][u].x, v[i][u].y, v[i][u].z, v[i][u].w};
 #pragma unroll
                   for (int j = 0; j < 4; ++j) {

@@ -584,8 +584,8 @@ size_t fluxb_gemm_rs_stage_bytes(int max_m, int n_dim, int world) {
   return 2ull * static_cast<size_t>(max_m) * n_dim * sizeof(float);
 }
 size_t fluxb_gemm_rs_cnt_bytes(int max_m, int n_dim, int world) {
-  // two parities x (arrival counters + ready flags)
-  return 2ull * 2ull * rs_cnt_cap(max_m, n_dim, world) * sizeof(int);
+  // two parities x (arrival counters of the early peers + ready flags + arrival counters of the late peers)
+  return 2ull * 3ull * rs_cnt_cap(max_m, n_dim, world) * sizeof(int);
 }
 
 int fluxb_gemm_rs_create(fluxb_comm_t comm, int max_m, int n_dim, int in_dtype, int out_dtype,
@@ -659,8 +659,8 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   const int parity = static_cast<int>(op->calls & 1ull);
   // The other parity's counters and flags were consumed by the previous call and are next written by
   // peers only after they have seen this call's pushes: clear them now.
-  FLUXB_CUDA(cudaMemsetAsync(op->cnt[comm->rank] + (parity ^ 1) * 2 * op->cnt_cap, 0,
-                             2 * op->cnt_cap * sizeof(int), stream));
+  FLUXB_CUDA(cudaMemsetAsync(op->cnt[comm->rank] + (parity ^ 1) * 3 * op->cnt_cap, 0,
+                             3 * op->cnt_cap * sizeof(int), stream));
   GemmParams p;
   zero_params(p);
   int ot;
@@ -689,7 +689,7 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   const size_t half_stage = static_cast<size_t>(op->max_m) * op->n_dim;
   for (int r = 0; r < world; ++r) {
     p.rs_stage[r] = op->stage[r] + parity * half_stage + static_cast<size_t>(comm->rank) * mpr * n;
-    p.rs_cnt[r] = op->cnt[r] + parity * 2 * op->cnt_cap;
+    p.rs_cnt[r] = op->cnt[r] + parity * 3 * op->cnt_cap;
     rc = p.rs_wire16 ? encode_tmap_b16_store(&p.tmap_rs[r], p.rs_stage[r], mpr, n)
                      : encode_tmap_f32_store(&p.tmap_rs[r], p.rs_stage[r], mpr, n);
     if (rc != FLUXB_OK) return rc;
@@ -711,8 +711,23 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   t.block_n = bn;
   // the owner-side reduction runs in the same kernel (comm warps)
   p.rs_local_stage = op->stage[comm->rank] + parity * half_stage;
-  p.rs_local_cnt = op->cnt[comm->rank] + parity * 2 * op->cnt_cap;
+  p.rs_local_cnt = op->cnt[comm->rank] + parity * 3 * op->cnt_cap;
   p.rs_local_ready = p.rs_local_cnt + op->cnt_cap;
+  p.rs_late_off = static_cast<int>(2 * op->cnt_cap);
+  // Late peers: those that compute this rank's rows in their last band of peer rows (by symmetry, the ranks
+  // rank+1 .. rank+n_late, where n_late is the number of owners in that band). Not with the ring-order
+  // reduction (its order and roundings are fixed) nor with fp32 partials.
+  p.rs_n_late = 0;
+  if (p.rs_wire16 && !p.rs_ring) {
+    if (p.n_bands >= 2) {
+      const int tile_m = resolve_cta_group(p, tuning) == 2 ? 2 * kBM : kBM;
+      const int tps = (mpr + tile_m - 1) / tile_m;
+      const int first_seg = p.n_bands >= 3 ? p.band_end[p.n_bands - 3] / tps : 0;
+      p.rs_n_late = (world - 1) - first_seg;
+    } else {
+      p.rs_n_late = 1;
+    }
+  }
   p.rs_out = out;
   p.rs_out_type = ot;
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);

@@ -87,6 +87,10 @@ def test_parity_gate():
     assert bench.parity_ok(good)
     assert not bench.parity_ok(dict(good, rs_max_rel_err=2e-2))
     assert not bench.parity_ok(dict(good, **{"ag_allclose_1e-2": False}))
+    # GEMM-RS elementwise bar: an isolated rounding flip is tolerated, a pattern is not
+    assert bench.parity_ok(dict(good, **{"rs_allclose_2e-2": False, "rs_outside_2e-2_frac": 1 / 128}))
+    assert not bench.parity_ok(dict(good, **{"rs_allclose_2e-2": False, "rs_outside_2e-2_frac": 0.05}))
+    assert not bench.parity_ok(dict(good, **{"rs_allclose_2e-2": False}))
 
 
 # ------------------------------------------------------------------------------------------------
