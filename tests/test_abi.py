@@ -40,7 +40,7 @@ def test_size_helpers():
     assert lib.fluxb_ag_gemm_scale_bytes(4096) == 2 * 4096 * 4
     # fp32 partial tiles, two parities
     assert lib.fluxb_gemm_rs_stage_bytes(4096, 12288, 8) == 2 * 4096 * 12288 * 4
-    assert lib.fluxb_gemm_rs_cnt_bytes(4096, 12288, 8) == 2 * 2 * 4 * (12288 // 64) * 4
+    assert lib.fluxb_gemm_rs_cnt_bytes(4096, 12288, 8) == 2 * 3 * 4 * (12288 // 64) * 4  # early, ready, late
 
 
 def test_no_gpu_means_loud_failure():
