@@ -172,9 +172,10 @@ struct GemmParams {
   int* gr_local_cnt;
   void* gr_out;                  // [tokens_per_rank][N]
   // split-K tail: the tiles of the last, partial wave are split along K over the otherwise idle
-  // workers; parts 1.. park their fp32 accumulators here, part 0 adds them before its epilogue
-  float* splitk_scratch;  // null = never split
-  int* splitk_cnt;        // [tail tile][half][epilogue warp] arrivals, self-clearing
+  // workers; every part parks here its fp32 accumulators of the 64-column boxes that another part finishes
+  float* splitk_scratch;  // [tail tile][split - 1 other parts][tile rows][BN]; null = never split
+  int* splitk_cnt;        // [tail tile][half][epilogue warp] parts that have parked, self-clearing
+  int* splitk_done;       // same shape: parts that have seen all others parked (the last one clears both)
   // optional timeline: 8 x u64 per CTA (globaltimer ns): 0 kernel start, 1 first operands landed,
   // 2 last UMMA issued, 3 epilogue done, 4 comm warps done, 5 ns spent waiting on arrival flags,
   // 6 ns the epilogue waited for "peers summed" flags, 7 work items of this CTA
@@ -220,13 +221,15 @@ __host__ __device__ __forceinline__ int imax(int a, int b) { return a > b ? a : 
 
 // Rasterisation bands for the segmented ops, in units of segments (= shards / owners) of `tps` M tiles.
 // Bands are at most 8 M tiles tall (taller bands re-stream B less often and draw less power).
-// first_single: the first band is exactly one segment (all-gather: this rank's own shard, available at
-// once) and the following bands double in size, so that early tiles only need early arrivals.
+// first_single: the first band starts with this rank's own shard (all-gather: available at once) and is
+// filled up to 4 M tiles with the shards that arrive first (the push is slice-major, so their first 2 KB
+// slices are in after a few microseconds; a band of 2 M tiles costs 8 % of its tiles' time, one of 4 costs
+// 2 %); the following bands double in size, so that early tiles only need early arrivals.
 // last_single: the last band is exactly one segment (reduce-scatter: this rank's own rows, finished last).
 inline void make_bands(GemmParams& p, int nseg, int tps, bool first_single, bool last_single) {
   int max_seg = tps > 0 ? 8 / tps : 1;
   if (max_seg < 1) max_seg = 1;
-  int done = 0, nb = 0, next = 1;
+  int done = 0, nb = 0, next = tps > 0 && 4 / tps > 1 ? 4 / tps : 1;
   const int body_end = last_single ? nseg - 1 : nseg;
   while (done < body_end && nb < 7) {
     int take = first_single ? next : max_seg;
@@ -806,16 +809,27 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       const bool is_tail = split > 1 && it == full_waves;
       float* sk_rows = nullptr;
       int* sk_cnt = nullptr;
+      int* sk_done = nullptr;
       if (is_tail) {
         const int tt = t - full_tiles;
         sk_rows = p.splitk_scratch + (static_cast<long long>(tt) * (split - 1) * TILE_M + half * kBM + quad * 32 + lane) * BN;
         sk_cnt = p.splitk_cnt + (tt * 2 + half) * 4 + quad;
+        sk_done = p.splitk_done + (tt * 2 + half) * 4 + quad;
       }
-      if (is_tail && part > 0) {
-        // not the finisher: park the raw fp32 accumulators, signal, done with this item
-        float* dst = sk_rows + static_cast<long long>(part - 1) * TILE_M * BN;
+      // Every part of a split tail tile finishes a share of the tile's 64-column boxes (box b belongs to part
+      // b * owners / boxes, owners = min(split, boxes)): it parks its raw fp32 accumulators of the other boxes
+      // for their owners, waits until all parts have parked, and runs the ordinary epilogue on its own boxes
+      // with the other parts' partials added. The tail's epilogue work - bound by load latency - is thereby
+      // spread over all the CTAs that worked on the tile instead of falling on one.
+      constexpr int kBoxes = BN / 64 > 0 ? BN / 64 : 1;
+      const int sk_owners = split < kBoxes ? split : kBoxes;
+      auto sk_owner_of = [&](int c) { return ((BN >= 64 ? c >> 1 : 0) * sk_owners) / kBoxes; };
+      if (is_tail) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {
+          const int oc = sk_owner_of(c);
+          if (oc == part) continue;
+          float* dst = sk_rows + static_cast<long long>(part < oc ? part : part - 1) * TILE_M * BN;
           uint32_t r[32];
           tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + static_cast<uint32_t>(acc * BN + c * 32), r);
           tmem_ld_wait();
@@ -823,25 +837,30 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           for (int q = 0; q < 8; ++q)
             *reinterpret_cast<uint4*>(dst + c * 32 + q * 4) = make_uint4(r[q * 4], r[q * 4 + 1], r[q * 4 + 2], r[q * 4 + 3]);
         }
-        tc_fence_before();
         __threadfence();
         __syncwarp();
-        if (lane == 0) {
-          if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
-          else mbar_arrive(bar_tempty(acc));
-          red_add_release_sys(sk_cnt, 1);
-        }
-        continue;
-      }
-      if (is_tail) {
-        // finisher: every other part of this warp's rows must have been parked
         int okw = 1;
         if (lane == 0) {
-          okw = flag_wait_eq(sk_cnt, split - 1, ab, kStatusTimeoutTmemFull, budget) ? 1 : 0;
-          if (okw) *sk_cnt = 0;  // this warp is the only reader: clear for the next launch
+          red_add_release_sys(sk_cnt, 1);
+          if (part < sk_owners) okw = flag_wait_eq(sk_cnt, split, ab, kStatusTimeoutTmemFull, budget) ? 1 : 0;
+          // the last part through clears both counters for the next launch
+          if (okw && atomicAdd(sk_done, 1) == split - 1) {
+            *sk_cnt = 0;
+            *sk_done = 0;
+          }
         }
         okw = __shfl_sync(0xffffffffu, okw, 0);
         if (!okw) break;
+        if (part >= sk_owners) {
+          // more parts than boxes: this one only parked
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) {
+            if (CTA2) mbar_arrive_cluster(mapa_u32(bar_tempty(acc), 0));
+            else mbar_arrive(bar_tempty(acc));
+          }
+          continue;
+        }
       }
       const bool row_ok = row_in_tile < tc.rows;
       const int grow = tc.row0 + row_in_tile;  // global / sorted row
@@ -915,6 +934,7 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
                            p.g_scatter_rows == nullptr && quad * 32 + 32 <= tc.rows;
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
+        if (is_tail && sk_owner_of(c) != part) continue;  // another part finishes this box
         uint32_t r[32];
         const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                static_cast<uint32_t>(acc * BN + c * 32);
@@ -1193,7 +1213,10 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
         // role that gave up must never strand the others.)
         if (lane == 0) {
           if (pending_cnt != nullptr) {
-            if (p.rs_wire16) bulk_wait_all_but<BN / 64>(); else bulk_wait_all_but<BN / 32>();
+            // (a split tail tile issues fewer store groups than a whole tile: wait for everything there)
+            if (is_tail) bulk_wait_all();
+            else if (p.rs_wire16) bulk_wait_all_but<BN / 64>();
+            else bulk_wait_all_but<BN / 32>();
             fence_acq_rel_sys();
             red_add_release_sys(pending_cnt, 1);
           }

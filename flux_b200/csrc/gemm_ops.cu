@@ -214,6 +214,7 @@ int launch_fused_gemm(fluxb_comm* comm, GemmParams& p, int in_dtype,
   p.trace = comm->trace;
   p.splitk_scratch = comm->splitk_scratch;
   p.splitk_cnt = comm->splitk_cnt;
+  p.splitk_done = comm->splitk_cnt + comm->sm_count * 8;
   p.rank = comm->rank;
   p.world = comm->world;
   const int kind = is_8bit(in_dtype) ? 1 : 0;

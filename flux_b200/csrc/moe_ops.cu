@@ -24,6 +24,8 @@
 #include <mutex>
 #include <vector>
 
+#include <stdlib.h>
+
 #include "internal.h"
 
 namespace fluxb {
@@ -657,7 +659,9 @@ int fluxb_moe_gather_rs_forward_ep(fluxb_moe_gather_rs_t op, const void* x, int 
   } else {
     // four column groups: A streams from HBM four times (there is bandwidth to spare next to a tensor-bound GEMM),
     // and the combine of a group overlaps the GEMM of the next one
-    p.n_group = (n_tiles + 3) / 4;
+    int groups = 4;
+    if (const char* g = getenv("FLUXB_MOE_L1_GROUPS")) groups = atoi(g) > 0 ? atoi(g) : 4;
+    p.n_group = (n_tiles + groups - 1) / groups;
   }
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
   if (rc != FLUXB_OK) return rc;

@@ -198,7 +198,7 @@ int fluxb_comm_create(int rank, int world, fluxb_comm_t* out) {
   }
   // scratch of the split-K tail: one 128 x 256 fp32 tile per SM bounds every launch's need
   const size_t sk_bytes = static_cast<size_t>(sms) * kBM * 256 * sizeof(float);
-  const size_t cnt_bytes = static_cast<size_t>(sms) * 8 * sizeof(int);
+  const size_t cnt_bytes = static_cast<size_t>(sms) * 16 * sizeof(int);  // "parked" and "seen" counters
   if (cudaMalloc(reinterpret_cast<void**>(&c->splitk_scratch), sk_bytes) != cudaSuccess ||
       cudaMalloc(reinterpret_cast<void**>(&c->splitk_cnt), cnt_bytes) != cudaSuccess ||
       cudaMemset(c->splitk_cnt, 0, cnt_bytes) != cudaSuccess) {
@@ -247,6 +247,15 @@ int fluxb_status_peek(fluxb_comm_t comm, int* status) {
 int fluxb_status_clear(fluxb_comm_t comm) {
   FLUXB_REQUIRE(comm != nullptr, "status_clear: comm is NULL");
   *reinterpret_cast<volatile int*>(comm->status_host) = 0;
+  // a launch that gave up may have left the split-K tail's self-clearing counters part-way
+  if (comm->splitk_cnt != nullptr) {
+    int cur = -1;
+    FLUXB_CUDA(cudaGetDevice(&cur));
+    if (cur != comm->device) FLUXB_CUDA(cudaSetDevice(comm->device));
+    const cudaError_t e = cudaMemset(comm->splitk_cnt, 0, static_cast<size_t>(comm->sm_count) * 16 * sizeof(int));
+    if (cur != comm->device) cudaSetDevice(cur);
+    FLUXB_CUDA(e);
+  }
   return FLUXB_OK;
 }
 

@@ -39,6 +39,7 @@ def _show(name: str, event_ms: float, tr: torch.Tensor) -> None:
 
     print(f"{name:40s} event {event_ms:.4f} ms | us after first CTA start (min/med/max): first-operands {_fmt(rel(1))}"
           f" | last-UMMA {_fmt(rel(2))} | epilogue-end {_fmt(rel(3))} | comm-end {_fmt(rel(4))}"
+          f" | drain {_fmt((t[:, 3] - t[:, 2])[(t[:, 2] > 0) & (t[:, 3] > 0)] / 1e3)}"
           f" | flag-wait {_fmt(t[:, 5] / 1e3)} | ready-wait {_fmt(t[:, 6] / 1e3)}"
           f" | work items per CTA {int(t[:, 7].min())}-{int(t[:, 7].max())}", flush=True)
 

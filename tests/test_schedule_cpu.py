@@ -71,9 +71,12 @@ def check_order(segs, nseg, seg_first, bands):
     assert first_seen == [(seg_first + i) % nseg for i in range(nseg)]
     if nseg == 1:
         return
-    if bands == 1:  # all-gather: the own shard (= seg_first) is a band of its own at the start
-        k = next(i for i, s in enumerate(segs) if s != seg_first)
-        assert all(s != seg_first for s in segs[k:])
+    if bands == 1:  # all-gather: the own shard (= seg_first) is in the first band only
+        last_own = max(i for i, s in enumerate(segs) if s == seg_first)
+        early = set(segs[:last_own + 1])
+        assert early <= {(seg_first + i) % nseg for i in range(4)}, "the first band holds at most four segments"
+        k = next((i for i, s in enumerate(segs) if s not in early), len(segs))
+        assert all(s not in early for s in segs[k:]), "a later band returns to a segment of the first band"
     if bands == 2:  # reduce-scatter: the own rows (= the last segment of the rotation) are a band of their own at the end
         own = (seg_first + nseg - 1) % nseg
         k = next(i for i, s in enumerate(segs) if s == own)
