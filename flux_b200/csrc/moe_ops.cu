@@ -24,8 +24,6 @@
 #include <mutex>
 #include <vector>
 
-#include <stdlib.h>
-
 #include "internal.h"
 
 namespace fluxb {
@@ -657,10 +655,11 @@ int fluxb_moe_gather_rs_forward_ep(fluxb_moe_gather_rs_t op, const void* x, int 
     p.group_m = 1 << 20;
     t.group_m = p.group_m;
   } else {
-    // four column groups: A streams from HBM four times (there is bandwidth to spare next to a tensor-bound GEMM),
-    // and the combine of a group overlaps the GEMM of the next one
-    int groups = 4;
-    if (const char* g = getenv("FLUXB_MOE_L1_GROUPS")) groups = atoi(g) > 0 ? atoi(g) : 4;
+    // Column groups: A streams once per group (there is bandwidth to spare next to a tensor-bound GEMM) and the
+    // combine of a group overlaps the GEMM of the next one; only the last group's combine is exposed. Measured
+    // at config X: with A = 117 MB (TP=4) eight groups beat four (0.516 vs 0.537 ms; 2 and 16: 0.587, 0.55); with
+    // A = 470 MB (TP=1) four beat eight (1.68 vs 1.75 ms).
+    const int groups = static_cast<double>(p.M) * k_local * eb <= 128.0 * 1024 * 1024 ? 8 : 4;
     p.n_group = (n_tiles + groups - 1) / groups;
   }
   rc = launch_fused_gemm(comm, p, op->in_dtype, &t, stream);
