@@ -220,26 +220,39 @@ __host__ __device__ __forceinline__ int imin(int a, int b) { return a < b ? a : 
 __host__ __device__ __forceinline__ int imax(int a, int b) { return a > b ? a : b; }
 
 // Rasterisation bands for the segmented ops, in units of segments (= shards / owners) of `tps` M tiles.
-// Bands are at most 8 M tiles tall (taller bands re-stream B less often and draw less power).
-// first_single: the first band starts with this rank's own shard (all-gather: available at once) and is
-// filled up to 4 M tiles with the shards that arrive first (the push is slice-major, so their first 2 KB
-// slices are in after a few microseconds; a band of 2 M tiles costs 8 % of its tiles' time, one of 4 costs
-// 2 %); the following bands double in size, so that early tiles only need early arrivals.
-// last_single: the last band is exactly one segment (reduce-scatter: this rank's own rows, finished last).
+// Bands are at most 8 M tiles tall (taller bands re-stream B less often and draw less power; measured on the
+// plain GEMM: a band of 2 M tiles costs 8 % of its tiles' time, one of 4 costs 2 %).
+// first_single (all-gather): the first band starts with this rank's own shard, available at once, and is filled
+// up to 4 M tiles with the shards that arrive first (the push is slice-major: their first 2 KB slices are in
+// after a few microseconds). The second band has the same size and the sizes double from the third on: a
+// shard crosses NVLink in about 40 % of the time its tiles take to compute, so when band k starts, at
+// (segments before it) x (compute time of a segment), its last shard has been in for a while.
+// last_single (reduce-scatter): this rank's own rows are the last band, and the segment before them - the
+// owner that is about to start its own rows and waits for exactly these partials - is a band of its own, so
+// that every owner has one late peer only.
 inline void make_bands(GemmParams& p, int nseg, int tps, bool first_single, bool last_single) {
   int max_seg = tps > 0 ? 8 / tps : 1;
   if (max_seg < 1) max_seg = 1;
   int done = 0, nb = 0, next = tps > 0 && 4 / tps > 1 ? 4 / tps : 1;
-  const int body_end = last_single ? nseg - 1 : nseg;
-  while (done < body_end && nb < 7) {
+  const int tail_single = last_single ? (nseg >= 3 ? 2 : 1) : 0;
+  const int body_end = nseg - tail_single;
+  while (done < body_end && nb < 8 - 1 - tail_single) {
     int take = first_single ? next : max_seg;
     if (take > max_seg) take = max_seg;
     if (take > body_end - done) take = body_end - done;
     done += take;
     p.band_end[nb++] = done * tps;
-    next *= 2;
+    if (nb >= 2) next *= 2;
   }
-  if (done < nseg) p.band_end[nb++] = nseg * tps;
+  if (done < body_end) {
+    if (nb > 0) p.band_end[nb - 1] = body_end * tps; else p.band_end[nb++] = body_end * tps;
+    done = body_end;
+  }
+  while (done < nseg && nb < 8) {
+    done += 1;
+    p.band_end[nb++] = done * tps;
+  }
+  p.band_end[nb - 1] = nseg * tps;
   p.n_bands = nb;
 }
 
@@ -1278,7 +1291,9 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           // units of this CTA: u = cta_id, cta_id + num_ctas, ...; while the epilogue warps help (step 0, see
           // there) they take every second one
           const int stride = perm_helped && d == 0 ? 2 * num_ctas : num_ctas;
-          for (int u = cta_id; comm_ok && u < perm_units; u += stride)
+          int pu_first = cta_id - static_cast<int>((static_cast<long long>(d) * perm_units) % num_ctas);
+          if (pu_first < 0) pu_first += num_ctas;  // as for the push below: rotate the CTA that takes unit 0
+          for (int u = pu_first; comm_ok && u < perm_units; u += stride)
             comm_ok = permute_unit(std::integral_constant<int, 1>{}, u, src_rank, ctid, true);
         }
         if (p.ag_src != nullptr && d + d_first < p.world) {
@@ -1286,7 +1301,11 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
           if (dest < 0) dest += p.world;
           // units of one destination in slice-major order: the first 2 KB of every row go out first, so
           // that the consumer's walk along K can begin after a fraction of the shard has crossed
-          for (int u = cta_id; u < units_per_dest; u += num_ctas) {
+          // (the CTA that takes unit 0 rotates from destination to destination, so that all CTAs push even
+          // when a destination has fewer units than there are CTAs: 96 units per destination at TP=8)
+          int u_first = cta_id - static_cast<int>((static_cast<long long>(d) * units_per_dest) % num_ctas);
+          if (u_first < 0) u_first += num_ctas;
+          for (int u = u_first; u < units_per_dest; u += num_ctas) {
             const int ks = u / (push_chunks * ag_ups);
             const int rem = u - ks * (push_chunks * ag_ups);
             const int chunk = rem / ag_ups;

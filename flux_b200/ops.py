@@ -383,10 +383,12 @@ class GemmRS:
     the GEMM epilogue (src/pybind/gemm_rs.cc:30-60).
 
     Partial products travel to the rank that owns their rows in the 16-bit output format (one rounding per
-    partial, as in the reference, whose reduce buffer has the output dtype) and are summed there in the order
-    rank+1, rank+2, ..., own partial last. By default the sum is kept in fp32 and rounded once;
-    `ring_reduction=True` rounds it to the element type after every addition, which is what the reference's
-    `ring_reduce` kernel computes (src/gemm_rs/ring_reduce.cu:54-80). `fuse_reduction` asks the reference for
+    partial, as in the reference, whose reduce buffer has the output dtype) and are summed there in fp32 in a
+    fixed order (the peers that delivered early, summed by the communication warps; then the own fp32 partial;
+    then the peers that deliver last, added by the epilogue of the own tiles) and rounded once.
+    `ring_reduction=True` sums in the order rank+1, rank+2, ..., own partial last, and rounds the sum to the
+    element type after every addition, which is what the reference's `ring_reduce` kernel computes
+    (src/gemm_rs/ring_reduce.cu:54-80). `fuse_reduction` asks the reference for
     an in-kernel reduction; here the reduction is always inside the kernel, so the flag changes nothing.
     `fp32_wire = True` sends the partials as fp32 instead (no rounding before the sum, twice the NVLink bytes).
     Rounding points against the 1e-2 tolerance: one per partial + one at the end (default)."""
