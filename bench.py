@@ -104,9 +104,9 @@ def make_line(meas):
         "frac_of_burst_peak": ag_tflops / burst, "frac_of_sustained_peak": ag_tflops / sustained,
         "peak_burst": burst, "peak_sustained": sustained, "peak_source": f"{peak_src} cuBLAS bf16",
         "kernel": "fused_gemm_kernel (AG-GEMM launch)",
-        # ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the M=4096, N=6144, K=12288 launch: 709.2 MB;
+        # ncu (dram__bytes_read.sum + dram__bytes_write.sum) on the M=4096, N=6144, K=12288 launch: 712.7 MB;
         # DRAM traffic grows with the number of 6144-column blocks a launch covers
-        "traffic": 709.2e6 * (N0 // world) / 6144.0,
+        "traffic": 712.7e6 * (N0 // world) / 6144.0,
         "traffic_source": "ncu capture of the N=6144 launch (profiles/), scaled by N/6144",
         "algorithmic_bytes": 2.0 * (M * K0 + (N0 // world) * K0 + M * (N0 // world)),
         "gemm_rs": {"achieved": rs_tflops, "frac": rs_tflops / peak},
