@@ -1380,19 +1380,43 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc4[j][e] = 0.f;
               }
-              for (int k = 0; k < p.gr_topk; ++k) {
-                uint4 raw[4];
+              // The rows of the 4 tokens' top-k entries: lane (j * topk + k) fetches one entry of the scatter index
+              // and shuffles hand them out (a load of the index in front of every data load doubled the length
+              // of the dependent chain); the data loads of two k are in flight together.
+              int my_row = -1;
+              {
+                const int jj = lane / p.gr_topk, kk = lane - jj * p.gr_topk;
+                const int tok = blk * kGrTokBlock + cw * 8 + b4 + jj;
+                if (jj < 4 && tok < tpr)
+                  my_row = p.gr_scatter_index[(static_cast<long long>(owner) * tpr + tok) * p.gr_topk + kk] - p.gr_row_lo;
+                if (my_row < 0 || my_row >= p.gr_rows) my_row = -1;  // rows of other ranks' experts; a corrupt entry must not become a wild load
+              }
+              const bool idx_in_regs = 4 * p.gr_topk <= 32;
+              for (int k0 = 0; k0 < p.gr_topk; k0 += 2) {
+                uint4 raw2[2][4];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  raw[j] = make_uint4(0u, 0u, 0u, 0u);
-                  if (tl[j] < tpr && lane_on) {
-                    const int row = p.gr_scatter_index[(static_cast<long long>(owner) * tpr + tl[j]) * p.gr_topk + k] - p.gr_row_lo;
-                    if (row >= 0 && row < p.gr_rows)  // rows of other ranks' experts; a corrupt entry must not become a wild load
-                      raw[j] = ld_relaxed_gpu_v4(static_cast<const uint16_t*>(p.out) + static_cast<long long>(row) * p.ldo + col0 + lane * 8);
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    raw2[u][j] = make_uint4(0u, 0u, 0u, 0u);
+                    const int k = k0 + u;
+                    int row = -1;
+                    if (k < p.gr_topk) {
+                      if (idx_in_regs) {
+                        row = __shfl_sync(0xffffffffu, my_row, j * p.gr_topk + k);
+                      } else if (tl[j] < tpr) {
+                        row = p.gr_scatter_index[(static_cast<long long>(owner) * tpr + tl[j]) * p.gr_topk + k] - p.gr_row_lo;
+                        if (row >= p.gr_rows) row = -1;
+                      }
+                    }
+                    if (row >= 0 && tl[j] < tpr && lane_on)
+                      raw2[u][j] = ld_relaxed_gpu_v4(static_cast<const uint16_t*>(p.out) + static_cast<long long>(row) * p.ldo + col0 + lane * 8);
                   }
-                }
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
+                  const uint4* raw = raw2[u];
                   const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
@@ -1452,17 +1476,23 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
 #pragma unroll
                 for (int e = 0; e < 8; ++e) acc4[j][e] = 0.f;
               }
-              for (int sr = 0; sr < p.world; ++sr) {
-                uint4 raw[4];
+              for (int sr0 = 0; sr0 < p.world; sr0 += 2) {  // two sources' loads in flight together
+                uint4 raw2[2][4];
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
+#pragma unroll
+                  for (int j = 0; j < 4; ++j) {
+                    raw2[u][j] = make_uint4(0u, 0u, 0u, 0u);
+                    if (sr0 + u < p.world && tl[j] < tpr && lane_on)
+                      raw2[u][j] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.gr_local_stage) +
+                                                                   (sr0 + u) * slot + static_cast<long long>(tl[j]) * p.N +
+                                                                   col0 + lane * 8);
+                  }
+#pragma unroll
+                for (int u = 0; u < 2; ++u)
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  raw[j] = make_uint4(0u, 0u, 0u, 0u);
-                  if (tl[j] < tpr && lane_on)
-                    raw[j] = *reinterpret_cast<const uint4*>(static_cast<const uint16_t*>(p.gr_local_stage) + sr * slot +
-                                                             static_cast<long long>(tl[j]) * p.N + col0 + lane * 8);
-                }
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
+                  const uint4* raw = raw2[u];
                   const uint32_t w[4] = {raw[j].x, raw[j].y, raw[j].z, raw[j].w};
 #pragma unroll
                   for (int e = 0; e < 4; ++e) {
