@@ -1,5 +1,6 @@
 // Host side of the dense ops: the launcher of the fused kernel, the plain
 // GEMM entry point, AG-GEMM and GEMM-RS (with the owner-side fp32 reduction).
+#include <stdlib.h>
 #include <string.h>
 
 #include <vector>
@@ -83,13 +84,21 @@ int ag_slices_per_flag(long long row_bytes) {
   return spf < 1 ? 1 : static_cast<int>(spf);
 }
 
+// Transport when the caller's tuning names none: the environment variable FLUXB_AG_MODE (1 or 2), else the
+// kernel's own push.
+static int default_ag_mode() {
+  const char* e = getenv("FLUXB_AG_MODE");
+  return (e != nullptr && atoi(e) == kAgModeCopyEngine) ? kAgModeCopyEngine : kAgModeKernelPush;
+}
+
 int resolve_ag_mode(const fluxb_tuning* tuning) {
   if (tuning != nullptr && tuning->ag_mode == kAgModeCopyEngine) return kAgModeCopyEngine;
-  return kAgModeKernelPush;
+  if (tuning != nullptr && tuning->ag_mode != 0) return kAgModeKernelPush;
+  return default_ag_mode();
 }
 
 int resolve_ag_unit_rows(const fluxb_tuning* tuning) {
-  if (tuning != nullptr && tuning->ag_mode == kAgModeCopyEngine) return kBM;  // a copied piece arrives whole
+  if (resolve_ag_mode(tuning) == kAgModeCopyEngine) return kBM;  // a copied piece arrives whole
   if (tuning != nullptr && tuning->ag_mode == 3) return 64;
   if (tuning != nullptr && tuning->ag_mode == 4) return 128;
   return 32;
@@ -135,7 +144,10 @@ int ag_dma_push(const fluxb_comm* comm, AgDma* d, const void* src, int m_local, 
   }
   FLUXB_CUDA(cudaEventRecord(d->ev_start, main));
   FLUXB_CUDA(cudaStreamWaitEvent(d->side, d->ev_start, 0));
-  const int piece = 2 * kBM;
+  // One copy per 1024 rows: a peer-to-peer cudaMemcpyAsync costs the host ~20 us, so pieces of 256 rows made a
+  // launch at TP=8 host-bound (28 copies: ten launches in a row took 0.6 ms each, a single one 0.47 ms), and the
+  // tiles of a peer's shard are not due before this rank's own shard is worked off anyway.
+  const int piece = 8 * kBM;
   for (int dd = include_self ? 0 : 1; dd < world; ++dd) {
     const int dest = (rank - dd + world) % world;
     for (int r0 = 0; r0 < m_local; r0 += piece) {

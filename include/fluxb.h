@@ -76,7 +76,8 @@ typedef struct fluxb_tuning {
   int ag_mode;  /* transport of the all-gather: 1 = pushed by the fused kernel's communication warps (units of 32
                    rows x 2 KB per system-scope release; 3 = units of 64 rows, 4 = units of 128 rows), 2 = copy
                    engines on a side stream (AllGatherOption.use_cuda_core_ag = true / false in the reference,
-                   src/coll/ths_op/all_gather_types.h:35-43); the consuming kernel is the same */
+                   src/coll/ths_op/all_gather_types.h:35-43); the consuming kernel is the same; 0 = the environment variable
+                   FLUXB_AG_MODE (1 or 2) if set, else 1 */
 } fluxb_tuning;
 
 const char* fluxb_last_error(void);
