@@ -150,3 +150,34 @@ def test_tile_shape_choice(probe):
     # the caller's tuning wins
     assert resolve(probe, 8, 512, 6144, bn=128, cg=1) == (128, 1)
     assert resolve(probe, 8, 512, 6144, cg=1)[1] == 1
+
+
+def _band_segments(segs, nseg):
+    """Segments grouped by band, from the visiting order: a band ends where a segment that was already left
+    is never returned to; inside a band the walk interleaves the band's segments column by column."""
+    last_seen = {s: max(i for i, x in enumerate(segs) if x == s) for s in set(segs)}
+    bands, cur, end = [], [], -1
+    for i, s in enumerate(segs):
+        if s not in cur:
+            cur.append(s)
+        end = max(end, last_seen[s])
+        if i == end:
+            bands.append(cur)
+            cur = []
+    return bands
+
+
+def test_band_sizes_of_the_benchmark_shapes(probe):
+    """The bands the two protocols rely on, at the per-rank shapes of the dense benchmark."""
+    # all-gather (bands = 1), rank 3 of 8: own shard + the first arrival, two more, then the remaining four
+    segs = walk(probe, 8, 512, 6144, 256, 2, 3, 0, 1)
+    assert _band_segments(segs, 8) == [[3, 4], [5, 6], [7, 0, 1, 2]]
+    # TP=4: own, next, last two; TP=2: one shard per band
+    assert _band_segments(walk(probe, 4, 1024, 12288, 256, 2, 1, 0, 1), 4) == [[1], [2], [3, 0]]
+    assert _band_segments(walk(probe, 2, 2048, 24576, 256, 2, 1, 0, 1), 2) == [[1], [0]]
+    # reduce-scatter (bands = 2), rank 2 of 8 (seg_first = 3): the owner that starts its own rows next (rank 1)
+    # is a band of its own before this rank's own rows, so every owner has exactly one late peer
+    segs = walk(probe, 8, 512, 12288, 256, 2, 3, 0, 2)
+    assert _band_segments(segs, 8) == [[3, 4, 5, 6], [7, 0], [1], [2]]
+    assert _band_segments(walk(probe, 4, 1024, 12288, 256, 2, 3, 0, 2), 4) == [[3, 0], [1], [2]]
+    assert _band_segments(walk(probe, 2, 2048, 12288, 256, 2, 1, 0, 2), 2) == [[1], [0]]
