@@ -835,7 +835,10 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       // with the other parts' partials added. The tail's epilogue work - bound by load latency - is thereby
       // spread over all the CTAs that worked on the tile instead of falling on one.
       constexpr int kBoxes = BN / 64 > 0 ? BN / 64 : 1;
-      const int sk_owners = split < kBoxes ? split : kBoxes;
+      // A tile whose result is pushed to its owner (reduce-scatter, another rank's rows) is finished by part 0
+      // alone: the owner counts one publish per epilogue warp of ONE CTA (pair half) per tile.
+      const bool sk_pushed = p.epi_mode == kEpiRsPush && tc.seg != p.rank;
+      const int sk_owners = sk_pushed ? 1 : (split < kBoxes ? split : kBoxes);
       auto sk_owner_of = [&](int c) { return ((BN >= 64 ? c >> 1 : 0) * sk_owners) / kBoxes; };
       if (is_tail) {
 #pragma unroll 1
