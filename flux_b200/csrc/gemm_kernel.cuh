@@ -256,6 +256,18 @@ inline void make_bands(GemmParams& p, int nseg, int tps, bool first_single, bool
   p.n_bands = nb;
 }
 
+// Reduce-scatter: how many peers deliver their partials of an owner's rows late, i.e. compute them in their
+// last band of peer rows (the band whose tiles the pushing side publishes at once). By symmetry it is the number
+// of segments in that band: with explicit bands the band before the last, otherwise (uniform bands) the rows of
+// the previous rank only. The kernel's pushing side and the owner side must agree on this number.
+inline int rs_late_peers(const GemmParams& p, int world, int tps) {
+  if (p.n_bands >= 2 && tps > 0) {
+    const int first_seg = p.n_bands >= 3 ? p.band_end[p.n_bands - 3] / tps : 0;
+    return (world - 1) - first_seg;
+  }
+  return 1;
+}
+
 // TILE_M = 128 (one CTA) or 256 (CTA pair, `half` = rank of this CTA inside the pair).
 // Also compiled for the host: the CPU tests walk the schedule to check that every tile is visited once.
 template <int BN, int TILE_M>

@@ -732,14 +732,8 @@ int fluxb_gemm_rs_forward(fluxb_gemm_rs_t op, const void* a, const void* b, int 
   // reduction (its order and roundings are fixed) nor with fp32 partials.
   p.rs_n_late = 0;
   if (p.rs_wire16 && !p.rs_ring) {
-    if (p.n_bands >= 2) {
-      const int tile_m = resolve_cta_group(p, tuning) == 2 ? 2 * kBM : kBM;
-      const int tps = (mpr + tile_m - 1) / tile_m;
-      const int first_seg = p.n_bands >= 3 ? p.band_end[p.n_bands - 3] / tps : 0;
-      p.rs_n_late = (world - 1) - first_seg;
-    } else {
-      p.rs_n_late = 1;
-    }
+    const int tile_m = resolve_cta_group(p, tuning) == 2 ? 2 * kBM : kBM;
+    p.rs_n_late = rs_late_peers(p, world, (mpr + tile_m - 1) / tile_m);
   }
   p.rs_out = out;
   p.rs_out_type = ot;

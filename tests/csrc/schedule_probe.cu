@@ -85,3 +85,13 @@ extern "C" void probe_resolve(int nseg, int seg_rows, int n, int sm_count, int b
   *cg = resolve_cta_group(p, tp);
   *bn = resolve_block_n(&comm, p, tp, 0);
 }
+
+// Late peers per owner of a reduce-scatter launch with the library's own bands (rs_late_peers of gemm_kernel.cuh).
+extern "C" int probe_rs_late_peers(int nseg, int seg_rows, int cta_group) {
+  GemmParams p;
+  memset(&p, 0, sizeof(p));
+  const int tile_m = cta_group == 2 ? 2 * kBM : kBM;
+  const int tps = (seg_rows + tile_m - 1) / tile_m;
+  make_bands(p, nseg, tps, false, true);
+  return rs_late_peers(p, nseg, tps);
+}

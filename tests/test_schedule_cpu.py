@@ -42,6 +42,8 @@ def probe():
     lib = C.CDLL(so)
     lib.probe_dense_schedule.restype = C.c_int
     lib.probe_dense_schedule.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int)] * 3 + [C.c_int]
+    lib.probe_rs_late_peers.restype = C.c_int
+    lib.probe_rs_late_peers.argtypes = [C.c_int] * 3
     lib.probe_resolve.restype = None
     lib.probe_resolve.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int)] * 2
     return lib
@@ -181,3 +183,20 @@ def test_band_sizes_of_the_benchmark_shapes(probe):
     assert _band_segments(segs, 8) == [[3, 4, 5, 6], [7, 0], [1], [2]]
     assert _band_segments(walk(probe, 4, 1024, 12288, 256, 2, 3, 0, 2), 4) == [[3, 0], [1], [2]]
     assert _band_segments(walk(probe, 2, 2048, 12288, 256, 2, 1, 0, 2), 2) == [[1], [0]]
+
+
+def test_late_peers_match_the_last_peer_band(probe):
+    """Reduce-scatter: the owner side's count of late peers equals the number of segments in the band whose tiles
+    the pushing side publishes at once (the band before this rank's own rows), for any shape: a mismatch would
+    leave an owner waiting for arrivals on the wrong counter."""
+    rng = random.Random(99)
+    cases = [(8, 512, 2), (4, 1024, 2), (2, 2048, 2), (8, 512, 1), (8, 37, 1), (3, 300, 2)]
+    cases += [(rng.choice([2, 3, 4, 8]), rng.choice([rng.randint(1, 2200), 128 * rng.randint(1, 16)]), rng.choice([1, 2]))
+              for _ in range(300)]
+    for nseg, seg_rows, cg in cases:
+        segs = walk(probe, nseg, seg_rows, 512, 256, cg, 1 % nseg, 0, 2)
+        bands = _band_segments(segs, nseg)
+        assert len(bands) >= 2 and len(bands[-1]) == 1
+        assert probe.probe_rs_late_peers(nseg, seg_rows, cg) == len(bands[-2]), (nseg, seg_rows, cg, bands)
+        if nseg >= 3:
+            assert len(bands[-2]) == 1, "every owner has exactly one late peer"
