@@ -256,6 +256,19 @@ inline void make_bands(GemmParams& p, int nseg, int tps, bool first_single, bool
   p.n_bands = nb;
 }
 
+// Split-K tail: which part finishes the 32-column step `c` of a tail tile that is BN columns wide and cut into
+// `split` parts. Steps are owned in pairs (one 64-column box = one staged store), box b by part
+// b * owners / boxes with owners = min(split, boxes); parts >= owners only park. A tile that is pushed to
+// another owner (`pushed`) is finished by part 0 alone.
+__host__ __device__ __forceinline__ int splitk_owners(int split, int bn, bool pushed) {
+  const int boxes = bn / 64 > 0 ? bn / 64 : 1;
+  return pushed ? 1 : (split < boxes ? split : boxes);
+}
+__host__ __device__ __forceinline__ int splitk_owner_of(int c, int split, int bn, bool pushed) {
+  const int boxes = bn / 64 > 0 ? bn / 64 : 1;
+  return ((bn >= 64 ? c >> 1 : 0) * splitk_owners(split, bn, pushed)) / boxes;
+}
+
 // Reduce-scatter: how many peers deliver their partials of an owner's rows late, i.e. compute them in their
 // last band of peer rows (the band whose tiles the pushing side publishes at once). By symmetry it is the number
 // of segments in that band: with explicit bands the band before the last, otherwise (uniform bands) the rows of
@@ -846,12 +859,11 @@ __device__ __forceinline__ void fused_gemm_body(const GemmParams& p, const uint3
       // for their owners, waits until all parts have parked, and runs the ordinary epilogue on its own boxes
       // with the other parts' partials added. The tail's epilogue work - bound by load latency - is thereby
       // spread over all the CTAs that worked on the tile instead of falling on one.
-      constexpr int kBoxes = BN / 64 > 0 ? BN / 64 : 1;
       // A tile whose result is pushed to its owner (reduce-scatter, another rank's rows) is finished by part 0
       // alone: the owner counts one publish per epilogue warp of ONE CTA (pair half) per tile.
       const bool sk_pushed = p.epi_mode == kEpiRsPush && tc.seg != p.rank;
-      const int sk_owners = sk_pushed ? 1 : (split < kBoxes ? split : kBoxes);
-      auto sk_owner_of = [&](int c) { return ((BN >= 64 ? c >> 1 : 0) * sk_owners) / kBoxes; };
+      const int sk_owners = splitk_owners(split, BN, sk_pushed);
+      auto sk_owner_of = [&](int c) { return splitk_owner_of(c, split, BN, sk_pushed); };
       if (is_tail) {
 #pragma unroll 1
         for (int c = 0; c < BN / 32; ++c) {

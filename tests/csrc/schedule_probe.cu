@@ -95,3 +95,7 @@ extern "C" int probe_rs_late_peers(int nseg, int seg_rows, int cta_group) {
   make_bands(p, nseg, tps, false, true);
   return rs_late_peers(p, nseg, tps);
 }
+
+// Owner part of column step c of a split tail tile (splitk_owner_of / splitk_owners of gemm_kernel.cuh).
+extern "C" int probe_splitk_owner(int c, int split, int bn, int pushed) { return splitk_owner_of(c, split, bn, pushed != 0); }
+extern "C" int probe_splitk_owners(int split, int bn, int pushed) { return splitk_owners(split, bn, pushed != 0); }

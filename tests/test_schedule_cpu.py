@@ -42,6 +42,10 @@ def probe():
     lib = C.CDLL(so)
     lib.probe_dense_schedule.restype = C.c_int
     lib.probe_dense_schedule.argtypes = [C.c_int] * 8 + [C.POINTER(C.c_int)] * 3 + [C.c_int]
+    for fn in (lib.probe_splitk_owner, lib.probe_splitk_owners):
+        fn.restype = C.c_int
+    lib.probe_splitk_owner.argtypes = [C.c_int] * 4
+    lib.probe_splitk_owners.argtypes = [C.c_int] * 3
     lib.probe_rs_late_peers.restype = C.c_int
     lib.probe_rs_late_peers.argtypes = [C.c_int] * 3
     lib.probe_resolve.restype = None
@@ -200,3 +204,21 @@ def test_late_peers_match_the_last_peer_band(probe):
         assert probe.probe_rs_late_peers(nseg, seg_rows, cg) == len(bands[-2]), (nseg, seg_rows, cg, bands)
         if nseg >= 3:
             assert len(bands[-2]) == 1, "every owner has exactly one late peer"
+
+
+def test_split_tail_box_ownership(probe):
+    """Split-K tail: every 32-column step of a tail tile is finished by exactly one part below `owners`, the two
+    steps of a 64-column box (one staged store) by the same part, every owning part has work, and a tile that is
+    pushed to another rank is finished by part 0 alone (its owner counts the publishes of one CTA per tile)."""
+    for bn in (64, 128, 192, 256):
+        steps = bn // 32
+        for split in range(2, 9):
+            owners = probe.probe_splitk_owners(split, bn, 0)
+            assert owners == min(split, max(1, bn // 64))
+            own = [probe.probe_splitk_owner(c, split, bn, 0) for c in range(steps)]
+            assert all(0 <= o < owners for o in own) and sorted(set(own)) == list(range(owners))
+            assert own == sorted(own)
+            if bn >= 64:
+                assert all(own[c] == own[c ^ 1] for c in range(steps))
+            assert probe.probe_splitk_owners(split, bn, 1) == 1
+            assert all(probe.probe_splitk_owner(c, split, bn, 1) == 0 for c in range(steps))
